@@ -1,0 +1,124 @@
+// NVFP4 -> dense conversion and the quantized matrix x vector product.
+#include "common.cuh"
+
+namespace metis {
+
+__device__ __forceinline__ float scale_at(const uint8_t* scales, int32_t sf_layout, int64_t r,
+                                          int64_t k, int64_t sf_cols, int64_t tiles) {
+  const int64_t off = (sf_layout == METIS_SF_MMA) ? sf_mma_offset(r, k, tiles) : r * sf_cols + k;
+  return e4m3_to_float(__ldg(scales + off));
+}
+
+// One thread per 8 elements (4 code bytes).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+dequantize_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                  const float* __restrict__ unit_ptr, int32_t sf_layout, int64_t R, int64_t C,
+                  const float* __restrict__ add_row_vec, TO* __restrict__ out, int64_t ld) {
+  const float unit = __ldg(unit_ptr);
+  const int64_t chunks_per_row = C >> 3;
+  const int64_t total = R * chunks_per_row;
+  const int64_t sf_cols = C >> 4;
+  const int64_t tiles = sf_tiles_per_row(C);
+  for (int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x; c < total; c += (int64_t)gridDim.x * 256) {
+    const int64_t r = c / chunks_per_row;
+    const int64_t ch = c - r * chunks_per_row;
+    const uint32_t w = __ldg(codes + c);
+    // value = e2m1 * (e4m3 * unit): the same two roundings as quant.py:23-35
+    const float d = __fmul_rn(scale_at(scales, sf_layout, r, ch >> 1, sf_cols, tiles), unit);
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t nib = (w >> (4 * i)) & 15u;
+      float val = __fmul_rn(e2m1_value(nib & 7u), d);
+      if (nib & 8u) val = -val;
+      y[i] = val;
+    }
+    if (add_row_vec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = __fadd_rn(__ldg(add_row_vec + ch * 8 + i), y[i]);
+    }
+    TO* dst = out + r * ld + ch * 8;
+    if constexpr (sizeof(TO) == 2) {
+      __nv_bfloat162 o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(o);
+    } else {
+      reinterpret_cast<float4*>(dst)[0] = make_float4(y[0], y[1], y[2], y[3]);
+      reinterpret_cast<float4*>(dst)[1] = make_float4(y[4], y[5], y[6], y[7]);
+    }
+  }
+}
+
+// out[r] = sum_c v[c] * value(Q[r][c]).  One warp per row; a lane walks chunks of 8 elements.
+// Per block of 16 the inner sum of v * e2m1 is formed first, then scaled once.
+__global__ void __launch_bounds__(256)
+gemv_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+            const float* __restrict__ unit_ptr, int32_t sf_layout, int64_t R, int64_t C,
+            const float* __restrict__ v, float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= R) return;
+  const int64_t chunks_per_row = C >> 3;
+  const int64_t sf_cols = C >> 4;
+  const int64_t tiles = sf_tiles_per_row(C);
+  float acc = 0.0f;
+  for (int64_t ch = lane; ch < chunks_per_row; ch += 32) {
+    const uint32_t w = __ldg(codes + row * chunks_per_row + ch);
+    const float sc = scale_at(scales, sf_layout, row, ch >> 1, sf_cols, tiles);
+    float part = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t nib = (w >> (4 * i)) & 15u;
+      float val = e2m1_value(nib & 7u);
+      if (nib & 8u) val = -val;
+      part = fmaf(val, v ? __ldg(v + ch * 8 + i) : 1.0f, part);
+    }
+    acc = fmaf(part, sc, acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) out[row] = acc * __ldg(unit_ptr);
+}
+
+}  // namespace metis
+
+using namespace metis;
+
+extern "C" int32_t metis_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales, const float* unit,
+                                          int32_t sf_layout, int64_t R, int64_t C,
+                                          const float* add_row_vec, void* out, int32_t out_dtype,
+                                          int64_t ld, void* stream) {
+  if (!codes || !scales || !unit || !out) return fail(METIS_ERR_BAD_ARGUMENT, "null pointer");
+  if (R <= 0 || C <= 0 || C % 16 != 0) return fail(METIS_ERR_BAD_SHAPE, "bad shape [%lld, %lld]", (long long)R, (long long)C);
+  if (sf_layout != METIS_SF_ROWMAJOR && sf_layout != METIS_SF_MMA) return fail(METIS_ERR_BAD_ARGUMENT, "unknown sf_layout %d", sf_layout);
+  if (out_dtype != METIS_DTYPE_BF16 && out_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown out_dtype %d", out_dtype);
+  if (ld < C || ld % 8 != 0 || !aligned16(out) || !aligned16(codes))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "out and codes must be 16-byte aligned, ld a multiple of 8 and >= C");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t total = R * (C >> 3);
+  int64_t blocks = ceil_div(total, 256);
+  const int64_t cap = (int64_t)device_sm_count() * 32;
+  if (blocks > cap) blocks = cap;
+  const uint32_t* c32 = reinterpret_cast<const uint32_t*>(codes);
+  if (out_dtype == METIS_DTYPE_BF16)
+    dequantize_kernel<<<(unsigned)blocks, 256, 0, st>>>(c32, scales, unit, sf_layout, R, C, add_row_vec, static_cast<__nv_bfloat16*>(out), ld);
+  else
+    dequantize_kernel<<<(unsigned)blocks, 256, 0, st>>>(c32, scales, unit, sf_layout, R, C, add_row_vec, static_cast<float*>(out), ld);
+  METIS_CUDA_OK(cudaGetLastError());
+  return METIS_OK;
+}
+
+extern "C" int32_t metis_nvfp4_gemv(const uint8_t* codes, const uint8_t* scales, const float* unit,
+                                    int32_t sf_layout, int64_t R, int64_t C, const float* v, float* out,
+                                    void* stream) {
+  if (!codes || !scales || !unit || !out) return fail(METIS_ERR_BAD_ARGUMENT, "null pointer");
+  if (R <= 0 || C <= 0 || C % 16 != 0) return fail(METIS_ERR_BAD_SHAPE, "bad shape [%lld, %lld]", (long long)R, (long long)C);
+  if (sf_layout != METIS_SF_ROWMAJOR && sf_layout != METIS_SF_MMA) return fail(METIS_ERR_BAD_ARGUMENT, "unknown sf_layout %d", sf_layout);
+  if (!aligned16(codes)) return fail(METIS_ERR_BAD_ALIGNMENT, "codes must be 16-byte aligned");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  gemv_kernel<<<(unsigned)ceil_div(R, 8), 256, 0, st>>>(reinterpret_cast<const uint32_t*>(codes), scales, unit, sf_layout, R, C, v, out);
+  METIS_CUDA_OK(cudaGetLastError());
+  return METIS_OK;
+}

@@ -1,0 +1,523 @@
+// NVFP4 block-scaled GEMM with a fused bf16 rank-r side product, for sm_100a.
+//
+//   D[M,N] = g * ( sum_k A[m,k] B[n,k] + sum_j T[m,j] U[n,j] ) + rank-1 terms (+ C)
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0     TMA producer: per pipeline stage one 128 x 128-byte box of A codes, one
+//              BN x 128-byte box of B codes (both 128-byte swizzled) and the matching E4M3
+//              scale tiles (plain bulk copies: the scale layout makes them contiguous).
+//   warp 1     tensor-core issuer: copies the scale tiles shared memory -> tensor memory
+//              (tcgen05.cp), then issues four K=64 tcgen05.mma.kind::mxf4nvf4.block_scale per
+//              stage into the fp32 accumulator in tensor memory; the rank-r product runs as extra
+//              pipeline iterations whose stages hold 64-column bf16 panels of T and U and are
+//              consumed by tcgen05.mma.kind::f16 into the same accumulator.
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32 lanes), apply the
+//              scalar, the rank-1 terms and the optional addend, store bf16 or fp32.
+// Hand-offs are mbarriers; every wait is bounded and reports through the status word.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace metis {
+
+constexpr int kBM = 128;             // rows of A per tile (the MMA M)
+constexpr int kBKBytes = 128;        // bytes of packed codes per row per stage = 256 elements
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kSfaCol = 448;         // tensor-memory columns [448,464): scales of A for one stage
+constexpr int kSfbCol = 464;         // tensor-memory columns [464,496): scales of B for one stage
+constexpr uint32_t kSpinLimit = 4u << 20;
+
+// debug knob carried in metis_gemm_args.reserved: the producer arms the first stage's barrier
+// for the scale bytes of A but never issues that copy, so the consumer's bounded wait expires.
+constexpr int kDebugDropFirstSfa = 1;
+
+template <int BN> struct GemmCfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kAccStages = (BN == 256) ? 1 : 2;
+  static constexpr int kABytes = kBM * kBKBytes;                   // 16 KiB
+  static constexpr int kBBytes = BN * kBKBytes;                    // 16 or 32 KiB
+  static constexpr int kSfaBytes = 4 * 512;                        // 4 scale tiles (256 elements)
+  static constexpr int kSfbBytes = (BN / 128) * 4 * 512;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+  int64_t M, N, K;
+  int32_t rank;
+  int32_t debug;
+  const uint8_t* a_scales;
+  const uint8_t* b_scales;
+  const float* a_unit;
+  const float* b_unit;
+  float alpha;
+  const float* cvec0;  const float* rvec0;
+  const float* cvec1;  const float* rvec1;
+  const void* c;  int64_t ldc;
+  void* d;        int64_t ldd;
+  int32_t* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the phase did not complete within the limit or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if (i > 32) __nanosleep(64);
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_copy_scales(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_fp4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t acc) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p; }"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (64-bit): start address >> 4 in [0,14), leading byte offset
+// >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in [46,48), swizzle
+// mode in [61,64) (0 none, 2 = 128-byte).
+// K-major operand tile stored as rows of 128 bytes, 128-byte swizzled: groups of 8 rows are
+// 1024 bytes apart.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// One 512-byte scale tile: 32 rows of 16 bytes, not swizzled; groups of 8 rows are 128 bytes apart.
+__device__ __forceinline__ uint64_t scale_tile_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+
+// Instruction descriptors (32-bit): formats of A [7,10) and B [10,13), N>>3 in [17,23),
+// M>>4 in [24,29); both operands K-major.
+__host__ __device__ constexpr uint32_t idesc_fp4(int bn) {
+  // A, B = e2m1 (1); scale format UE4M3 (bit 23 = 0); scale ids 0; K = 64 (bit 31 = 0)
+  return (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t idesc_bf16(int bn) {
+  // D = f32 (1 in [4,6)); A, B = bf16 (1)
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ void report(int32_t* status, volatile int* abort_flag, int32_t code) {
+  *abort_flag = 1;
+  if (status) atomicCAS(status, 0, code);
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------------
+
+template <int BN, typename TD>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_u,
+                  const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kAccStages = Cfg::kAccStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;                                   // [kStages]  TMA bytes landed
+  uint64_t* empty = bars + kStages;                        // [kStages]  MMAs finished reading the stage
+  uint64_t* acc_full = bars + 2 * kStages;                 // [kAccStages] accumulator complete
+  uint64_t* acc_empty = bars + 2 * kStages + kAccStages;   // [kAccStages] accumulator drained
+  uint64_t* drain = bars + 2 * kStages + 2 * kAccStages;   // error path only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccStages + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int64_t tiles_m = (p.M + kBM - 1) / kBM;
+  const int64_t tiles_n = (p.N + BN - 1) / BN;
+  const int64_t num_tiles = tiles_m * tiles_n;
+  const int k_iters = (int)((p.K + 255) / 256);
+  const int r_iters = (p.rank + 63) / 64;
+  const int iters = k_iters + r_iters;
+  const int64_t sf_tiles_a = sf_tiles_per_row(p.K);        // per 128-row block (A and B share K)
+  const int64_t b_row_blocks = (p.N + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool first = true;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
+        const int32_t m0 = (int32_t)(tm * kBM), n0 = (int32_t)(tn * BN);
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
+            report(p.status, abort_flag, METIS_DEV_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + stage * Cfg::kStageBytes;
+          uint8_t* sa = st;
+          uint8_t* sb = st + Cfg::kABytes;
+          uint8_t* ssfa = sb + Cfg::kBBytes;
+          uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
+          if (it < k_iters) {
+            // scale tiles of B exist only for whole 128-row blocks of N
+            const int64_t rb0 = (int64_t)n0 >> 7;
+            int sfb_blocks = 0;
+            for (int b = 0; b < BN / 128; ++b) sfb_blocks += (rb0 + b < b_row_blocks) ? 1 : 0;
+            mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes + Cfg::kSfaBytes + sfb_blocks * 2048);
+            tma_load_2d(sa, &map_a, it * kBKBytes, m0, &full[stage]);
+            tma_load_2d(sb, &map_b, it * kBKBytes, n0, &full[stage]);
+            const bool drop = first && (p.debug & kDebugDropFirstSfa);
+            if (!drop)
+              bulk_load(ssfa, p.a_scales + (((int64_t)m0 >> 7) * sf_tiles_a + (int64_t)it * 4) * 512, 2048, &full[stage]);
+            for (int b = 0; b < sfb_blocks; ++b)
+              bulk_load(ssfb + b * 2048, p.b_scales + ((rb0 + b) * sf_tiles_a + (int64_t)it * 4) * 512, 2048, &full[stage]);
+            first = false;
+          } else {
+            const int j = it - k_iters;   // 64-column panel of the rank-r factors
+            mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes);
+            tma_load_2d(sa, &map_t, j * 64, m0, &full[stage]);
+            tma_load_2d(sb, &map_u, j * 64, n0, &full[stage]);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== tensor-core issuer =====
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      bool issued = false;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
+          report(p.status, abort_flag, METIS_DEV_TIMEOUT_EPI);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int it = 0; it < iters; ++it) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) {
+            report(p.status, abort_flag, METIS_DEV_TIMEOUT_TMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint8_t* st = smem + stage * Cfg::kStageBytes;
+          const uint32_t sa = smem_u32(st);
+          const uint32_t sb = sa + Cfg::kABytes;
+          const uint32_t ssfa = sb + Cfg::kBBytes;
+          const uint32_t ssfb = ssfa + Cfg::kSfaBytes;
+          if (it < k_iters) {
+            // scale tile j of this stage serves MMA j: 4 tensor-memory columns per 128 rows
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              tc_copy_scales(tmem_base + kSfaCol + 4 * j, scale_tile_desc(ssfa + j * 512));
+#pragma unroll
+              for (int b = 0; b < BN / 128; ++b)
+                tc_copy_scales(tmem_base + kSfbCol + (BN / 128) * 4 * j + 4 * b,
+                               scale_tile_desc(ssfb + b * 2048 + j * 512));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // 64 elements of K = 32 bytes inside the 128-byte swizzled row
+              tc_mma_fp4(d_tmem, operand_desc(sa + j * 32), operand_desc(sb + j * 32), idesc_fp4(BN),
+                         tmem_base + kSfaCol + 4 * j, tmem_base + kSfbCol + (BN / 128) * 4 * j,
+                         (it > 0 || j > 0) ? 1u : 0u);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // 16 bf16 of the rank dimension = 32 bytes
+              tc_mma_bf16(d_tmem, operand_desc(sa + j * 32), operand_desc(sb + j * 32), idesc_bf16(BN),
+                          (it > 0 || j > 0) ? 1u : 0u);
+            }
+          }
+          issued = true;
+          tc_commit(&empty[stage]);          // frees the stage once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(&acc_full[acc]);           // accumulator complete
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok && issued) {
+        // error path: let the tensor core finish what was issued before tensor memory is freed
+        tc_commit(drain);
+        for (uint32_t i = 0; i < kSpinLimit && !mbar_test(drain, 0); ++i) __nanosleep(64);
+      }
+    }
+  } else {
+    // ===== epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 =====
+    const int q = warp & 3;
+    const float g = p.alpha * __ldg(p.a_unit) * __ldg(p.b_unit);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
+      const int64_t row = tm * kBM + q * 32 + lane;
+      const int64_t n0 = tn * BN;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
+        if (lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_MMA);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      const float c0 = p.rvec0 ? (p.cvec0 ? (row < p.M ? __ldg(p.cvec0 + row) : 0.f) : 1.0f) : 0.0f;
+      const float c1 = p.rvec1 ? (p.cvec1 ? (row < p.M ? __ldg(p.cvec1 + row) : 0.f) : 1.0f) : 0.0f;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        uint32_t r[32];
+        tc_load32(t_row + ch * 32, r);
+        tc_wait_ld();
+        const int64_t col0 = n0 + ch * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * g;
+          const bool full_chunk = col0 + 32 <= p.N;
+          if (p.rvec0) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(c0, __ldg(p.rvec0 + col0 + i), v[i]);
+          }
+          if (p.rvec1) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(c1, __ldg(p.rvec1 + col0 + i), v[i]);
+          }
+          TD* dst = static_cast<TD*>(p.d) + row * p.ldd + col0;
+          const TD* src = p.c ? static_cast<const TD*>(p.c) + row * p.ldc + col0 : nullptr;
+          if (full_chunk) {
+            if constexpr (sizeof(TD) == 2) {
+              if (src) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const uint4 w = __ldg(reinterpret_cast<const uint4*>(src) + i);
+                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) { v[8 * i + 2 * k] += bf16_lo(ww[k]); v[8 * i + 2 * k + 1] += bf16_hi(ww[k]); }
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(v[8 * i + 2 * k], v[8 * i + 2 * k + 1]);
+                reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<uint4*>(o);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                if (src) {
+                  const float4 w = __ldg(reinterpret_cast<const float4*>(src) + i);
+                  o.x += w.x; o.y += w.y; o.z += w.z; o.w += w.w;
+                }
+                reinterpret_cast<float4*>(dst)[i] = o;
+              }
+            }
+          } else {
+            for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
+              float o = v[i];
+              if constexpr (sizeof(TD) == 2) {
+                if (src) o += __bfloat162float(src[i]);
+                dst[i] = __float2bfloat16_rn(o);
+              } else {
+                if (src) o += src[i];
+                dst[i] = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows, inner] with a row pitch in bytes; box = [box_rows, box_inner],
+// 128-byte swizzle, out-of-range elements read as zero.
+static int32_t make_map(CUtensorMap* map, CUtensorMapDataType dt, int64_t esz, const void* base, int64_t inner,
+                        int64_t rows, int64_t pitch_bytes, int box_inner, int box_rows, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(METIS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  (void)esz;
+  const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(METIS_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
+  return METIS_OK;
+}
+
+template <int BN, typename TD>
+static int32_t launch_gemm(const metis_gemm_args* a, const CUtensorMap& ma, const CUtensorMap& mb,
+                           const CUtensorMap& mt, const CUtensorMap& mu, const GemmParams& p) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = nvfp4_gemm_kernel<BN, TD>;
+  // per device and cheap, so it is simply repeated on every launch
+  METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  const int64_t tiles = ceil_div(a->M, kBM) * ceil_div(a->N, BN);
+  int64_t grid = device_sm_count();
+  if (grid > tiles) grid = tiles;
+  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, reinterpret_cast<cudaStream_t>(a->stream)>>>(ma, mb, mt, mu, p);
+  METIS_CUDA_OK(cudaGetLastError());
+  return METIS_OK;
+}
+
+}  // namespace metis
+
+using namespace metis;
+
+extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
+  if (!a) return fail(METIS_ERR_BAD_ARGUMENT, "args is null");
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty GEMM %lld x %lld x %lld", (long long)a->M, (long long)a->N, (long long)a->K);
+  if (a->K % 32 != 0) return fail(METIS_ERR_BAD_SHAPE, "K = %lld must be a multiple of 32 (16-byte rows of packed codes)", (long long)a->K);
+  if (a->M >= ((int64_t)1 << 31) || a->N >= ((int64_t)1 << 31) || a->K >= ((int64_t)1 << 31)) return fail(METIS_ERR_TOO_LARGE, "dimension too large");
+  if (!a->a_codes || !a->a_scales || !a->a_unit || !a->b_codes || !a->b_scales || !a->b_unit || !a->d)
+    return fail(METIS_ERR_BAD_ARGUMENT, "null operand pointer");
+  if (!aligned16(a->a_codes) || !aligned16(a->b_codes) || !aligned16(a->a_scales) || !aligned16(a->b_scales) || !aligned16(a->d))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "codes, scales and d must be 16-byte aligned");
+  if (a->d_dtype != METIS_DTYPE_BF16 && a->d_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown d_dtype %d", a->d_dtype);
+  const int64_t dsz = a->d_dtype == METIS_DTYPE_BF16 ? 2 : 4;
+  if (a->ldd < a->N || (a->ldd * dsz) % 16 != 0) return fail(METIS_ERR_BAD_ALIGNMENT, "ldd must be >= N and give 16-byte aligned rows");
+  if (a->c && (a->ldc < a->N || (a->ldc * dsz) % 16 != 0 || !aligned16(a->c))) return fail(METIS_ERR_BAD_ALIGNMENT, "c must be 16-byte aligned with 16-byte aligned rows");
+  if (a->rank < 0 || a->rank > 256 || a->rank % 8 != 0) return fail(METIS_ERR_BAD_SHAPE, "rank %d must be a multiple of 8 in [0, 256]", a->rank);
+  if (a->rank > 0) {
+    if (!a->lr_t || !a->lr_u) return fail(METIS_ERR_BAD_ARGUMENT, "rank > 0 needs lr_t and lr_u");
+    if (!aligned16(a->lr_t) || !aligned16(a->lr_u) || a->ldt < a->rank || a->ldu < a->rank || a->ldt % 8 != 0 || a->ldu % 8 != 0)
+      return fail(METIS_ERR_BAD_ALIGNMENT, "lr_t and lr_u must be 16-byte aligned with leading dimensions that are multiples of 8");
+  }
+  if ((a->cvec0 && !a->rvec0) || (a->cvec1 && !a->rvec1)) return fail(METIS_ERR_BAD_ARGUMENT, "a cvec needs its rvec");
+  if (a->reserved & ~kDebugDropFirstSfa) return fail(METIS_ERR_BAD_ARGUMENT, "reserved must be 0");
+
+  const int bn = (a->N > 128) ? 256 : 128;
+  CUtensorMap ma, mb, mt, mu;
+  if (int32_t rc = make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->a_codes, a->K / 2, a->M, a->K / 2, kBKBytes, kBM, "A")) return rc;
+  if (int32_t rc = make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b_codes, a->K / 2, a->N, a->K / 2, kBKBytes, bn, "B")) return rc;
+  if (a->rank > 0) {
+    if (int32_t rc = make_map(&mt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->lr_t, a->rank, a->M, a->ldt * 2, 64, kBM, "T")) return rc;
+    if (int32_t rc = make_map(&mu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->lr_u, a->rank, a->N, a->ldu * 2, 64, bn, "U")) return rc;
+  } else {
+    mt = ma;
+    mu = mb;
+  }
+  GemmParams p;
+  p.M = a->M; p.N = a->N; p.K = a->K; p.rank = a->rank; p.debug = a->reserved;
+  p.a_scales = a->a_scales; p.b_scales = a->b_scales; p.a_unit = a->a_unit; p.b_unit = a->b_unit;
+  p.alpha = a->alpha;
+  p.cvec0 = a->cvec0; p.rvec0 = a->rvec0; p.cvec1 = a->cvec1; p.rvec1 = a->rvec1;
+  p.c = a->c; p.ldc = a->ldc; p.d = a->d; p.ldd = a->ldd; p.status = a->status;
+  if (bn == 256) {
+    if (a->d_dtype == METIS_DTYPE_BF16) return launch_gemm<256, __nv_bfloat16>(a, ma, mb, mt, mu, p);
+    return launch_gemm<256, float>(a, ma, mb, mt, mu, p);
+  }
+  if (a->d_dtype == METIS_DTYPE_BF16) return launch_gemm<128, __nv_bfloat16>(a, ma, mb, mt, mu, p);
+  return launch_gemm<128, float>(a, ma, mb, mt, mu, p);
+}

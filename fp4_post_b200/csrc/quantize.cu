@@ -1,0 +1,457 @@
+// NVFP4 block quantizer kernels (row-major and transposed, round-to-nearest and stochastic),
+// the scale finalisation pass, column means, and the C entry points that launch them.
+//
+// The work is split in two launches because of one global dependency: the E4M3 block
+// scales are expressed relative to the tensor-wide maximum block scale, while the 4-bit
+// codes only depend on their own block.  Pass 1 streams x once, writes the packed codes and
+// the fp32 block maxima, and folds the global maximum with one atomicMax per warp.  Pass 2
+// touches 1/16 of the elements: it turns the block maxima into E4M3 bytes in the layout the
+// consumer wants and publishes the per-tensor unit.
+#include "common.cuh"
+
+namespace metis {
+
+constexpr int kQuantThreads = 256;
+constexpr int kHeaderBytes = kWorkspaceHeaderBytes;
+
+__device__ __forceinline__ void fold_global_max(unsigned int* gmax, float local) {
+  // amax >= 0, so the IEEE bit pattern orders like the value.
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, o));
+  if ((threadIdx.x & 31) == 0 && local > 0.0f) atomicMax(gmax, __float_as_uint(local));
+}
+
+// ---- pass 1, row-major ------------------------------------------------------------------------
+// One thread owns 8 consecutive elements (one 128-bit load for bf16); two neighbouring
+// lanes form a 16-element block and exchange their maxima with one shuffle.  Each thread
+// stores 4 code bytes; the even lane stores the block maximum.
+template <typename T, bool kMean, bool kSR>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+                     const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
+                     uint32_t* __restrict__ codes, float* __restrict__ amax_out,
+                     unsigned int* __restrict__ gmax) {
+  const int64_t chunks_per_row = cols >> 3;
+  const int64_t total = rows * chunks_per_row;
+  const int64_t stride = (int64_t)gridDim.x * kQuantThreads;
+  float running = 0.0f;
+  const bool flat = (ld == cols) && !kMean;
+  const Philox rng(seed);
+  // total is even (cols % 16 == 0) and stride is even, so both lanes of a pair always run
+  // the same number of iterations; the loop bound is rounded up to keep whole warps inside.
+  const int64_t total_w = (total + 31) & ~(int64_t)31;
+  for (int64_t c = (int64_t)blockIdx.x * kQuantThreads + threadIdx.x; c < total_w; c += stride) {
+    const bool live = c < total;
+    float v[8];
+    int64_t col = 0;
+    if (live) {
+      int64_t src;
+      if (flat) {
+        src = c << 3;
+      } else {
+        const int64_t r = c / chunks_per_row;
+        col = (c - r * chunks_per_row) << 3;
+        src = r * ld + col;
+      }
+      Load8<T>::load(x + src, v);
+      if (kMean) {
+        float m[8];
+        Load8<float>::load(col_mean + col, m);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fsub_rn(v[i], m[i]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
+    float a = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a = fmaxf(a, fabsf(v[i]));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    const float s = block_scale_from_amax(a);
+    uint32_t packed;
+    if (kSR) {
+      packed = quantize8_sr(v, s, rng((uint64_t)c, offset));
+    } else {
+      packed = quantize8_rn(v, s);
+    }
+    if (live) {
+      codes[c] = packed;
+      if ((c & 1) == 0) amax_out[c >> 1] = a;
+    }
+    running = fmaxf(running, a);
+  }
+  fold_global_max(gmax, running);
+}
+
+// ---- pass 1, transposed ---------------------------------------------------------------------------
+// Output Q = quantize(x^T): blocks of 16 run along the rows of x.  A CTA owns a tile of
+// kTileRows x kTileCols of x.  A thread loads 16 rows x kCpt columns (kCpt columns = one
+// 128-bit load), so it holds kCpt complete blocks, one per column.  Codes and maxima are
+// staged in shared memory and written out as contiguous runs along the output rows.
+template <typename T> struct TransposeTile {
+  static constexpr int kCpt = 16 / sizeof(T);          // columns per thread (8 bf16, 4 fp32)
+  static constexpr int kColGroups = 8;                   // threads along the columns
+  static constexpr int kRowGroups = kQuantThreads / kColGroups;  // 32 groups of 16 rows
+  static constexpr int kTileCols = kCpt * kColGroups;    // 64 (bf16) or 32 (fp32)
+  static constexpr int kTileRows = 16 * kRowGroups;      // 512
+};
+
+template <typename T, bool kMean, bool kSR>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_cols_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+                     const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
+                     uint8_t* __restrict__ codes, float* __restrict__ amax_out,
+                     unsigned int* __restrict__ gmax) {
+  using TT = TransposeTile<T>;
+  constexpr int kCpt = TT::kCpt;
+  // +16 bytes of padding per staged row keeps the 8-byte stores of a warp off the same banks
+  __shared__ __align__(16) uint8_t s_codes[TT::kTileCols][TT::kTileRows / 2 + 16];
+  __shared__ float s_amax[TT::kTileCols][TT::kRowGroups + 1];
+
+  const int cg = threadIdx.x % TT::kColGroups;
+  const int rg = threadIdx.x / TT::kColGroups;
+  const int64_t col0 = (int64_t)blockIdx.x * TT::kTileCols + cg * kCpt;
+  const int64_t row_tiles = (rows + TT::kTileRows - 1) / TT::kTileRows;
+  const Philox rng(seed);
+  float running = 0.0f;
+
+  for (int64_t rt = blockIdx.y; rt < row_tiles; rt += gridDim.y) {
+    const int64_t row0 = rt * TT::kTileRows + rg * 16;
+    const bool live = (row0 < rows) && (col0 < cols);   // rows % 16 == 0, cols % kCpt == 0
+    float v[16][kCpt];
+    if (live) {
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const T* p = x + (row0 + r) * ld + col0;
+        if constexpr (sizeof(T) == 2) {
+          const uint4 w = __ldg(reinterpret_cast<const uint4*>(p));
+          v[r][0] = bf16_lo(w.x); v[r][1] = bf16_hi(w.x); v[r][2] = bf16_lo(w.y); v[r][3] = bf16_hi(w.y);
+          v[r][4] = bf16_lo(w.z); v[r][5] = bf16_hi(w.z); v[r][6] = bf16_lo(w.w); v[r][7] = bf16_hi(w.w);
+        } else {
+          const float4 w = __ldg(reinterpret_cast<const float4*>(p));
+          v[r][0] = w.x; v[r][1] = w.y; v[r][2] = w.z; v[r][3] = w.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kCpt; ++j) {
+      float blk[2][8];
+      float a = 0.0f;
+      float m = 0.0f;
+      if (kMean && live) m = __ldg(col_mean + col0 + j);
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        float e = live ? v[r][j] : 0.0f;
+        if (kMean) e = __fsub_rn(e, m);
+        blk[r >> 3][r & 7] = e;
+        a = fmaxf(a, fabsf(e));
+      }
+      const float s = block_scale_from_amax(a);
+      uint32_t p0, p1;
+      if (kSR) {
+        // one counter per 8 output elements: output row (col0+j), output column row0 (+8)
+        const uint64_t e0 = (uint64_t)(col0 + j) * (uint64_t)rows + (uint64_t)row0;
+        p0 = quantize8_sr(blk[0], s, rng(e0 >> 3, offset));
+        p1 = quantize8_sr(blk[1], s, rng((e0 >> 3) + 1, offset));
+      } else {
+        p0 = quantize8_rn(blk[0], s);
+        p1 = quantize8_rn(blk[1], s);
+      }
+      *reinterpret_cast<uint2*>(&s_codes[cg * kCpt + j][rg * 8]) = make_uint2(p0, p1);
+      s_amax[cg * kCpt + j][rg] = a;
+      running = fmaxf(running, a);
+    }
+    __syncthreads();
+    // write-out: tile column c (an output row) owns kTileRows/2 = 256 code bytes and
+    // kRowGroups = 32 maxima, both contiguous in the output.
+    const int64_t tile_row0 = rt * TT::kTileRows;
+    const int64_t valid_rows = min((int64_t)TT::kTileRows, rows - tile_row0);  // multiple of 16
+    const int code_bytes = (int)(valid_rows >> 1);                              // multiple of 8
+    for (int i = threadIdx.x; i < TT::kTileCols * (TT::kTileRows / 2 / 8); i += kQuantThreads) {
+      const int c = i / (TT::kTileRows / 2 / 8);
+      const int b = (i % (TT::kTileRows / 2 / 8)) * 8;
+      const int64_t oc = (int64_t)blockIdx.x * TT::kTileCols + c;
+      if (oc < cols && b < code_bytes) {
+        const uint2 w = *reinterpret_cast<const uint2*>(&s_codes[c][b]);
+        *reinterpret_cast<uint2*>(codes + oc * (rows >> 1) + (tile_row0 >> 1) + b) = w;
+      }
+    }
+    for (int i = threadIdx.x; i < TT::kTileCols * TT::kRowGroups; i += kQuantThreads) {
+      const int c = i / TT::kRowGroups;
+      const int g = i % TT::kRowGroups;
+      const int64_t oc = (int64_t)blockIdx.x * TT::kTileCols + c;
+      if (oc < cols && g * 16 < valid_rows)
+        amax_out[oc * (rows >> 4) + (tile_row0 >> 4) + g] = s_amax[c][g];
+    }
+    __syncthreads();
+  }
+  fold_global_max(gmax, running);
+}
+
+// ---- pass 2: block maxima -> E4M3 bytes + unit ------------------------------------------------------
+// One thread per group of 4 scale columns (one 128-bit read of maxima, one 32-bit write).
+// For METIS_SF_MMA the loop runs over the padded extent and pads with zero bytes.
+__global__ void __launch_bounds__(kQuantThreads)
+finalize_scales_kernel(const float* __restrict__ amax, const unsigned int* __restrict__ gmax,
+                       int64_t R, int64_t sf_cols, int32_t sf_layout, uint8_t* __restrict__ scales,
+                       float* __restrict__ unit_out) {
+  const float smax = block_scale_from_amax(__uint_as_float(*gmax));
+  const float unit = __fdiv_rn(smax, 448.0f);           // quant.py:21-22
+  if (blockIdx.x == 0 && threadIdx.x == 0) *unit_out = unit;
+  const int64_t elem_cols = sf_cols * 16;
+  const int64_t tiles = sf_tiles_per_row(elem_cols);
+  const int64_t groups_per_row = (sf_layout == METIS_SF_MMA) ? tiles : (sf_cols + 3) / 4;
+  const int64_t R_out = (sf_layout == METIS_SF_MMA) ? ((R + 127) / 128) * 128 : R;
+  const int64_t total = R_out * groups_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * kQuantThreads + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * kQuantThreads) {
+    const int64_t r = i / groups_per_row;
+    const int64_t k0 = (i - r * groups_per_row) * 4;
+    uint32_t packed = 0;
+    if (r < R) {
+      float a[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* src = amax + r * sf_cols + k0;
+      if (k0 + 4 <= sf_cols && ((sf_cols & 3) == 0)) {
+        const float4 w = *reinterpret_cast<const float4*>(src);
+        a[0] = w.x; a[1] = w.y; a[2] = w.z; a[3] = w.w;
+      } else {
+        for (int j = 0; j < 4; ++j) if (k0 + j < sf_cols) a[j] = src[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (k0 + j < sf_cols) {
+          const float ratio = __fdiv_rn(block_scale_from_amax(a[j]), unit);   // quant.py:23
+          packed |= (uint32_t)float_to_e4m3(ratio) << (8 * j);
+        }
+      }
+    }
+    if (sf_layout == METIS_SF_MMA) {
+      *reinterpret_cast<uint32_t*>(scales + sf_mma_offset(r, k0, tiles)) = packed;
+    } else {
+      uint8_t* dst = scales + r * sf_cols + k0;
+      if (k0 + 4 <= sf_cols && ((sf_cols & 3) == 0)) {
+        *reinterpret_cast<uint32_t*>(dst) = packed;
+      } else {
+        for (int j = 0; j < 4; ++j) if (k0 + j < sf_cols) dst[j] = (uint8_t)(packed >> (8 * j));
+      }
+    }
+  }
+}
+
+// ---- column means -----------------------------------------------------------------------------------------
+// Stage 1: CTA (bx, by) sums rows [by*rows_per_split, ...) of 8*32 columns into
+// partial[by][col]; stage 2 adds the partials in a fixed order and divides by rows.
+constexpr int kMeanThreads = 256;
+template <typename T>
+__global__ void __launch_bounds__(kMeanThreads)
+col_partial_sum_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+                       int64_t rows_per_split, float* __restrict__ partial) {
+  // 32 lanes x 8 columns = 256 columns per CTA; 8 warps stride over the rows.
+  __shared__ float s_part[kMeanThreads / 32][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t col = (int64_t)blockIdx.x * 256 + lane * 8;
+  const int64_t r_begin = (int64_t)blockIdx.y * rows_per_split;
+  const int64_t r_end = min(rows, r_begin + rows_per_split);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (col < cols) {
+    for (int64_t r = r_begin + warp; r < r_end; r += kMeanThreads / 32) {
+      float v[8];
+      Load8<T>::load(x + r * ld + col, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += v[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s_part[warp][lane * 8 + i] = acc[i];
+  __syncthreads();
+  const int c = threadIdx.x;
+  float sum = 0.0f;
+#pragma unroll
+  for (int w = 0; w < kMeanThreads / 32; ++w) sum += s_part[w][c];
+  const int64_t oc = (int64_t)blockIdx.x * 256 + c;
+  if (oc < cols) partial[(int64_t)blockIdx.y * cols + oc] = sum;
+}
+
+__global__ void col_mean_finish_kernel(const float* __restrict__ partial, int64_t splits, int64_t rows,
+                                       int64_t cols, float* __restrict__ mean) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float sum = 0.0f;
+  for (int64_t s = 0; s < splits; ++s) sum += partial[s * cols + c];
+  mean[c] = __fdiv_rn(sum, (float)rows);
+}
+
+static int64_t col_mean_splits(int64_t rows) {
+  int64_t s = ceil_div(rows, 128);
+  return s < 1 ? 1 : (s > 64 ? 64 : s);
+}
+
+// ---- launch helpers ------------------------------------------------------------------------------------------
+
+int device_sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+    return n;
+  return 148;
+}
+static int sm_count() { return device_sm_count(); }
+
+template <typename T>
+static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
+                        uint64_t seed, uint64_t offset, uint32_t* codes, const WorkspaceView& ws,
+                        cudaStream_t st) {
+  const int64_t total = rows * (cols >> 3);
+  int64_t blocks = ceil_div(total, (int64_t)kQuantThreads * 4);   // ~4 chunks per thread
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  const dim3 g((unsigned)blocks), b(kQuantThreads);
+#define METIS_LAUNCH_ROWS(MEAN, SR)                                                          \
+  quantize_rows_kernel<T, MEAN, SR><<<g, b, 0, st>>>(x, rows, cols, ld, mean, seed, offset,  \
+                                                     codes, ws.amax, ws.gmax)
+  if (mean) { if (sr) METIS_LAUNCH_ROWS(true, true); else METIS_LAUNCH_ROWS(true, false); }
+  else      { if (sr) METIS_LAUNCH_ROWS(false, true); else METIS_LAUNCH_ROWS(false, false); }
+#undef METIS_LAUNCH_ROWS
+}
+
+template <typename T>
+static void launch_cols(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
+                        uint64_t seed, uint64_t offset, uint8_t* codes, const WorkspaceView& ws,
+                        cudaStream_t st) {
+  using TT = TransposeTile<T>;
+  const int64_t col_tiles = ceil_div(cols, TT::kTileCols);
+  const int64_t row_tiles = ceil_div(rows, TT::kTileRows);
+  int64_t gy = ceil_div((int64_t)sm_count() * 4, col_tiles);
+  if (gy > row_tiles) gy = row_tiles;
+  if (gy < 1) gy = 1;
+  if (gy > 65535) gy = 65535;
+  const dim3 g((unsigned)col_tiles, (unsigned)gy), b(kQuantThreads);
+#define METIS_LAUNCH_COLS(MEAN, SR)                                                          \
+  quantize_cols_kernel<T, MEAN, SR><<<g, b, 0, st>>>(x, rows, cols, ld, mean, seed, offset,  \
+                                                     codes, ws.amax, ws.gmax)
+  if (mean) { if (sr) METIS_LAUNCH_COLS(true, true); else METIS_LAUNCH_COLS(true, false); }
+  else      { if (sr) METIS_LAUNCH_COLS(false, true); else METIS_LAUNCH_COLS(false, false); }
+#undef METIS_LAUNCH_COLS
+}
+
+int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t sf_layout,
+                        uint8_t* scales, float* unit, cudaStream_t st) {
+  const int64_t sf_cols = C / 16;
+  const int64_t groups = (sf_layout == METIS_SF_MMA)
+                             ? ceil_div(R, 128) * 128 * sf_tiles_per_row(C)
+                             : R * ceil_div(sf_cols, 4);
+  int64_t blocks = ceil_div(groups, kQuantThreads);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  finalize_scales_kernel<<<(unsigned)blocks, kQuantThreads, 0, st>>>(ws.amax, ws.gmax, R, sf_cols,
+                                                                    sf_layout, scales, unit);
+  METIS_CUDA_OK(cudaGetLastError());
+  return METIS_OK;
+}
+
+int32_t check_quant_outputs(int64_t R, int64_t C, int32_t sf_layout, const void* codes,
+                            const void* scales, const void* unit, const void* workspace,
+                            int64_t workspace_bytes) {
+  if (R <= 0 || C <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)R, (long long)C);
+  if (C % 16 != 0)
+    return fail(METIS_ERR_BAD_SHAPE, "NVFP4 block shape (1, 16) does not divide tensor shape (%lld, %lld)",
+                (long long)R, (long long)C);
+  if (sf_layout != METIS_SF_ROWMAJOR && sf_layout != METIS_SF_MMA)
+    return fail(METIS_ERR_BAD_ARGUMENT, "unknown sf_layout %d", sf_layout);
+  if (!codes || !scales || !unit || !workspace) return fail(METIS_ERR_BAD_ARGUMENT, "null output pointer");
+  if (!aligned16(codes) || !aligned16(scales) || !aligned16(workspace))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "codes, scales and workspace must be 16-byte aligned");
+  if (workspace_bytes < metis_nvfp4_quantize_workspace_bytes(R, C))
+    return fail(METIS_ERR_WORKSPACE, "workspace of %lld bytes, need %lld", (long long)workspace_bytes,
+                (long long)metis_nvfp4_quantize_workspace_bytes(R, C));
+  return METIS_OK;
+}
+
+}  // namespace metis
+
+using namespace metis;
+
+extern "C" int64_t metis_nvfp4_sf_bytes(int64_t R, int64_t C, int32_t sf_layout) {
+  if (R <= 0 || C <= 0) return 0;
+  if (sf_layout == METIS_SF_MMA) return ceil_div(R, 128) * sf_tiles_per_row(C) * 512;
+  return R * ceil_div(C, 16);
+}
+
+extern "C" int64_t metis_nvfp4_quantize_workspace_bytes(int64_t R, int64_t C) {
+  if (R <= 0 || C <= 0) return kHeaderBytes;
+  return kHeaderBytes + R * ceil_div(C, 16) * (int64_t)sizeof(float);
+}
+
+extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64_t cols,
+                                        int64_t ld, const float* col_mean, uint32_t flags,
+                                        uint64_t seed, uint64_t offset, int32_t sf_layout,
+                                        uint8_t* codes, uint8_t* scales, float* unit, void* workspace,
+                                        int64_t workspace_bytes, void* stream) {
+  const bool transpose = flags & METIS_Q_TRANSPOSE;
+  const bool sr = flags & METIS_Q_STOCHASTIC;
+  if (flags & ~(METIS_Q_TRANSPOSE | METIS_Q_STOCHASTIC)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x", flags);
+  if (!x) return fail(METIS_ERR_BAD_ARGUMENT, "x is null");
+  if (x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown x_dtype %d", x_dtype);
+  if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)rows, (long long)cols);
+  if (ld < cols) return fail(METIS_ERR_BAD_ARGUMENT, "ld %lld < cols %lld", (long long)ld, (long long)cols);
+  const int64_t R = transpose ? cols : rows, C = transpose ? rows : cols;
+  if (int32_t rc = check_quant_outputs(R, C, sf_layout, codes, scales, unit, workspace, workspace_bytes)) return rc;
+  const int64_t esz = x_dtype == METIS_DTYPE_BF16 ? 2 : 4;
+  // vector loads: 8 elements per thread row-major, 16 bytes per thread transposed
+  const int64_t need = transpose ? 16 / esz : 8;
+  if (cols % need != 0 || ld % need != 0 || !aligned16(x))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "x must be 16-byte aligned with cols and ld multiples of %lld", (long long)need);
+  if (col_mean && !aligned16(col_mean)) return fail(METIS_ERR_BAD_ALIGNMENT, "col_mean must be 16-byte aligned");
+  if (R * (C / 16) >= ((int64_t)1 << 40)) return fail(METIS_ERR_TOO_LARGE, "tensor too large");
+
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const WorkspaceView ws = view_workspace(workspace);
+  METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, sizeof(unsigned int), st));
+  if (!transpose) {
+    if (x_dtype == METIS_DTYPE_BF16)
+      launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset,
+                  reinterpret_cast<uint32_t*>(codes), ws, st);
+    else
+      launch_rows(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset,
+                  reinterpret_cast<uint32_t*>(codes), ws, st);
+  } else {
+    if (x_dtype == METIS_DTYPE_BF16)
+      launch_cols(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, codes, ws, st);
+    else
+      launch_cols(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, codes, ws, st);
+  }
+  METIS_CUDA_OK(cudaGetLastError());
+  return launch_finalize(ws, R, C, sf_layout, scales, unit, st);
+}
+
+extern "C" int64_t metis_col_mean_workspace_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return col_mean_splits(rows) * cols * (int64_t)sizeof(float);
+}
+
+extern "C" int32_t metis_col_mean(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                  float* mean, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!x || !mean || !workspace) return fail(METIS_ERR_BAD_ARGUMENT, "null pointer");
+  if (x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown x_dtype %d", x_dtype);
+  if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor");
+  if (cols % 8 != 0 || ld % 8 != 0 || ld < cols || !aligned16(x))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "x must be 16-byte aligned with cols and ld multiples of 8");
+  if (workspace_bytes < metis_col_mean_workspace_bytes(rows, cols))
+    return fail(METIS_ERR_WORKSPACE, "workspace too small");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t splits = col_mean_splits(rows);
+  const int64_t rows_per_split = ceil_div(rows, splits);
+  const dim3 g((unsigned)ceil_div(cols, 256), (unsigned)splits);
+  float* partial = static_cast<float*>(workspace);
+  if (x_dtype == METIS_DTYPE_BF16)
+    col_partial_sum_kernel<<<g, kMeanThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, rows_per_split, partial);
+  else
+    col_partial_sum_kernel<<<g, kMeanThreads, 0, st>>>(static_cast<const float*>(x), rows, cols, ld, rows_per_split, partial);
+  METIS_CUDA_OK(cudaGetLastError());
+  col_mean_finish_kernel<<<(unsigned)ceil_div(cols, 256), 256, 0, st>>>(partial, splits, rows, cols, mean);
+  METIS_CUDA_OK(cudaGetLastError());
+  return METIS_OK;
+}

@@ -1,0 +1,200 @@
+/*
+ * metis_nvfp4.h - C ABI of the B200 (sm_100a) Metis NVFP4 linear-layer library.
+ *
+ * The reference project (decisivemoments/fp4-post) has no FFI for this path: its
+ * Metis layer is eager PyTorch (src/Metis/Metis/quant.py, src/Metis/Metis/bitlinear.py)
+ * and its only native surface is a pybind11 module taking torch::Tensor
+ * (src/Metis/kernels/src/binding.cpp:12-64).  This header is the boundary a host
+ * binding (ctypes, cgo, JNI, a torch extension) loads instead.  Every entry point
+ * cites the reference call site whose arithmetic it replaces.
+ *
+ * Conventions
+ *  - extern "C", plain pointers and sizes, no C++ or torch types.
+ *  - All data pointers are DEVICE pointers unless stated otherwise.  The caller owns
+ *    every buffer, including scratch ("workspace"); the library never allocates device
+ *    memory and keeps no pointer after a call returns.
+ *  - Every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL is the
+ *    legacy default stream) and returns a host-side status: 0 = launched,
+ *    negative = argument rejected (nothing was launched).  metis_last_error_string()
+ *    describes the last non-zero status of the calling thread.
+ *  - Device-side bounded waits (mbarrier, TMEM allocation) never spin forever: on expiry
+ *    the kernel writes a positive code to the caller's optional `status` word and exits.
+ *
+ * NVFP4 tensor representation (what the quantizers write and the GEMM reads)
+ *  - codes : uint8 [R, C/2]; element 2i of a row is the low nibble of byte i, element
+ *            2i+1 the high nibble.  A nibble is sign<<3 | e2m1 magnitude code 0..7 with
+ *            magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6}.
+ *  - scales: one E4M3 (float8_e4m3fn) byte per 16 consecutive elements of a row, either
+ *            row-major [R, C/16] (METIS_SF_ROWMAJOR) or in the tcgen05 block-scale tile
+ *            order (METIS_SF_MMA): tiles of 128 rows x 4 scale columns, 512 bytes each,
+ *            byte (r%32)*16 + (r/32%4)*4 + (k%4) inside a tile, tiles ordered
+ *            [ceil(R/128)][4*ceil(C/256)].  Padding bytes are written as 0.
+ *  - unit  : one fp32 per tensor.  value = e2m1(code) * e4m3(scale) * unit.
+ */
+#ifndef METIS_NVFP4_H_
+#define METIS_NVFP4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define METIS_NVFP4_ABI_VERSION 1
+
+/* element types of dense operands */
+#define METIS_DTYPE_BF16 0
+#define METIS_DTYPE_F32  1
+
+/* scale-factor layouts */
+#define METIS_SF_ROWMAJOR 0
+#define METIS_SF_MMA      1
+
+/* quantizer flags */
+#define METIS_Q_TRANSPOSE   (1u << 0) /* quantize x^T: blocks run along the rows of x     */
+#define METIS_Q_STOCHASTIC  (1u << 1) /* stochastic rounding (Philox4x32-10, seed/offset) */
+
+/* status codes (host return values are <= 0, device status words are >= 0) */
+#define METIS_OK                 0
+#define METIS_ERR_BAD_ARGUMENT  -1
+#define METIS_ERR_BAD_SHAPE     -2  /* block of 16 does not divide the quantized dim (quant.py:400-403) */
+#define METIS_ERR_BAD_ALIGNMENT -3
+#define METIS_ERR_WORKSPACE     -4
+#define METIS_ERR_CUDA          -5
+#define METIS_ERR_UNSUPPORTED   -6
+#define METIS_ERR_TOO_LARGE     -7
+#define METIS_DEV_TIMEOUT_TMA    1  /* a bounded mbarrier wait on TMA data expired     */
+#define METIS_DEV_TIMEOUT_MMA    2  /* a bounded wait on tensor-core completion expired */
+#define METIS_DEV_TIMEOUT_EPI    3  /* a bounded wait on the accumulator hand-off expired */
+
+/* ---- queries ------------------------------------------------------------------------ */
+
+/* ABI version, compiled arch (100 for sm_100a), SM count of the current device (0 if no
+ * device).  Any pointer may be NULL.  Replaces nothing in the reference. */
+int32_t metis_query(int32_t* abi_version, int32_t* compiled_sm, int32_t* device_sm_count);
+
+/* Thread-local text for the last non-zero status returned to this thread. */
+const char* metis_last_error_string(void);
+
+/* Bytes of the scale array for a quantized [R, C] tensor in the given layout. */
+int64_t metis_nvfp4_sf_bytes(int64_t R, int64_t C, int32_t sf_layout);
+
+/* Bytes of scratch metis_nvfp4_quantize / metis_rmsnorm_nvfp4_quantize need for a
+ * quantized [R, C] tensor (per-block fp32 amax + a 256-byte header). */
+int64_t metis_nvfp4_quantize_workspace_bytes(int64_t R, int64_t C);
+
+/* ---- quantizers ----------------------------------------------------------------------- */
+
+/*
+ * NVFP4 block quantizer.  Replaces the fake-quant graph
+ * _nvfp4_nosr_quantize_dequantize (src/Metis/Metis/quant.py:6-36) reached from
+ * Cast2NVFp4e2m1BlockNOSR.quantize_dequantize (quant.py:393-433), and, with
+ * METIS_Q_STOCHASTIC, Cast2NVFp4e2m1Block (quant.py:273-388) whose rounding is
+ * Cast2Fp4e2m1Random.quant (quant.py:139-147).  Call sites replaced:
+ * bitlinear.py:392 (activations), :331 (mean-centred residual), :400-402 (output
+ * gradient), :580 (weights).
+ *
+ *   x         [rows, cols] row-major, leading dimension ld (elements), bf16 or fp32
+ *   col_mean  optional fp32 [cols]; x[r][c] - col_mean[c] is quantized instead of x
+ *             (the residual of _mean_quant_single, bitlinear.py:311-336)
+ *   output    tensor Q of shape [R, C] = [rows, cols], or [cols, rows] with
+ *             METIS_Q_TRANSPOSE; C must be a multiple of 16.
+ *   codes     uint8 [R, C/2]       scales  E4M3, metis_nvfp4_sf_bytes(R, C, sf_layout)
+ *   unit      fp32 [1]             workspace  metis_nvfp4_quantize_workspace_bytes(R, C)
+ *
+ * Arithmetic (fp32, round-to-nearest mode bit-exact with the reference run on
+ * x.float()): s = amax/6 + 1e-9 per block; unit = max(s)/448; scale = e4m3(s/unit);
+ * code = round-half-even of |x|/(s/2) folded onto the e2m1 grid; sign bit = (x < 0).
+ * Stochastic mode adds U[-0.5, 0.5) to the folded index before rounding.
+ */
+int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                             const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,
+                             int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,
+                             void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
+ * Fused RMSNorm -> NVFP4 quantizer: reads each activation row from HBM once.
+ * Replaces RMSNorm.forward (src/Metis/models/llama.py:23-31) followed by the activation
+ * quantizer (bitlinear.py:392 -> quant.py:6-36).
+ *   y = round_to_x_dtype(x * rsqrt(mean(x^2) + eps)) * gamma     (llama.py:23-31)
+ * gamma is bf16 or fp32 [cols]; when x and gamma are both bf16 the product is rounded to
+ * bf16 as torch does.  norm_out (optional, dtype of that product, [rows, cols]) receives y.
+ * Round-to-nearest only; other outputs as metis_nvfp4_quantize without METIS_Q_TRANSPOSE.
+ */
+int32_t metis_rmsnorm_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64_t cols,
+                                     int64_t ld, const void* gamma, int32_t gamma_dtype, float eps,
+                                     int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,
+                                     void* norm_out, void* workspace, int64_t workspace_bytes,
+                                     void* stream);
+
+/*
+ * codes/scales/unit -> dense [R, C] (ld elements per row), bf16 or fp32:
+ * out = e2m1(code) * (e4m3(scale) * unit), the last two steps of quant.py:19-35.
+ * If add_row_vec (fp32 [C]) is given it is added to every row (me + QDQ(x - me),
+ * bitlinear.py:332).
+ */
+int32_t metis_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales, const float* unit,
+                               int32_t sf_layout, int64_t R, int64_t C, const float* add_row_vec,
+                               void* out, int32_t out_dtype, int64_t ld, void* stream);
+
+/*
+ * Column means of x [rows, cols]: mean[c] = (sum_r x[r][c]) / rows in fp32
+ * (input_flat.mean(dim=0), bitlinear.py:326).  Deterministic summation order.
+ * workspace: at least metis_col_mean_workspace_bytes(rows, cols) bytes.
+ */
+int64_t metis_col_mean_workspace_bytes(int64_t rows, int64_t cols);
+int32_t metis_col_mean(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                       float* mean, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
+ * out[r] = sum_c v[c] * value(Q[r][c])  for a quantized [R, C] tensor (v == NULL: all ones).
+ * Gives the rank-1 terms of the mean-centred products: me @ Wq^T (bitlinear.py:332 with
+ * :435) and the column sums of the four-term dW expansion.  fp32 output [R].
+ */
+int32_t metis_nvfp4_gemv(const uint8_t* codes, const uint8_t* scales, const float* unit,
+                         int32_t sf_layout, int64_t R, int64_t C, const float* v, float* out,
+                         void* stream);
+
+/* ---- GEMM --------------------------------------------------------------------------------- */
+
+/*
+ * D[M,N] = g * ( sum_k A[m,k] B[n,k]  +  sum_j T[m,j] U[n,j] )
+ *          + cvec0[m]*rvec0[n] + cvec1[m]*rvec1[n]  ( + C[m,n] )
+ * with g = alpha * (*a_unit) * (*b_unit).
+ *
+ * A [M,K] and B [N,K] are NVFP4 tensors with METIS_SF_MMA scales; the K loop runs on
+ * tcgen05 block-scaled MMA (kind::mxf4nvf4, 16-element blocks, UE4M3 scales) with
+ * TMA-fed shared-memory stages and the accumulator in tensor memory.  T [M,rank] and
+ * U [N,rank] (bf16, rank % 8 == 0, rank <= 256, given in accumulator units, i.e. already
+ * divided by (*a_unit)*(*b_unit)) are a rank-r side product issued as kind::f16 MMAs into
+ * the same accumulator.  cvec NULL means a vector of ones; a NULL rvec disables its term.
+ *
+ * Replaces torch.matmul at bitlinear.py:435 (forward), :502-505 (dW), :508 (dX), :748
+ * (merged rollout weight) and the vlinear -> s -> ulinear -> add chain (bitlinear.py:752-760),
+ * whose native ancestor is lora_fuse (src/Metis/kernels/src/lora/lora_fuse.cu:106-291).
+ */
+typedef struct metis_gemm_args {
+  int64_t M, N, K;
+  const uint8_t* a_codes;  const uint8_t* a_scales;  const float* a_unit;
+  const uint8_t* b_codes;  const uint8_t* b_scales;  const float* b_unit;
+  float alpha;
+  int32_t rank;             /* 0: no side product */
+  const void* lr_t;  int64_t ldt;   /* bf16 [M, rank] */
+  const void* lr_u;  int64_t ldu;   /* bf16 [N, rank] */
+  const float* cvec0;  const float* rvec0;
+  const float* cvec1;  const float* rvec1;
+  const void* c;  int64_t ldc;      /* optional addend, dtype d_dtype */
+  void* d;        int64_t ldd;
+  int32_t d_dtype;          /* METIS_DTYPE_BF16 or METIS_DTYPE_F32 */
+  int32_t reserved;
+  int32_t* status;          /* optional device int32: 0, or a METIS_DEV_* code */
+  void* stream;
+} metis_gemm_args;
+
+int32_t metis_nvfp4_gemm(const metis_gemm_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* METIS_NVFP4_H_ */
