@@ -1,0 +1,827 @@
+"""The Metis linear layer, API-compatible with the reference's src/Metis/Metis/bitlinear.py:
+`LinearLowbitFunction` (autograd), `LinearLowbit`, `BitLinear`, with the same constructor
+arguments, attributes, parameter names (warmup_linear / vlinear / ulinear / s), class-level
+configuration and caches (weight cache keyed on Parameter._version, shared activation per
+projection group by weakref identity, merged rollout weight, rolling decode mean).
+
+Two execution modes, chosen per call:
+
+  packed   operands are real NVFP4 (packed codes + E4M3 scales + unit, `PackedOperand`) produced
+           by the native quantizers, and every product runs on the tcgen05 block-scaled GEMM with
+           the bf16 rank-r term  U (s . x V^T)  fused into the same accumulator.  Taken when the
+           configured quantizer classes are the native NVFP4 ones, tensors live on a CUDA device
+           and `LinearLowbitFunction.gemm_mode == "packed"` (the default).
+  dense    operands are dequantized tensors and the products are torch.matmul, exactly the
+           reference's wiring (bitlinear.py:407-513).  Taken for stub / non-NVFP4 quantizer classes
+           on any device (this is what the reference's own tests exercise), or when
+           `gemm_mode == "dense"` (used to check the autograd wiring against the reference).
+
+In packed mode the backward products contract over N (dX) and over tokens (dW), so W, D and x are
+quantized a second time along those dimensions by the transposed quantizer; the reference
+instead reuses values quantized along the last dimension (bitlinear.py:502-508).
+"""
+from __future__ import annotations
+
+import math
+import weakref
+
+import torch
+import torch.nn as nn
+import torch.nn.init as init
+
+from fp4_post_b200 import ops
+from .quant import *  # noqa: F401,F403  (the reference re-exports its quantizers the same way)
+from .quant import is_native, quant_func
+
+
+class PackedOperand:
+    """One GEMM operand in NVFP4 with everything the backward products need.
+
+    `q`      NVFP4Tensor of the matrix viewed as [rows, cols], blocks along cols; q.row_vec is the
+             column mean that was subtracted (mean mode) or None.
+    `source` the tensor it was quantized from (kept so that the transposed quantization needed by
+             dX / dW can be produced on demand) and `quantizer` the class that did it.
+    """
+
+    def __init__(self, q, source, quantizer, shape):
+        self.q = q
+        self.source = source
+        self.quantizer = quantizer
+        self.shape = tuple(shape)      # shape of the tensor this stands for, e.g. [B, T, K]
+        self._qt = None
+        self._dense = {}
+
+    @property
+    def dtype(self):
+        return self.source.dtype
+
+    @property
+    def mean(self):
+        return self.q.row_vec
+
+    def transposed(self):
+        """Quantization of the transpose (blocks along the rows of the source), cached."""
+        if self._qt is None:
+            self._qt = self.quantizer.quantize_packed(self.source, transpose=True, mean=self.q.row_vec)
+        return self._qt
+
+    def dense(self, dtype):
+        """The dequantized tensor the reference would have produced (mean added back)."""
+        if dtype not in self._dense:
+            native = dtype if dtype in (torch.bfloat16, torch.float32) else torch.float32
+            self._dense[dtype] = self.q.dequantize(native).to(dtype).reshape(self.shape)
+        return self._dense[dtype]
+
+
+def _packed_matmul(a, b, rank1=(), lowrank=None, c=None, out_dtype=torch.bfloat16):
+    return ops.nvfp4_gemm(a, b, rank1=rank1, lowrank=lowrank, c=c, out_dtype=out_dtype)
+
+
+def _backward_can_pack(shared) -> bool:
+    """Whether the configured backward can run on packed operands for this activation."""
+    return LinearLowbitFunction._packed_backward_ok(shared.source)
+
+
+def _gemm_ok(M, N, K):
+    """Shapes the packed GEMM takes (rows of packed codes must be multiples of 16 bytes)."""
+    return K % 32 == 0 and M > 0 and N > 0
+
+
+# -----------------------------------------------------------------------------
+# autograd.Function: quantized linear, forward and backward
+# -----------------------------------------------------------------------------
+class LinearLowbitFunction(torch.autograd.Function):
+    """y = Q(x) @ Q(W)^T + b with a quantized backward (reference: bitlinear.py:18-513).
+    Class attributes are process-global configuration written by BitLinear.__init__."""
+
+    q_forward_input = Cast2Fp4e2m1
+    q_forward_weight = Cast2Fp4e2m1
+    q_backward_input = Cast2Fp4e2m1
+    q_backward_weight = Cast2Fp4e2m1
+    q_backward_outputgrad = Cast2Fp4e2m1
+
+    enable_nv_recipe = False
+    _hadamard_cache = {}
+    hadamard_workspace_mb = 128
+    hadamard_tile_size = 16
+    hadamard_backend = "auto"
+    _dao_hadamard_transform = None
+    _dao_hadamard_checked = False
+    _hadamard_sign_cache = {}
+
+    activation_lowrank_niter = 0
+    backward_lowrank_niter = 0
+    enable_activation_svd = False
+    activation_lowrank_svd = -1
+    enable_backward_svd = False
+    backward_lowrank_svd = -1
+    activation_broadcast_dim = -1
+    backward_broadcast_dim = -1
+
+    tp_simulate = False
+    tp_parts = 4
+
+    compute_dtype = torch.float32
+    metis_mode = "mean"
+    mean_cache = None
+    mean_cache_key = "default"
+
+    # "packed": real FP4 operands on the tensor-core GEMM; "dense": dequantize + torch.matmul
+    gemm_mode = "packed"
+
+    # ---- random Hadamard transform of the NV baseline (kept in torch; bitlinear.py:75-211) ----------
+    @staticmethod
+    def _get_hadamard(size: int, device, dtype) -> torch.Tensor:
+        key = (int(size), device, dtype)
+        hit = LinearLowbitFunction._hadamard_cache.get(key)
+        if hit is not None:
+            return hit
+        if size <= 0 or size & (size - 1):
+            raise ValueError(f"Hadamard block size must be a power of two, got {size}")
+        h = torch.ones((1, 1), device=device, dtype=dtype)
+        while h.shape[0] < size:   # Sylvester doubling
+            h = torch.cat((torch.cat((h, h), dim=1), torch.cat((h, -h), dim=1)), dim=0)
+        LinearLowbitFunction._hadamard_cache[key] = h
+        return h
+
+    @staticmethod
+    def _get_hadamard_sign(size: int, device, dtype) -> torch.Tensor:
+        key = (int(size), device, dtype)
+        hit = LinearLowbitFunction._hadamard_sign_cache.get(key)
+        if hit is not None:
+            return hit
+        gen = torch.Generator(device="cpu")
+        gen.manual_seed(1729 + size)     # the reference's fixed seed, so both sides rotate alike
+        bits = torch.randint(0, 2, (size,), generator=gen, dtype=torch.int8)
+        signs = (bits * 2 - 1).to(device=device, dtype=dtype)
+        LinearLowbitFunction._hadamard_sign_cache[key] = signs
+        return signs
+
+    @staticmethod
+    def _get_dao_hadamard_transform():
+        F = LinearLowbitFunction
+        if not F._dao_hadamard_checked:
+            try:
+                from fast_hadamard_transform import hadamard_transform
+                F._dao_hadamard_transform = hadamard_transform
+            except ImportError:
+                F._dao_hadamard_transform = None
+            F._dao_hadamard_checked = True
+        return F._dao_hadamard_transform
+
+    @staticmethod
+    def _apply_hadamard_blocks(value: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+        """x -> (x . signs) H per tile of the last dimension; inverse: (y H / d) . signs."""
+        F = LinearLowbitFunction
+        dim = value.shape[-1]
+        if dim <= 1 or value.numel() == 0:
+            return value
+        tile = int(F.hadamard_tile_size)
+        if tile <= 0 or tile & (tile - 1):
+            raise ValueError(f"Hadamard tile size must be a positive power of two, got {tile}")
+        if dim % tile:
+            raise ValueError(f"RHT tile size {tile} must divide hidden dimension {dim}; "
+                             "set --metis_hadamard_tile_size to a compatible power of two")
+        if F.hadamard_backend not in {"auto", "dao_cuda", "torch_gemm"}:
+            raise ValueError(f"Unsupported Hadamard backend: {F.hadamard_backend}")
+        dao = F._get_dao_hadamard_transform() if (F.hadamard_backend in {"auto", "dao_cuda"} and value.is_cuda) else None
+        if F.hadamard_backend == "dao_cuda" and dao is None:
+            raise RuntimeError("Hadamard backend dao_cuda was requested but fast_hadamard_transform is unavailable. "
+                               "Install it with: pip install -v git+https://github.com/Dao-AILab/fast-hadamard-transform.git")
+        if dao is not None:
+            flat = value.reshape(-1, tile)
+            signs = F._get_hadamard_sign(tile, value.device, value.dtype)
+            out = dao(flat, scale=1.0 / tile) * signs if inverse else dao(flat * signs, scale=1.0)
+            return out.reshape_as(value)
+
+        work_dtype = torch.float32 if value.dtype in (torch.float16, torch.bfloat16) else value.dtype
+        h = F._get_hadamard(tile, value.device, work_dtype)
+        signs = F._get_hadamard_sign(tile, value.device, work_dtype)
+        tiles = value.reshape(-1, tile)
+        out = torch.empty_like(tiles)
+        # two work-dtype copies of a chunk are alive at once; stay inside the budget
+        budget = max(1, int(F.hadamard_workspace_mb)) * 1024 * 1024
+        step = max(1, budget // (2 * tile * torch.empty((), dtype=work_dtype).element_size()))
+        for start in range(0, tiles.shape[0], step):
+            chunk = tiles[start:start + step].to(work_dtype)
+            if inverse:
+                res = torch.mm(chunk, h).mul_(1.0 / tile).mul_(signs)
+            else:
+                res = torch.mm(chunk * signs, h)
+            out[start:start + step].copy_(res)
+        return out.reshape_as(value)
+
+    # ---- low-rank / mean-centred fake quantization (dense mode; bitlinear.py:213-368) ---------------
+    @staticmethod
+    def _rolling_mean(flat: torch.Tensor, seq_len: int, mean_cache, cache_key):
+        """Column mean of `flat`; at decode (one token per sequence) the count-weighted running
+        mean over everything seen since the last prefill (bitlinear.py:314-328)."""
+        rows = flat.shape[0]
+        fresh = flat.mean(dim=0, keepdim=True)
+        if seq_len == 1 and mean_cache is not None and cache_key in mean_cache:
+            old, count = mean_cache[cache_key]
+            total = count + rows
+            me = (old * count + fresh * rows) / total
+            mean_cache[cache_key] = (me.detach(), total)
+            return me
+        if mean_cache is not None:
+            mean_cache[cache_key] = (fresh.detach(), rows)
+        return fresh
+
+    @staticmethod
+    def svd_quant(input_: torch.Tensor, quant_func, rank: int = 60, niter: int = 0, broadcast_dim: int = -1,
+                  tp_simulate: bool = False, tp_parts: int = 4, metis_mode="mean",
+                  mean_cache: dict = None, cache_key: str = "default"):
+        """Split the input into a high-precision part and a quantized remainder, then recombine.
+        "mean": column mean + QDQ(x - mean).  "svd": rank-`rank` randomized SVD with quantized
+        factors + QDQ(residual)."""
+
+        def svd_piece(piece):
+            picked = piece.select(broadcast_dim, 0) if broadcast_dim >= 0 else piece
+            shape = picked.shape
+            three_d = len(shape) == 3
+            picked2 = picked.reshape(-1, shape[-1]) if three_d else picked
+            full2 = piece.reshape(-1, shape[-1]) if three_d else piece
+            dt = picked2.dtype
+            as32 = picked2.to(torch.float32)
+            if torch.isnan(as32).any() or torch.isinf(as32).any():
+                print("⚠️ Warning: NaN or Inf detected in input before SVD")
+            with torch.amp.autocast(as32.device.type, enabled=False):
+                u, s, v = torch.svd_lowrank(as32, q=rank, niter=niter)
+            u, s, vt = u.to(dt), s.to(dt), v.to(dt).T
+
+            def three_call(t):
+                sc = quant_func.get_scalar(t)
+                return quant_func.rquant(quant_func.quant(t, sc), sc)
+
+            kernel = three_call(u) @ torch.diag(s) @ three_call(vt)
+            if broadcast_dim >= 0:
+                kernel = kernel.unsqueeze(broadcast_dim)
+            out = kernel + quant_func.quantize_dequantize(full2 - kernel)
+            return out.view(shape[0], shape[1], -1) if three_d else out
+
+        def mean_piece(piece):
+            shape = piece.shape
+            flat = piece.reshape(-1, shape[-1])
+            seq_len = shape[1] if len(shape) == 3 else shape[0]
+            me = LinearLowbitFunction._rolling_mean(flat, seq_len, mean_cache, cache_key)
+            out = me + quant_func.quantize_dequantize(flat - me)
+            return out.view(shape[0], shape[1], -1) if len(shape) == 3 else out
+
+        if tp_simulate:
+            width = input_.shape[-1]
+            parts = max(1, int(tp_parts))
+            cuts = [(width * p) // parts for p in range(parts + 1)]
+            return torch.cat([svd_piece(input_[..., a:b]) for a, b in zip(cuts, cuts[1:]) if b > a], dim=-1)
+        if metis_mode == "svd":
+            return svd_piece(input_)
+        if metis_mode == "mean":
+            return mean_piece(input_)
+        raise ValueError(f"Unsupported metis_mode: {metis_mode}")
+
+    # ---- packed-mode quantization of activations / gradients ---------------------------------------------
+    @staticmethod
+    def _use_packed(tensor: torch.Tensor, quantizer) -> bool:
+        F = LinearLowbitFunction
+        return (F.gemm_mode == "packed" and tensor.is_cuda and is_native(quantizer)
+                and not F.tp_simulate and tensor.shape[-1] % 16 == 0)
+
+    @staticmethod
+    def _pack_centred(tensor, quantizer, centred: bool, mean_cache=None, cache_key="default"):
+        """NVFP4 of `tensor` ([..., C] viewed as rows), optionally after subtracting the column
+        mean (rolling at decode).  The native counterpart of svd_quant(metis_mode="mean")."""
+        flat = tensor.reshape(-1, tensor.shape[-1])
+        mean = None
+        if centred:
+            seq_len = tensor.shape[1] if tensor.dim() == 3 else tensor.shape[0]
+            fresh = ops.col_mean(flat)
+            rows = flat.shape[0]
+            if seq_len == 1 and mean_cache is not None and cache_key in mean_cache:
+                old, count = mean_cache[cache_key]
+                total = count + rows
+                mean = (old.reshape(-1).float() * count + fresh * rows) / total
+                mean_cache[cache_key] = (mean.detach().reshape(1, -1), total)
+            else:
+                mean = fresh
+                if mean_cache is not None:
+                    mean_cache[cache_key] = (fresh.detach().reshape(1, -1), rows)
+        q = quantizer.quantize_packed(flat, mean=mean)
+        return PackedOperand(q, flat, quantizer, tensor.shape)
+
+    @staticmethod
+    def _backward_centred() -> bool:
+        """True when the output gradient is mean-centred before quantization (bitlinear.py:462-474)."""
+        F = LinearLowbitFunction
+        return bool(F.enable_backward_svd and F.backward_lowrank_svd > 0 and F.metis_mode == "mean")
+
+    @staticmethod
+    def _packed_backward_ok(grad_output: torch.Tensor) -> bool:
+        """The packed backward covers direct quantization of the gradient and the mean mode."""
+        F = LinearLowbitFunction
+        mode_ok = (not F.enable_backward_svd) or F._backward_centred()
+        return bool(mode_ok and not F.enable_nv_recipe and F._use_packed(grad_output, F.q_backward_outputgrad))
+
+    @staticmethod
+    def quantize_input(input_: torch.Tensor, mean_cache: dict = None, cache_key: str = "default"):
+        """Quantized activation: a PackedOperand in packed mode, else the dequantized tensor
+        (bitlinear.py:371-393)."""
+        F = LinearLowbitFunction
+        input_ = input_.to(F.compute_dtype)
+        centred = F.enable_activation_svd
+        if F._use_packed(input_, F.q_forward_input) and (not centred or F.metis_mode == "mean"):
+            return F._pack_centred(input_, F.q_forward_input, centred, mean_cache, cache_key)
+        if centred:
+            return F.svd_quant(input_, quant_func=F.q_forward_input, rank=F.activation_lowrank_svd,
+                               niter=F.activation_lowrank_niter, broadcast_dim=F.activation_broadcast_dim,
+                               tp_simulate=F.tp_simulate, tp_parts=F.tp_parts, metis_mode=F.metis_mode,
+                               mean_cache=mean_cache, cache_key=cache_key)
+        return F.q_forward_input.quantize_dequantize(input_)
+
+    @staticmethod
+    def _quantize_wgrad_operand(value: torch.Tensor, quantizer) -> torch.Tensor:
+        """Dense QDQ of one weight-gradient operand; rotated only for the NV baseline
+        (bitlinear.py:395-405).  The three-call sequence is kept because stubs override it."""
+        F = LinearLowbitFunction
+        if F.enable_nv_recipe:
+            value = F._apply_hadamard_blocks(value, inverse=False)
+        scalar = quantizer.get_scalar(value)
+        value = quantizer.rquant(quantizer.quant(value, scalar), scalar)
+        if F.enable_nv_recipe:
+            value = F._apply_hadamard_blocks(value, inverse=True)
+        return value
+
+    # ---- forward / backward ----------------------------------------------------------------------------------------
+    @staticmethod
+    def forward(ctx, input_: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, quantized_weight,
+                quantized_input):
+        F = LinearLowbitFunction
+        if quantized_input is None:
+            quantized_input = F.quantize_input(input_, mean_cache=F.mean_cache, cache_key=F.mean_cache_key)
+        xa, wq = quantized_input, quantized_weight
+        packed = isinstance(xa, PackedOperand) and isinstance(wq, PackedOperand) \
+            and _gemm_ok(xa.q.shape[0], wq.q.shape[0], xa.q.shape[1])
+        ctx.packed = packed
+        ctx.has_bias = bias is not None
+        if packed:
+            ctx.xa, ctx.wq = xa, wq
+            ctx.save_for_backward(bias)
+            rank1 = []
+            if xa.mean is not None:
+                rank1.append((None, ops.nvfp4_gemv(wq.q, xa.mean)))     # 1 (x) (mean @ Wq^T)
+            if bias is not None:
+                rank1.append((None, bias.float()))
+            out_dtype = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
+            y = _packed_matmul(xa.q, wq.q, rank1=rank1, out_dtype=out_dtype)
+            return y.reshape(*xa.shape[:-1], wq.q.shape[0]).to(xa.dtype)
+        # dense mode: the reference's wiring
+        if isinstance(xa, PackedOperand):
+            xa = xa.dense(F.compute_dtype)
+        if isinstance(wq, PackedOperand):
+            wq = wq.dense(weight.dtype)
+        ctx.save_for_backward(xa, wq, bias)
+        output = torch.matmul(xa, wq.T)
+        if bias is not None:
+            output += bias
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        F = LinearLowbitFunction
+        grad_output = grad_output.to(F.compute_dtype)
+        grad_bias = grad_output.sum(dim=(0, 1)) if ctx.has_bias else None
+        d0, d1, d2 = grad_output.shape[0], grad_output.shape[1], grad_output.shape[2]   # 3-D, as the reference
+        if ctx.packed:
+            xa, wq = ctx.xa, ctx.wq
+            M, N, K = d0 * d1, d2, xa.q.shape[1]
+            if F._packed_backward_ok(grad_output) and _gemm_ok(M, K, N) and _gemm_ok(N, K, M):
+                da = F._pack_centred(grad_output, F.q_backward_outputgrad, F._backward_centred())
+                grad_input, grad_weight = _packed_backward(da, xa, wq, M, N, K)
+                grad_input = grad_input.reshape(d0, d1, K)
+                grad_bias = grad_bias.to(torch.float32) if grad_bias is not None else None
+                return grad_input, grad_weight, grad_bias, None, None
+            # shapes or quantizers the packed backward does not take: continue densely
+            input_, weight = xa.dense(F.compute_dtype), wq.dense(F.compute_dtype)
+        else:
+            input_, weight, _ = ctx.saved_tensors
+
+        if F.enable_backward_svd:
+            if F.backward_lowrank_svd > 0:
+                grad_output = F.svd_quant(grad_output, quant_func=F.q_backward_outputgrad,
+                                          rank=F.backward_lowrank_svd, niter=F.backward_lowrank_niter,
+                                          broadcast_dim=F.backward_broadcast_dim, tp_simulate=F.tp_simulate,
+                                          tp_parts=F.tp_parts, metis_mode=F.metis_mode)
+                grad_t = grad_output.reshape(-1, d2).T
+            else:
+                ug, sg, vg = torch.linalg.svd(grad_output, full_matrices=False)
+                us, vs = ug.abs().mean(), vg.abs().mean()
+                q = F.q_backward_outputgrad
+                grad_t = q(ug / us) @ torch.diag(sg) @ q(vg / vs)
+                grad_t *= us * vs
+        else:
+            grad_t = F._quantize_wgrad_operand(grad_output, F.q_backward_outputgrad).reshape(-1, d2).T
+
+        wgrad_input = input_
+        if F.enable_nv_recipe:
+            wgrad_input = F._quantize_wgrad_operand(input_, F.q_backward_input)
+        grad_weight = torch.matmul(grad_t, wgrad_input.reshape(-1, wgrad_input.shape[-1]))
+        grad_input = torch.matmul(grad_t.T.reshape(d0, d1, d2), weight)
+        grad_weight = grad_weight.to(torch.float32)
+        grad_bias = grad_bias.to(torch.float32) if grad_bias is not None else None
+        return grad_input, grad_weight, grad_bias, None, None
+
+
+def _packed_backward(da: PackedOperand, xa: PackedOperand, wq: PackedOperand, M: int, N: int, K: int):
+    """dX = D^ @ W^ and dW = D^T @ x^ on the FP4 GEMM (bitlinear.py:502-508), where
+    D^ = 1 mu_D^T + Q(D - mu_D) and x^ = 1 mu_x^T + Q(x - mu_x).
+
+    dX contracts over N: A = Q(D) [M, N], B = W quantized along N ([K, N], transposed quantizer),
+    plus the row vector mu_D @ W^.  dW contracts over tokens: A = Q(D)^T [N, M], B = Q(x)^T [K, M]
+    (both from the transposed quantizer) plus the two rank-1 terms of the expansion
+      dW = Qd^T Qx + (Qd^T 1) mu_x^T + mu_D (Qx^T 1 + M mu_x)^T."""
+    out_dtype = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
+    w_t = wq.transposed()                                   # [K, N]
+    rank1 = []
+    if da.mean is not None:
+        rank1.append((None, ops.nvfp4_gemv(w_t, da.mean)))
+    grad_input = _packed_matmul(da.q, w_t, rank1=rank1, out_dtype=out_dtype)
+
+    d_t = da.transposed()                                   # [N, M], col_vec = mu_D
+    x_t = xa.transposed()                                   # [K, M], col_vec = mu_x
+    rank1 = []
+    mu_x, mu_d = x_t.col_vec, d_t.col_vec
+    if mu_x is not None:
+        rank1.append((ops.nvfp4_gemv(d_t), mu_x))
+    if mu_d is not None:
+        tail = ops.nvfp4_gemv(x_t)
+        if mu_x is not None:
+            tail = tail + float(M) * mu_x
+        rank1.append((mu_d, tail))
+    grad_weight = _packed_matmul(d_t, x_t, rank1=rank1, out_dtype=torch.float32)
+    return grad_input, grad_weight
+
+
+class LinearLowbit(torch.nn.Module):
+    """Linear layer whose weight and input are quantized on the fly (bitlinear.py:515-595)."""
+
+    def __init__(self, in_features: int, out_features: int, bias=True, args=None, device=None,
+                 storage_dtype=torch.float32, compute_dtype=torch.float32) -> None:
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.storage_dtype = storage_dtype
+        self.compute_dtype = compute_dtype
+        self.cache_quantized_weight = getattr(args, "cache_quantized_weight", False)
+        self._quantized_weight_cache = None
+        where = args.device if device is None else device
+        self.weight = torch.nn.Parameter(torch.empty((out_features, in_features), dtype=storage_dtype, device=where))
+        self.bias = torch.nn.Parameter(torch.empty((out_features,), dtype=storage_dtype, device=where)) if bias else None
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+        if self.bias is not None:
+            fan_in, _ = init._calculate_fan_in_and_fan_out(self.weight)
+            bound = 1 / math.sqrt(fan_in) if fan_in > 0 else 0
+            init.uniform_(self.bias, -bound, bound)
+
+    def forward(self, input, quantized_input=None):
+        weight_compute = self.weight.to(self.compute_dtype)
+        bias_compute = self.bias.to(self.compute_dtype) if self.bias is not None else None
+        quantized_weight = self._get_quantized_weight(weight_compute)
+        return LinearLowbitFunction.apply(input, weight_compute, bias_compute, quantized_weight, quantized_input)
+
+    @torch.no_grad()
+    def _get_quantized_weight(self, weight_compute):
+        """Quantized weight with a one-entry cache keyed on the parameter version.  In packed
+        mode the entry is a PackedOperand (codes + scales, later also the transposed
+        quantization), otherwise the dequantized tensor."""
+        F = LinearLowbitFunction
+        packed = F._use_packed(weight_compute, F.q_forward_weight) and not F.enable_nv_recipe
+        cache_key = (self.weight._version, weight_compute.device, weight_compute.dtype, F.q_forward_weight,
+                     F.enable_nv_recipe, packed)
+        if self.cache_quantized_weight and self._quantized_weight_cache is not None:
+            cached_key, cached_weight = self._quantized_weight_cache
+            if cached_key == cache_key:
+                return cached_weight
+        if packed:
+            source = weight_compute.detach()
+            quantized_weight = PackedOperand(F.q_forward_weight.quantize_packed(source), source,
+                                             F.q_forward_weight, source.shape)
+        else:
+            quant_input = weight_compute
+            if F.enable_nv_recipe:
+                quant_input = F._apply_hadamard_blocks(quant_input, inverse=False)
+            quantized_weight = F.q_forward_weight.quantize_dequantize(quant_input)
+            if F.enable_nv_recipe:
+                quantized_weight = F._apply_hadamard_blocks(quantized_weight, inverse=True)
+        if self.cache_quantized_weight:
+            self._quantized_weight_cache = (cache_key, quantized_weight)
+        return quantized_weight
+
+    def _apply(self, fn, recurse=True):
+        self._quantized_weight_cache = None
+        return super()._apply(fn, recurse=recurse)
+
+
+# -----------------------------------------------------------------------------
+# fused low-rank + residual product (packed mode of BitLinear.forward)
+# -----------------------------------------------------------------------------
+class MetisFusedFunction(torch.autograd.Function):
+    """y = U (s . (x^ Vq^T)) + x^ Rq^T + b as ONE autograd node on the FP4 GEMM.
+
+    Forward: one small FP4 GEMM gives Yv = x^ Vq^T [M, r]; the residual GEMM then adds the
+    bf16 rank-r product (s . Yv) U^T inside the same tensor-memory accumulator, plus the mean and
+    bias row vectors in its epilogue.  Backward reproduces, node by node, what autograd derives
+    for the reference's chain vlinear -> s -> ulinear -> + warmup_linear (bitlinear.py:752-760):
+    ulinear is a plain (unquantized) linear, vlinear and warmup_linear use the quantized
+    backward of LinearLowbitFunction."""
+
+    @staticmethod
+    def forward(ctx, x, xa: PackedOperand, v_weight, vq: PackedOperand, s, u_weight, r_weight,
+                rq: PackedOperand, bias):
+        M, K = xa.q.shape
+        N = rq.q.shape[0]
+        act = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
+        rank1_v, rank1_r = [], []
+        if xa.mean is not None:
+            rank1_v.append((None, ops.nvfp4_gemv(vq.q, xa.mean)))
+            rank1_r.append((None, ops.nvfp4_gemv(rq.q, xa.mean)))
+        if bias is not None:
+            rank1_r.append((None, bias.float()))
+        yv = _packed_matmul(xa.q, vq.q, rank1=rank1_v, out_dtype=act)                 # [M, r]
+        ts = yv * s.to(act)                                                           # torch.mul(self.s, y)
+        # the side product accumulates in units of 1/(unit_x * unit_R)
+        t_acc = (ts.float() / (xa.q.unit * rq.q.unit)).to(torch.bfloat16)
+        u16 = u_weight.detach().to(torch.bfloat16)
+        y = _packed_matmul(xa.q, rq.q, rank1=rank1_r, lowrank=(t_acc, u16), out_dtype=act)
+        ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
+        ctx.has_bias = bias is not None
+        ctx.dims = (M, N, K)
+        ctx.save_for_backward(yv, s, u_weight)
+        return y.reshape(*xa.shape[:-1], N).to(xa.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        F = LinearLowbitFunction
+        yv, s, u_weight = ctx.saved_tensors
+        xa, vq, rq = ctx.xa, ctx.vq, ctx.rq
+        M, N, K = ctx.dims
+        r = yv.shape[1]
+        act = yv.dtype
+        g = grad_output.reshape(M, N).to(act)
+        grad_bias = g.sum(dim=0).to(torch.float32) if ctx.has_bias else None
+        # ulinear: plain linear on ts = s . yv
+        ts = yv * s.to(act)
+        u = u_weight.to(act)
+        grad_u = (g.T @ ts).to(u_weight.dtype)
+        d_ts = g @ u                                                                # [M, r]
+        grad_s = (d_ts * yv).sum(dim=0).to(s.dtype)
+        d_yv = d_ts * s.to(act)
+        centred = F._backward_centred()
+        quantizer = F.q_backward_outputgrad
+        # vlinear: quantized backward with grad_output = d_yv
+        dv = F._pack_centred(d_yv, quantizer, centred)
+        gx_v, grad_v = _packed_backward(dv, xa, vq, M, r, K)
+        # warmup_linear (the residual): quantized backward with grad_output = g
+        dg = F._pack_centred(g, quantizer, centred)
+        gx_r, grad_r = _packed_backward(dg, xa, rq, M, N, K)
+        grad_x = (gx_v + gx_r).reshape(xa.shape)
+        return grad_x, None, grad_v, None, grad_s, grad_u, grad_r, None, grad_bias
+
+
+class BitLinear(nn.Module):
+    """Drop-in replacement of nn.Linear: W = U diag(s) V + R with V and R in NVFP4
+    (reference: bitlinear.py:597-940)."""
+    rollout_merge_active = False
+
+    def __init__(self, in_features, out_features, args=None, bias=True, dtype=torch.float32, compute_dtype=None):
+        super().__init__()
+        self.storage_dtype = dtype
+        self.compute_dtype = compute_dtype if compute_dtype is not None else dtype
+        if self.compute_dtype not in [torch.float32, torch.float16, torch.bfloat16]:
+            raise ValueError(f"Unsupported compute_dtype: {self.compute_dtype}")
+
+        if args.enable_forward_svd == False and args.enable_lowbit == True:  # noqa: E712 (as the reference)
+            if args.enable_te:
+                raise RuntimeError("enable_te needs transformer_engine, which this build does not use")
+            self.warmup_linear = LinearLowbit(in_features, out_features, bias=bias, args=args,
+                                              storage_dtype=self.storage_dtype, compute_dtype=self.compute_dtype)
+        else:
+            self.warmup_linear = nn.Linear(in_features, out_features, bias=bias, device=args.device, dtype=self.storage_dtype)
+            init.kaiming_uniform_(self.warmup_linear.weight, a=math.sqrt(5))
+            if bias:
+                fan_in, _ = init._calculate_fan_in_and_fan_out(self.warmup_linear.weight)
+                bound = 1 / math.sqrt(fan_in) if fan_in > 0 else 0
+                init.uniform_(self.warmup_linear.bias, -bound, bound)
+
+        self.ulinear = None
+        self.vlinear = None
+        self.s = None
+
+        # process-global configuration: the last constructed layer wins (bitlinear.py:634-661)
+        F = LinearLowbitFunction
+        F.q_forward_input = quant_func[args.q_forward_input]
+        F.q_forward_weight = quant_func[args.q_forward_weight]
+        compile_qdq = getattr(args, "compile_qdq", False)
+        F.q_forward_input.compile_quantize_dequantize = compile_qdq
+        F.q_forward_weight.compile_quantize_dequantize = compile_qdq
+        F.q_backward_input = quant_func[args.q_backward_input]
+        F.q_backward_weight = quant_func[args.q_backward_weight]
+        F.q_backward_outputgrad = quant_func[args.q_backward_outputgrad]
+        F.enable_backward_svd = args.enable_backward_svd
+        F.backward_lowrank_svd = args.backward_lowrank_svd
+        F.backward_lowrank_niter = args.backward_lowrank_niter
+        F.enable_activation_svd = args.enable_activation_svd
+        F.activation_lowrank_svd = args.activation_lowrank_svd
+        F.activation_lowrank_niter = args.activation_lowrank_niter
+        F.activation_broadcast_dim = args.activation_broadcast_dim
+        F.backward_broadcast_dim = args.backward_broadcast_dim
+        F.enable_nv_recipe = args.enable_nv_recipe
+        F.hadamard_workspace_mb = getattr(args, "hadamard_workspace_mb", 128)
+        F.hadamard_tile_size = getattr(args, "hadamard_tile_size", 16)
+        F.hadamard_backend = getattr(args, "hadamard_backend", "auto")
+        F.tp_simulation = args.tp_simulation      # sic: the reference writes tp_simulation and reads tp_simulate
+        F.tp_parts = args.tp_parts
+        F.compute_dtype = self.compute_dtype
+        F.metis_mode = args.metis_mode
+        F.gemm_mode = getattr(args, "gemm_mode", "packed")
+
+        self.args = args
+        self.is_svd_quant = False
+        if args.forward_svd_warmup_steps <= 0 and args.enable_forward_svd:
+            print("split")
+            self.split()
+
+        self.mean_cache = {}
+        self.activation_group = None
+        self._merged_rollout_weight_cache = None
+        self.layer_name = ""
+
+    # ---- shared quantized activation (bitlinear.py:676-702) ------------------------------------------------
+    def _get_shared_quantized_input(self, x: torch.Tensor):
+        group = getattr(self, "activation_group", None)
+        if group is None:
+            return LinearLowbitFunction.quantize_input(x, mean_cache=self.mean_cache,
+                                                       cache_key=f"{self.layer_name}.shared")
+        ref = group.get("input_ref")
+        if ref is not None and ref() is x:
+            return group["quantized_input"]
+        quantized = LinearLowbitFunction.quantize_input(x, mean_cache=group["mean_cache"],
+                                                        cache_key=f"{group['name']}.shared")
+
+        def forget(dead):
+            if group.get("input_ref") is dead:
+                group["input_ref"] = None
+                group["quantized_input"] = None
+
+        group["input_ref"] = weakref.ref(x, forget)
+        group["quantized_input"] = quantized
+        return quantized
+
+    # ---- merged weight for rollout (bitlinear.py:704-730) -------------------------------------------------------
+    @torch.no_grad()
+    def _get_merged_rollout_weight(self, dtype: torch.dtype) -> torch.Tensor:
+        F = LinearLowbitFunction
+        cache_key = (self.vlinear.weight._version, self.ulinear.weight._version, self.s._version,
+                     self.warmup_linear.weight._version, self.vlinear.weight.device, dtype,
+                     F.q_forward_weight, F.enable_nv_recipe)
+        if self._merged_rollout_weight_cache is not None:
+            cached_key, cached_weight = self._merged_rollout_weight_cache
+            if cached_key == cache_key:
+                return cached_weight
+
+        def dense(w):
+            return w.dense(dtype) if isinstance(w, PackedOperand) else w
+
+        v_weight = dense(self.vlinear._get_quantized_weight(self.vlinear.weight.to(dtype)))
+        residual = dense(self.warmup_linear._get_quantized_weight(self.warmup_linear.weight.to(dtype)))
+        merged = (self.ulinear.weight.to(dtype) * self.s.to(dtype).unsqueeze(0)) @ v_weight + residual
+        self._merged_rollout_weight_cache = (cache_key, merged)
+        return merged
+
+    def _apply(self, fn, recurse=True):
+        self._merged_rollout_weight_cache = None
+        return super()._apply(fn, recurse=recurse)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        F = LinearLowbitFunction
+        F.mean_cache = self.mean_cache
+        if not self.is_svd_quant:
+            return self.warmup_linear(x)
+
+        share_activation = (isinstance(self.vlinear, LinearLowbit) and isinstance(self.warmup_linear, LinearLowbit)
+                            and self.args.forward_svd_rank > 0)
+        if share_activation:
+            shared = self._get_shared_quantized_input(x)
+            if isinstance(shared, PackedOperand):
+                fused = self._forward_packed(x, shared)
+                if fused is not None:
+                    return fused
+            if BitLinear.rollout_merge_active and not torch.is_grad_enabled():
+                dense_in = shared.dense(F.compute_dtype) if isinstance(shared, PackedOperand) else shared
+                y = torch.matmul(dense_in, self._get_merged_rollout_weight(dense_in.dtype).T)
+                if self.warmup_linear.bias is not None:
+                    y = y + self.warmup_linear.bias.to(y.dtype)
+                return y
+            y = self.vlinear(x, quantized_input=shared)
+        else:
+            F.mean_cache_key = f"{self.layer_name}.vlinear"
+            y = self.vlinear(x)
+        y = torch.mul(self.s, y)
+        y = self.ulinear(y)
+        if self.args.forward_svd_rank > 0:
+            if share_activation:
+                y = y + self.warmup_linear(x, quantized_input=shared)
+            else:
+                F.mean_cache_key = f"{self.layer_name}.warmup"
+                y = y + self.warmup_linear(x)
+        return y
+
+    def _forward_packed(self, x, shared: PackedOperand):
+        """Packed mode of the shared-activation branch: both weights as PackedOperand, one fused
+        autograd node.  Also serves rollout (no merged bf16 weight is needed: the FP4 weights are
+        a quarter of its bytes).  Returns None when a shape does not fit the FP4 GEMM."""
+        v, w = self.vlinear, self.warmup_linear
+        vq = v._get_quantized_weight(v.weight.to(v.compute_dtype))
+        rq = w._get_quantized_weight(w.weight.to(w.compute_dtype))
+        if not (isinstance(vq, PackedOperand) and isinstance(rq, PackedOperand)):
+            return None
+        M, K = shared.q.shape
+        r, N = vq.q.shape[0], rq.q.shape[0]
+        if not (_gemm_ok(M, N, K) and r % 16 == 0 and r <= 256):
+            return None
+        if torch.is_grad_enabled():
+            # the backward products contract over M, N and r and quantize the gradients natively
+            if not (M % 32 == 0 and N % 32 == 0 and r % 32 == 0 and _backward_can_pack(shared)):
+                return None
+        bias = w.bias.to(w.compute_dtype) if w.bias is not None else None
+        return MetisFusedFunction.apply(x, shared, v.weight, vq, self.s, self.ulinear.weight, w.weight, rq, bias)
+
+    @staticmethod
+    def _init_telinear(w, weight):
+        torch.nn.init.ones_(weight)
+        weight.mul_(w)
+
+    @torch.no_grad()
+    def split(self):
+        """One-time W -> U diag(s) V + R by exact fp32 SVD (bitlinear.py:776-924).  Works on any
+        device (the reference hard-codes .cuda())."""
+        args = self.args
+        if not args.enable_forward_svd:
+            return
+        if self.vlinear is not None:
+            u, s, v = torch.linalg.svd(self.ulinear.weight @ torch.diag(self.s) @ self.vlinear.weight, full_matrices=False)
+            bias = self.ulinear.bias
+            device = self.ulinear.weight.device
+            original_dtype = self.ulinear.weight.dtype
+        else:
+            w = self.warmup_linear.weight
+            device, original_dtype = w.device, w.dtype
+            u, s, v = torch.linalg.svd(w.to(torch.float32), full_matrices=False)
+            u, s, v = (t.to(device=device, dtype=original_dtype) for t in (u, s, v))
+            bias = self.warmup_linear.bias.to(device=device) if self.warmup_linear.bias is not None else None
+            rank = args.forward_svd_rank
+            if rank > 0:
+                residual = w - u[:, :rank] @ torch.diag(s[:rank]) @ v[:rank]
+                self.warmup_linear = LinearLowbit(w.shape[1], w.shape[0], bias=bias is not None, args=args,
+                                                  device=device, storage_dtype=original_dtype,
+                                                  compute_dtype=self.compute_dtype)
+                if bias is not None:
+                    self.warmup_linear.bias.copy_(bias)
+                self.warmup_linear.weight.copy_(residual)
+
+        rank = args.forward_svd_rank
+        if args.enable_lowbit:
+            if args.enable_te:
+                raise RuntimeError("enable_te needs transformer_engine, which this build does not use")
+            keep = rank if rank > 0 else v.shape[0]
+            self.vlinear = LinearLowbit(v.shape[1], keep, bias=False, args=args, device=device,
+                                        storage_dtype=original_dtype, compute_dtype=self.compute_dtype)
+            # the reference leaves ulinear at the default dtype/device; allocating it beside the
+            # weights saves a later .to() and is invisible to callers
+            self.ulinear = nn.Linear(keep, u.shape[0], bias=False, device=device, dtype=original_dtype)
+            self.vlinear.weight.copy_(v[:keep, :])
+            self.ulinear.weight.copy_(u[:, :keep])
+        else:
+            self.vlinear = nn.Linear(v.shape[1], v.shape[0], bias=False)
+            self.ulinear = nn.Linear(u.shape[1], u.shape[0])
+            self.vlinear.weight = nn.Parameter(v)
+            self.ulinear.weight = nn.Parameter(u)
+            if bias is not None:
+                self.ulinear.bias = nn.Parameter(bias.clone())
+
+        self.is_svd_quant = True
+        if rank > 0:
+            self.s = torch.nn.Parameter(s[:rank].clone())
+        else:
+            self.s = torch.nn.Parameter(s)
+            self.warmup_linear = None
+
+    @torch.no_grad()
+    def lowrank_initialization(self, rank: int = 32):
+        """Replace the weight by its best rank-`rank` approximation (bitlinear.py:926-940)."""
+        W = self.warmup_linear.weight
+        r = max(1, min(int(rank), min(W.shape)))
+        U, S, Vh = torch.linalg.svd(W.detach().to(torch.float32), full_matrices=False)
+        W.copy_(((U[:, :r] * S[:r]) @ Vh[:r, :]).to(dtype=W.dtype, device=W.device))
+        print(f"[lowrank_init] shape={tuple(W.shape)}  rank={r}")

@@ -1,0 +1,246 @@
+"""Tensor-level wrappers over the C ABI: PyTorch supplies device memory and streams only.
+
+Every function needs CUDA tensors and the built library; nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import cabi
+
+_DTYPES = {torch.bfloat16: cabi.DTYPE_BF16, torch.float32: cabi.DTYPE_F32}
+
+
+def _dtype_code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"{what} must be bfloat16 or float32, got {t.dtype}") from None
+
+
+def _need_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA tensor: the NVFP4 path has no CPU fallback")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _rows2d(x: torch.Tensor) -> torch.Tensor:
+    """View x as [rows, cols] with unit stride along cols (copy only if it has to)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) < x2.shape[1]):
+        x2 = x2.contiguous()
+    return x2
+
+
+@dataclass
+class NVFP4Tensor:
+    """A quantized [R, C] matrix: packed e2m1 codes, E4M3 block scales, fp32 unit.
+
+    `row_vec` (fp32 [C]) is the mean that was subtracted before quantization; the represented
+    matrix is value(codes, scales, unit) + 1 * row_vec (bitlinear.py:330-332).  For a
+    transposed quantization of x [M, K] with column means, `col_vec` (fp32 [R]) holds them
+    instead: the represented matrix is value + col_vec * 1^T.
+    """
+    codes: torch.Tensor          # uint8 [R, C/2]
+    scales: torch.Tensor         # uint8, flat
+    unit: torch.Tensor           # float32 [1]
+    shape: tuple
+    sf_layout: int
+    row_vec: Optional[torch.Tensor] = None
+    col_vec: Optional[torch.Tensor] = None
+
+    @property
+    def device(self):
+        return self.codes.device
+
+    def dequantize(self, dtype: torch.dtype = torch.float32, add_mean: bool = True) -> torch.Tensor:
+        return nvfp4_dequantize(self, dtype, add_mean=add_mean)
+
+
+def col_mean(x: torch.Tensor) -> torch.Tensor:
+    """Column means of x viewed as [rows, cols], fp32 (input_flat.mean(dim=0), bitlinear.py:326)."""
+    _need_cuda(x, "x")
+    x2 = _rows2d(x)
+    rows, cols = x2.shape
+    L = cabi.lib()
+    with torch.cuda.device(x2.device):
+        mean = torch.empty(cols, dtype=torch.float32, device=x2.device)
+        ws_bytes = L.metis_col_mean_workspace_bytes(rows, cols)
+        ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x2.device)
+        rc = L.metis_col_mean(x2.data_ptr(), _dtype_code(x2, "x"), rows, cols, x2.stride(0), mean.data_ptr(),
+                              ws.data_ptr(), ws.numel(), _stream())
+    cabi.check(rc, "metis_col_mean")
+    return mean
+
+
+def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool = False, seed: int = 0,
+                   offset: int = 0, sf_layout: int = cabi.SF_MMA,
+                   mean: Optional[torch.Tensor] = None) -> NVFP4Tensor:
+    """Quantize x (viewed as [rows, cols]) or, with transpose=True, its transpose.
+
+    `mean` (fp32 [cols]) is subtracted from every row of x first."""
+    _need_cuda(x, "x")
+    x2 = _rows2d(x)
+    rows, cols = x2.shape
+    R, Cc = (cols, rows) if transpose else (rows, cols)
+    if Cc % 16 != 0 or R == 0:
+        raise ValueError(f"NVFP4 block shape (1, 16) does not divide tensor shape {(R, Cc)}")
+    L = cabi.lib()
+    flags = (cabi.Q_TRANSPOSE if transpose else 0) | (cabi.Q_STOCHASTIC if stochastic else 0)
+    dev = x2.device
+    if mean is not None:
+        _need_cuda(mean, "mean")
+        mean = mean.reshape(-1).to(torch.float32).contiguous()
+        assert mean.numel() == cols
+    with torch.cuda.device(dev):
+        codes = torch.empty((R, Cc // 2), dtype=torch.uint8, device=dev)
+        scales = torch.empty(L.metis_nvfp4_sf_bytes(R, Cc, sf_layout), dtype=torch.uint8, device=dev)
+        unit = torch.empty(1, dtype=torch.float32, device=dev)
+        ws = torch.empty(L.metis_nvfp4_quantize_workspace_bytes(R, Cc), dtype=torch.uint8, device=dev)
+        rc = L.metis_nvfp4_quantize(x2.data_ptr(), _dtype_code(x2, "x"), rows, cols, x2.stride(0), _ptr(mean),
+                                    flags, seed & (2**64 - 1), offset & (2**64 - 1), sf_layout,
+                                    codes.data_ptr(), scales.data_ptr(), unit.data_ptr(), ws.data_ptr(),
+                                    ws.numel(), _stream())
+    cabi.check(rc, "metis_nvfp4_quantize")
+    q = NVFP4Tensor(codes, scales, unit, (R, Cc), sf_layout)
+    if mean is not None:
+        if transpose:
+            q.col_vec = mean
+        else:
+            q.row_vec = mean
+    return q
+
+
+def rmsnorm_nvfp4_quantize(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, *,
+                           sf_layout: int = cabi.SF_MMA, return_norm: bool = False):
+    """Fused RMSNorm -> NVFP4 quantization of x viewed as [rows, cols] (llama.py:23-31 then
+    quant.py:6-36).  Returns the NVFP4Tensor, and the normalised tensor too if asked."""
+    _need_cuda(x, "x")
+    _need_cuda(gamma, "gamma")
+    x2 = _rows2d(x)
+    rows, cols = x2.shape
+    if cols % 16 != 0 or rows == 0:
+        raise ValueError(f"NVFP4 block shape (1, 16) does not divide tensor shape {(rows, cols)}")
+    gamma = gamma.contiguous()
+    assert gamma.numel() == cols
+    L = cabi.lib()
+    dev = x2.device
+    with torch.cuda.device(dev):
+        codes = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+        scales = torch.empty(L.metis_nvfp4_sf_bytes(rows, cols, sf_layout), dtype=torch.uint8, device=dev)
+        unit = torch.empty(1, dtype=torch.float32, device=dev)
+        ws = torch.empty(L.metis_nvfp4_quantize_workspace_bytes(rows, cols), dtype=torch.uint8, device=dev)
+        norm = None
+        if return_norm:
+            out_dtype = torch.bfloat16 if (x2.dtype == torch.bfloat16 and gamma.dtype == torch.bfloat16) else torch.float32
+            norm = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+        rc = L.metis_rmsnorm_nvfp4_quantize(x2.data_ptr(), _dtype_code(x2, "x"), rows, cols, x2.stride(0),
+                                            gamma.data_ptr(), _dtype_code(gamma, "gamma"), float(eps), sf_layout,
+                                            codes.data_ptr(), scales.data_ptr(), unit.data_ptr(), _ptr(norm),
+                                            ws.data_ptr(), ws.numel(), _stream())
+    cabi.check(rc, "metis_rmsnorm_nvfp4_quantize")
+    q = NVFP4Tensor(codes, scales, unit, (rows, cols), sf_layout)
+    return (q, norm.reshape(x.shape)) if return_norm else q
+
+
+def nvfp4_dequantize(q: NVFP4Tensor, dtype: torch.dtype = torch.float32, add_mean: bool = True) -> torch.Tensor:
+    R, Cc = q.shape
+    L = cabi.lib()
+    with torch.cuda.device(q.device):
+        out = torch.empty((R, Cc), dtype=dtype, device=q.device)
+        rv = q.row_vec if add_mean else None
+        rc = L.metis_nvfp4_dequantize(q.codes.data_ptr(), q.scales.data_ptr(), q.unit.data_ptr(), q.sf_layout, R, Cc,
+                                      _ptr(rv), out.data_ptr(), _DTYPES[dtype], out.stride(0), _stream())
+    cabi.check(rc, "metis_nvfp4_dequantize")
+    if add_mean and q.col_vec is not None:
+        out += q.col_vec.to(dtype)[:, None]
+    return out
+
+
+def nvfp4_gemv(q: NVFP4Tensor, v: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = sum_c v[c] * value(q)[r, c] (v None: row sums), fp32; the mean vectors of q are ignored."""
+    R, Cc = q.shape
+    L = cabi.lib()
+    if v is not None:
+        v = v.reshape(-1).to(torch.float32).contiguous()
+        assert v.numel() == Cc
+    with torch.cuda.device(q.device):
+        out = torch.empty(R, dtype=torch.float32, device=q.device)
+        rc = L.metis_nvfp4_gemv(q.codes.data_ptr(), q.scales.data_ptr(), q.unit.data_ptr(), q.sf_layout, R, Cc,
+                                _ptr(v), out.data_ptr(), _stream())
+    cabi.check(rc, "metis_nvfp4_gemv")
+    return out
+
+
+def nvfp4_gemm(a: NVFP4Tensor, b: NVFP4Tensor, *, lowrank=None, rank1=(), c: Optional[torch.Tensor] = None,
+               out_dtype: torch.dtype = torch.bfloat16, alpha: float = 1.0,
+               status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+               _debug: int = 0) -> torch.Tensor:
+    """D = alpha*ua*ub * (A @ B^T + T @ U^T) + sum_i cvec_i (x) rvec_i (+ c), see metis_nvfp4_gemm.
+
+    a: [M, K], b: [N, K] (both METIS_SF_MMA).  lowrank = (T [M, r] bf16, U [N, r] bf16), already in
+    accumulator units.  rank1 = up to two (cvec or None, rvec) pairs of fp32 vectors.
+    Only the packed parts of a and b enter the product; their mean vectors do not."""
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise ValueError(f"inner dimensions differ: {K} vs {K2}")
+    if a.sf_layout != cabi.SF_MMA or b.sf_layout != cabi.SF_MMA:
+        raise ValueError("GEMM operands need METIS_SF_MMA scales")
+    dev = a.device
+    args = cabi.GemmArgs()
+    args.M, args.N, args.K = M, N, K
+    args.a_codes, args.a_scales, args.a_unit = a.codes.data_ptr(), a.scales.data_ptr(), a.unit.data_ptr()
+    args.b_codes, args.b_scales, args.b_unit = b.codes.data_ptr(), b.scales.data_ptr(), b.unit.data_ptr()
+    args.alpha = float(alpha)
+    keep = []
+    if lowrank is not None:
+        T, U = lowrank
+        if T.dtype != torch.bfloat16 or U.dtype != torch.bfloat16:
+            raise TypeError("low-rank factors must be bfloat16")
+        T, U = _rows2d(T), _rows2d(U)
+        if T.shape[0] != M or U.shape[0] != N or T.shape[1] != U.shape[1]:
+            raise ValueError(f"low-rank shapes {tuple(T.shape)} / {tuple(U.shape)} do not fit [{M}, r] / [{N}, r]")
+        keep += [T, U]
+        args.rank = T.shape[1]
+        args.lr_t, args.ldt = T.data_ptr(), T.stride(0)
+        args.lr_u, args.ldu = U.data_ptr(), U.stride(0)
+    if len(rank1) > 2:
+        raise ValueError("at most two rank-1 terms")
+    for i, (cv, rv) in enumerate(rank1):
+        rv = rv.reshape(-1).to(torch.float32).contiguous()
+        assert rv.numel() == N and rv.is_cuda
+        keep.append(rv)
+        if cv is not None:
+            cv = cv.reshape(-1).to(torch.float32).contiguous()
+            assert cv.numel() == M and cv.is_cuda
+            keep.append(cv)
+        setattr(args, f"cvec{i}", _ptr(cv))
+        setattr(args, f"rvec{i}", rv.data_ptr())
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=dev)
+        else:
+            assert out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1
+        if c is not None:
+            assert c.shape == (M, N) and c.dtype == out_dtype and c.stride(1) == 1 and c.is_cuda
+            args.c, args.ldc = c.data_ptr(), c.stride(0)
+        args.d, args.ldd = out.data_ptr(), out.stride(0)
+        args.d_dtype = _DTYPES[out_dtype]
+        args.reserved = int(_debug)
+        args.status = _ptr(status)
+        args.stream = _stream()
+        rc = cabi.lib().metis_nvfp4_gemm(C.byref(args))
+    cabi.check(rc, "metis_nvfp4_gemm")
+    return out

@@ -1,0 +1,173 @@
+"""NVFP4 quantizer kernels against the CPU oracle: packed codes, E4M3 bytes and unit bit-exact
+for round to nearest; stochastic rounding checked in distribution."""
+import numpy as np
+import pytest
+import torch
+
+from fp4_post_b200 import cabi, ops
+from oracle import nvfp4_oracle as O
+from gpu_helpers import assert_packed_equal, packed_to_numpy, synthetic
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib(built_library):
+    return built_library
+
+
+@pytest.mark.parametrize("name", ["randn_64x256", "outliers_32x512", "bf16valued_48x1536", "weights_128x256", "special_8x64"])
+@pytest.mark.parametrize("layout", [cabi.SF_ROWMAJOR, cabi.SF_MMA])
+def test_golden_vectors(quant_golden, name, layout):
+    g = quant_golden[name]
+    x = torch.from_numpy(g["x"]).to(DEV)
+    q = ops.nvfp4_quantize(x, sf_layout=layout)
+    codes, scales, unit = packed_to_numpy(q)
+    assert unit == g["unit"]
+    assert np.array_equal(codes, g["codes"])
+    want = g["scales"].reshape(-1) if layout == cabi.SF_ROWMAJOR else O.scales_to_mma_layout(g["scales"], x.shape[1])
+    assert np.array_equal(scales, want)
+    # and the dequantized tensor is the reference's fake-quant output, bit for bit
+    assert np.array_equal(q.dequantize(torch.float32).cpu().numpy(), g["qdq"])
+    if name == "bf16valued_48x1536":      # the same values arriving as bf16
+        qb = ops.nvfp4_quantize(x.to(torch.bfloat16), sf_layout=layout)
+        assert np.array_equal(qb.codes.cpu().numpy(), g["codes"])
+        assert np.array_equal(qb.scales.cpu().numpy(), want)
+
+
+def test_golden_mean_centred(quant_golden):
+    g = quant_golden["mean_96x256"]
+    x = torch.from_numpy(g["x"]).to(DEV)
+    mean = torch.from_numpy(g["mean"]).to(DEV)
+    q = ops.nvfp4_quantize(x, mean=mean, sf_layout=cabi.SF_ROWMAJOR)
+    codes, scales, unit = packed_to_numpy(q)
+    assert unit == g["unit"] and np.array_equal(codes, g["codes"]) and np.array_equal(scales, g["scales"].reshape(-1))
+    assert np.array_equal(q.dequantize(torch.float32).cpu().numpy(), g["qdq"])   # mean added back
+    # the kernel's own column mean is the torch mean up to summation order
+    got = ops.col_mean(x).cpu().numpy()
+    assert np.allclose(got, g["mean"], rtol=2e-6, atol=1e-6)
+
+
+SHAPES = [(1, 16, "normal"), (3, 48, "normal"), (33, 1536, "student"), (257, 272, "outliers"),
+          (2048, 2048, "outliers"), (1024, 3584, "student"), (96, 8960, "normal")]
+
+
+@pytest.mark.parametrize("rows,cols,kind", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("layout", [cabi.SF_ROWMAJOR, cabi.SF_MMA])
+def test_rows_match_oracle(rows, cols, kind, dtype, layout):
+    x = synthetic(rows, cols, kind, seed=rows * 7 + cols, dtype=dtype)
+    q = ops.nvfp4_quantize(x.to(DEV), sf_layout=layout)
+    assert_packed_equal(q, x.float().numpy(), layout, what=f"{rows}x{cols} {dtype}")
+
+
+@pytest.mark.parametrize("rows,cols,kind", [(16, 8, "normal"), (48, 24, "normal"), (512, 64, "outliers"),
+                                            (1040, 200, "student"), (2048, 2048, "outliers"), (4096, 1536, "student")])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_transposed_matches_oracle_on_the_transpose(rows, cols, kind, dtype):
+    x = synthetic(rows, cols, kind, seed=rows + cols, dtype=dtype)
+    q = ops.nvfp4_quantize(x.to(DEV), transpose=True, sf_layout=cabi.SF_MMA)
+    assert q.shape == (cols, rows)
+    assert_packed_equal(q, np.ascontiguousarray(x.float().numpy().T), cabi.SF_MMA, what="transposed")
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_mean_subtraction_matches_oracle(transpose, dtype):
+    x = synthetic(640, 384, "student", seed=5, dtype=dtype)
+    mean = x.float().mean(0)
+    q = ops.nvfp4_quantize(x.to(DEV), transpose=transpose, mean=mean.to(DEV), sf_layout=cabi.SF_ROWMAJOR)
+    centred = x.float().numpy() - mean.numpy()[None, :]      # fp32 subtraction, as the kernel does
+    if transpose:
+        assert_packed_equal(q, np.ascontiguousarray(centred.T), cabi.SF_ROWMAJOR, what="transposed mean")
+    else:
+        assert_packed_equal(q, x.float().numpy(), cabi.SF_ROWMAJOR, mean=mean.numpy(), what="row mean")
+
+
+def test_strided_rows():
+    wide = synthetic(100, 512, "normal", seed=9, dtype=torch.bfloat16).to(DEV)
+    view = wide[:, 128:384]                 # leading dimension 512, 256 columns
+    q = ops.nvfp4_quantize(view, sf_layout=cabi.SF_ROWMAJOR)
+    assert_packed_equal(q, view.float().cpu().numpy(), cabi.SF_ROWMAJOR, what="strided")
+    qt = ops.nvfp4_quantize(view[:96], transpose=True, sf_layout=cabi.SF_ROWMAJOR)
+    assert_packed_equal(qt, np.ascontiguousarray(view[:96].float().cpu().numpy().T), cabi.SF_ROWMAJOR, what="strided T")
+
+
+def test_all_zero_tensor_and_huge_values():
+    z = torch.zeros(32, 64, device=DEV)
+    q = ops.nvfp4_quantize(z, sf_layout=cabi.SF_ROWMAJOR)
+    assert_packed_equal(q, z.cpu().numpy(), cabi.SF_ROWMAJOR, what="zeros")
+    big = synthetic(64, 64, "normal", seed=3, dtype=torch.float32) * 1e30
+    q = ops.nvfp4_quantize(big.to(DEV), sf_layout=cabi.SF_ROWMAJOR)
+    assert_packed_equal(q, big.numpy(), cabi.SF_ROWMAJOR, what="1e30")
+
+
+def test_shape_errors_raise_value_error():
+    with pytest.raises(ValueError, match="does not divide"):
+        ops.nvfp4_quantize(torch.zeros(4, 24, device=DEV))
+    with pytest.raises(ValueError):
+        ops.nvfp4_quantize(torch.zeros(24, 32, device=DEV), transpose=True)     # 24 rows: not blocks of 16
+
+
+def test_dequantize_roundtrip_bf16_and_tiled_scales():
+    x = synthetic(300, 320, "outliers", seed=11, dtype=torch.bfloat16)
+    want = O.quantize_dequantize(x.float().numpy())
+    for layout in (cabi.SF_ROWMAJOR, cabi.SF_MMA):
+        q = ops.nvfp4_quantize(x.to(DEV), sf_layout=layout)
+        assert np.array_equal(q.dequantize(torch.float32).cpu().numpy(), want)
+        got16 = q.dequantize(torch.bfloat16).float().cpu().numpy()
+        assert np.array_equal(got16, torch.from_numpy(want).to(torch.bfloat16).float().numpy())
+
+
+def test_gemv_and_row_sums():
+    x = synthetic(200, 512, "normal", seed=13, dtype=torch.float32)
+    v = torch.randn(512, generator=torch.Generator().manual_seed(1))
+    q = ops.nvfp4_quantize(x.to(DEV), sf_layout=cabi.SF_MMA)
+    deq = O.quantize_dequantize(x.numpy()).astype(np.float64)
+    got = ops.nvfp4_gemv(q, v.to(DEV)).cpu().numpy()
+    assert np.allclose(got, deq @ v.numpy().astype(np.float64), rtol=1e-5, atol=1e-4)
+    assert np.allclose(ops.nvfp4_gemv(q).cpu().numpy(), deq.sum(1), rtol=1e-5, atol=1e-4)
+
+
+# ---- stochastic rounding ---------------------------------------------------------------------------
+
+GRID = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_stochastic_rounding_is_unbiased_and_stays_on_neighbours(transpose):
+    # every block: one element at 6 (so s = 1 exactly) and 15 copies of a probe value.
+    probes = [0.1, 0.3, 0.6, 0.85, 1.1, 1.7, 2.3, 3.3, 4.4, 5.5, -0.7, -2.6]
+    blocks = 70000                       # 15 * 70000 = 1.05e6 draws per probe
+    for p in probes:
+        row = torch.full((blocks, 16), p)
+        row[:, 0] = 6.0
+        x = row.t().contiguous() if transpose else row
+        q = ops.nvfp4_quantize(x.to(DEV), transpose=transpose, stochastic=True, seed=1234, offset=int(abs(p) * 100),
+                               sf_layout=cabi.SF_ROWMAJOR)
+        codes, scales, unit = packed_to_numpy(q)
+        vals = O.unpack_codes(codes)[:, 1:]
+        lo = GRID[GRID <= abs(p)].max()
+        hi = GRID[GRID >= abs(p)].min()
+        mags = np.abs(vals)
+        assert np.isin(mags, [lo, hi]).all(), f"probe {p}: codes off the two neighbours"
+        assert (np.sign(vals[vals != 0]) == np.sign(p)).all()
+        frac = (abs(p) - lo) / (hi - lo)
+        sigma = (hi - lo) * np.sqrt(frac * (1 - frac) / vals.size)
+        assert abs(mags.mean() - abs(p)) < 4 * sigma + 1e-7, f"probe {p}: mean {mags.mean()}"
+        # scales do not depend on the rounding mode
+        qr = ops.nvfp4_quantize(x.to(DEV), transpose=transpose, sf_layout=cabi.SF_ROWMAJOR)
+        assert np.array_equal(scales, qr.scales.cpu().numpy()) and unit == np.float32(qr.unit.item())
+
+
+def test_stochastic_rounding_depends_on_seed_and_offset_only():
+    x = synthetic(256, 256, "normal", seed=21, dtype=torch.bfloat16).to(DEV)
+    a = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=1).codes
+    b = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=1).codes
+    c = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=2).codes
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    # dequantized SR output is unbiased against the input within the block scale
+    deq = ops.nvfp4_quantize(x, stochastic=True, seed=9, offset=3, sf_layout=cabi.SF_ROWMAJOR).dequantize(torch.float32)
+    err = (deq - x.float()).mean().abs().item()
+    assert err < 5e-3
