@@ -1,0 +1,337 @@
+#!/usr/bin/env python
+"""Benchmark of the Metis NVFP4 linear-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one forward + backward of ONE Metis linear layer (rank-r bf16 low-rank product + NVFP4
+residual, mean-centred activations and gradients, stochastic-rounding backward: the GRPO default
+configuration) on a fixed batch of synthetic tokens, through the public `BitLinear` module.
+Workload: M = 16384 tokens, K = N = 4096, r = 128, bf16 -- the largest square shape of the GEMM
+shape sweep with a low-rank term.  value = algorithmic TFLOP/s, (6 M N K + 6 M r (K+N)) / step time,
+summed over all GPUs (token batch sharded, weights replicated; for N > 1 the weight gradients are
+all-reduced with NCCL inside the step, as a data-parallel trainer would).
+
+The JSON line also carries
+  e2e          the same step through the same API with HOST inputs: pinned host -> device copies of
+               x and grad_out and a device -> host read of a checksum inside the timed region
+  roofline     the tcgen05 GEMM kernel alone (CUDA events around back-to-back launches of the
+               forward residual GEMM with its fused rank-r product) against 4 x the measured dense bf16
+               rate, the dense NVFP4 : bf16 ratio of the part
+  quant        the HBM-bound kernels alone: fused RMSNorm->NVFP4 and the plain quantizer at hidden
+               4096 x 65536 tokens, algorithmic GB/s against the measured copy bandwidth
+  cpu_baseline the CPU oracle of the same layer (the reference's fake-quant algorithm restated,
+               oracle/metis_layer.py) timed on this host's cores on a slice of the same workload
+
+`--impl reference` times that CPU implementation as the whole job (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M_TOKENS, HIDDEN_K, HIDDEN_N, RANK = 16384, 4096, 4096, 128
+QUANT_ROWS, QUANT_COLS = 65536, 4096
+METRIC = "metis_nvfp4_linear_fwd_bwd_tflops"
+BYTES_PER_ELEM_BF16 = 2.5625          # 2 (bf16 in) + 0.5 (codes) + 1/16 (E4M3 scale)
+
+
+def layer_flops(M, N, K, r):
+    return 6 * M * N * K + 6 * M * r * (K + N)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+# ---- clocks during the timed region -----------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()          # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [c for c in sm if c > 0.5 * max(mx, default=1)] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---- CPU arm ------------------------------------------------------------------------------------------------
+
+def cpu_layer_step_seconds(tokens, steps, warmup, threads):
+    """fwd+bwd of the same layer on the CPU oracle for `tokens` tokens; median seconds per step."""
+    import torch
+    from oracle import metis_layer as ML
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1, tokens, HIDDEN_K, generator=g)
+    x[..., torch.randperm(HIDDEN_K, generator=g)[: HIDDEN_K // 100]] *= 20
+    W = torch.randn(HIDDEN_N, HIDDEN_K, generator=g) / HIDDEN_K ** 0.5
+    grad = torch.randn(1, tokens, HIDDEN_N, generator=g)
+    # a rank-r split without the (slow, one-time) exact SVD: random orthogonal-ish factors
+    U = torch.randn(HIDDEN_N, RANK, generator=g) / HIDDEN_N ** 0.5
+    V = torch.randn(RANK, HIDDEN_K, generator=g) / HIDDEN_K ** 0.5
+    s = torch.rand(RANK, generator=g) + 0.5
+    R = W - U @ torch.diag(s) @ V
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        y, saved = ML.forward(x, U, s, V, R, None, threads=threads)
+        ML.backward(grad, saved, U, s, has_bias=False, threads=threads)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return statistics.median(times)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = len(os.sched_getaffinity(0))
+    tokens = 2048                                  # bounded sample: 1/8 of the token batch per step
+    sec = cpu_layer_step_seconds(tokens, max(1, args.steps), max(0, min(args.warmup, 1)), threads)
+    tf = layer_flops(tokens, HIDDEN_N, HIDDEN_K, RANK) / sec / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * (M_TOKENS / tokens),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (simulated in fp32)",
+        "data": "synthetic", "config": workload_config(1),
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"{tokens} of {M_TOKENS} tokens per step, same N, K, r; ms_per_step is scaled to the full batch"},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": f"one Metis NVFP4 linear layer fwd+bwd, M={M_TOKENS} tokens per GPU, K={HIDDEN_K}, N={HIDDEN_N}, "
+                        f"rank {RANK}, bf16, mean mode, RTN forward / stochastic-rounding backward",
+            "tokens_per_gpu": M_TOKENS, "in_features": HIDDEN_K, "out_features": HIDDEN_N, "rank": RANK,
+            "parallelism": f"dp{n_gpus} (tokens sharded, weights replicated" + (", NCCL all-reduce of weight grads)" if n_gpus > 1 else ")"),
+            "l2": "inputs larger than L2 (x and grad_out are 128 MiB each)"}
+
+
+# ---- GPU arm ------------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    import fp4_post_b200
+    from fp4_post_b200 import cabi, ops
+    from fp4_post_b200.Metis.Metis.bitlinear import BitLinear
+    from fp4_post_b200.grpo.grpo import MetisArgs
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the NVFP4 path has no CPU fallback "
+                         "(use --impl reference for the CPU arm)")
+    cabi.lib()                                     # fail loudly if the library is not built
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(3, args.warmup)
+    peaks = measured_peaks()
+
+    # ---- the layer ----------------------------------------------------------------------------------------------
+    torch.manual_seed(0)
+    margs = MetisArgs(forward_svd_rank=RANK, activation_lowrank_svd=RANK, backward_lowrank_svd=RANK,
+                      cache_quantized_weight=True)
+    margs.device = dev
+    layer = BitLinear(HIDDEN_K, HIDDEN_N, args=margs, bias=False, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+    with torch.no_grad():
+        layer.warmup_linear.weight.copy_(torch.randn(HIDDEN_N, HIDDEN_K, device=dev) / HIDDEN_K ** 0.5)
+    layer.layer_name = "bench.layer"
+    layer.split()                                  # exact SVD once, outside the timed region
+    params = [p for p in layer.parameters()]
+
+    g = torch.Generator(device="cpu").manual_seed(1 + rank)
+    x_host = torch.randn(1, M_TOKENS, HIDDEN_K, generator=g).to(torch.bfloat16)
+    x_host[..., torch.randperm(HIDDEN_K, generator=g)[: HIDDEN_K // 100]] *= 20      # 1 % outlier channels
+    g_host = torch.randn(1, M_TOKENS, HIDDEN_N, generator=g).to(torch.bfloat16)
+    x_host, g_host = x_host.pin_memory(), g_host.pin_memory()
+    x_dev = x_host.to(dev).requires_grad_(True)
+    g_dev = g_host.to(dev)
+    flops = layer_flops(M_TOKENS, HIDDEN_N, HIDDEN_K, RANK)
+
+    def step(x, grad):
+        for p in params:
+            p.grad = None
+        x.grad = None
+        y = layer(x)
+        y.backward(grad)
+        if world > 1:
+            for p in params:                       # what DDP would do for this layer
+                dist.all_reduce(p.grad)
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        """n calls between events on the current stream; ms per call, max over ranks."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / n
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(warmup):
+        step(x_dev, g_dev)
+    with ClockSampler(local) as clocks:
+        launches0 = ops.launch_count()
+        ms_step = timed(lambda: step(x_dev, g_dev), args.steps)
+        launches = ops.launch_count() - launches0
+
+        # ---- end to end: host inputs, checksum back -------------------------------------------------------------
+        x_in = torch.empty_like(x_dev).requires_grad_(True)
+        g_in = torch.empty_like(g_dev)
+
+        def e2e_step():
+            with torch.no_grad():
+                x_in.copy_(x_host, non_blocking=True)
+                g_in.copy_(g_host, non_blocking=True)
+            y = step(x_in, g_in)
+            return float(y.float().abs().mean().item() + x_in.grad.float().abs().mean().item())
+
+        for _ in range(2):
+            e2e_step()
+        ms_e2e = timed(e2e_step, max(3, args.steps // 2))
+
+        # ---- kernel-level lines (rank 0's GPU; every rank runs them so that nobody idles) ----------------------
+        shared = layer._get_shared_quantized_input(x_dev.detach())
+        rq = layer.warmup_linear._get_quantized_weight(layer.warmup_linear.weight)
+        t_acc = torch.randn(M_TOKENS, RANK, device=dev, dtype=torch.bfloat16)
+        u16 = layer.ulinear.weight.detach().to(torch.bfloat16)
+        out = torch.empty(M_TOKENS, HIDDEN_N, device=dev, dtype=torch.bfloat16)
+        gemm = lambda: ops.nvfp4_gemm(shared.q, rq.q, lowrank=(t_acc, u16), out=out)
+        for _ in range(3):
+            gemm()
+        ms_gemm = timed(gemm, 20)
+        gemm_flops = 2 * M_TOKENS * HIDDEN_N * HIDDEN_K + 2 * M_TOKENS * HIDDEN_N * RANK
+
+        xq = torch.randn(QUANT_ROWS, QUANT_COLS, device=dev, dtype=torch.bfloat16)
+        gamma = torch.ones(QUANT_COLS, device=dev, dtype=torch.bfloat16)
+        quant_lines = {}
+        for name, fn in (("rmsnorm_quant", lambda: ops.rmsnorm_nvfp4_quantize(xq, gamma, 1e-6)),
+                         ("quant_rows", lambda: ops.nvfp4_quantize(xq)),
+                         ("quant_transposed", lambda: ops.nvfp4_quantize(xq, transpose=True))):
+            for _ in range(3):
+                fn()
+            ms = timed(fn, 10)
+            gbs = QUANT_ROWS * QUANT_COLS * BYTES_PER_ELEM_BF16 / ms / 1e6
+            quant_lines[name] = {"gbs": round(gbs, 1), "ms": round(ms, 4), "frac_of_hbm_copy": round(gbs / peaks["hbm_gbs"], 4)}
+        del xq
+    clock_summary = clocks.summary()
+
+    # ---- CPU baseline on this host's cores (rank 0, N = 1 only) ----------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1:
+        threads = len(os.sched_getaffinity(0))
+        tokens = 2048
+        sec = cpu_layer_step_seconds(tokens, steps=2, warmup=1, threads=threads)
+        cpu = {"value": layer_flops(tokens, HIDDEN_N, HIDDEN_K, RANK) / sec / 1e12, "unit": "TFLOP/s", "cores": threads,
+               "kind": "port", "sample": f"{tokens} of {M_TOKENS} tokens, same N, K, r, 2 timed steps after 1 warm-up"}
+
+    if rank == 0:
+        fp4_peak = 4.0 * peaks["bf16_tflops"]
+        achieved = gemm_flops / ms_gemm / 1e9
+        line = {
+            "metric": METRIC, "value": world * flops / ms_step / 1e9, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate) + bf16 rank-r",
+            "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": world * flops / ms_e2e / 1e9, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": x_host.numel() * 2 + g_host.numel() * 2, "d2h_bytes_per_step": 8,
+                    "ms_per_step": ms_e2e},
+            "gpu_launches": launches,
+            "clocks": clock_summary,
+            "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_kernel<256> forward residual GEMM + fused rank-128 product",
+                         "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
+                         "traffic": None, "peak_source": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s)",
+                         "frac_of_nominal_9000": achieved / 9000.0, "ms_per_launch": ms_gemm},
+            "quant": quant_lines,
+            "hbm_peak_gbs": peaks["hbm_gbs"],
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -82,6 +82,20 @@ def _backward_can_pack(shared) -> bool:
     return LinearLowbitFunction._packed_backward_ok(shared.source)
 
 
+def _bf16_factors(t32: torch.Tensor, u: torch.Tensor, act: torch.dtype):
+    """The rank-r factors as bf16 operands of the side product.  With bf16 activations they are
+    simply rounded (the reference computes them in bf16 too).  With fp32 activations each factor
+    is split into a bf16 head and tail and the product is issued as [Th Tl Th] [Uh Uh Ul]^T, which
+    keeps about 16 significant bits at three times the (small) rank."""
+    r = t32.shape[1]
+    if act != torch.float32 or 3 * r > 256:
+        return t32.to(torch.bfloat16), u.to(torch.bfloat16)
+    u32 = u.float()
+    t_hi, u_hi = t32.to(torch.bfloat16), u32.to(torch.bfloat16)
+    t_lo, u_lo = (t32 - t_hi.float()).to(torch.bfloat16), (u32 - u_hi.float()).to(torch.bfloat16)
+    return torch.cat([t_hi, t_lo, t_hi], dim=1), torch.cat([u_hi, u_hi, u_lo], dim=1)
+
+
 def _gemm_ok(M, N, K):
     """Shapes the packed GEMM takes (rows of packed codes must be multiples of 16 bytes)."""
     return K % 32 == 0 and M > 0 and N > 0
@@ -551,9 +565,9 @@ class MetisFusedFunction(torch.autograd.Function):
         yv = _packed_matmul(xa.q, vq.q, rank1=rank1_v, out_dtype=act)                 # [M, r]
         ts = yv * s.to(act)                                                           # torch.mul(self.s, y)
         # the side product accumulates in units of 1/(unit_x * unit_R)
-        t_acc = (ts.float() / (xa.q.unit * rq.q.unit)).to(torch.bfloat16)
-        u16 = u_weight.detach().to(torch.bfloat16)
-        y = _packed_matmul(xa.q, rq.q, rank1=rank1_r, lowrank=(t_acc, u16), out_dtype=act)
+        t_acc = ts.float() / (xa.q.unit * rq.q.unit)
+        y = _packed_matmul(xa.q, rq.q, rank1=rank1_r, lowrank=_bf16_factors(t_acc, u_weight.detach(), act),
+                           out_dtype=act)
         ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
         ctx.has_bias = bias is not None
         ctx.dims = (M, N, K)

@@ -14,6 +14,14 @@ from . import cabi
 
 _DTYPES = {torch.bfloat16: cabi.DTYPE_BF16, torch.float32: cabi.DTYPE_F32}
 
+# Kernels of this library launched since import, by entry point (two per quantizer call: the
+# streaming pass and the scale pass; the memset between them is not a kernel).
+LAUNCHES = {"quantize": 0, "rmsnorm_quantize": 0, "dequantize": 0, "col_mean": 0, "gemv": 0, "gemm": 0}
+
+
+def launch_count() -> int:
+    return sum(LAUNCHES.values())
+
 
 def _dtype_code(t: torch.Tensor, what: str) -> int:
     try:
@@ -81,6 +89,7 @@ def col_mean(x: torch.Tensor) -> torch.Tensor:
         rc = L.metis_col_mean(x2.data_ptr(), _dtype_code(x2, "x"), rows, cols, x2.stride(0), mean.data_ptr(),
                               ws.data_ptr(), ws.numel(), _stream())
     cabi.check(rc, "metis_col_mean")
+    LAUNCHES["col_mean"] += 2
     return mean
 
 
@@ -113,6 +122,7 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
                                     codes.data_ptr(), scales.data_ptr(), unit.data_ptr(), ws.data_ptr(),
                                     ws.numel(), _stream())
     cabi.check(rc, "metis_nvfp4_quantize")
+    LAUNCHES["quantize"] += 2
     q = NVFP4Tensor(codes, scales, unit, (R, Cc), sf_layout)
     if mean is not None:
         if transpose:
@@ -150,6 +160,7 @@ def rmsnorm_nvfp4_quantize(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e
                                             codes.data_ptr(), scales.data_ptr(), unit.data_ptr(), _ptr(norm),
                                             ws.data_ptr(), ws.numel(), _stream())
     cabi.check(rc, "metis_rmsnorm_nvfp4_quantize")
+    LAUNCHES["rmsnorm_quantize"] += 2
     q = NVFP4Tensor(codes, scales, unit, (rows, cols), sf_layout)
     return (q, norm.reshape(x.shape)) if return_norm else q
 
@@ -163,6 +174,7 @@ def nvfp4_dequantize(q: NVFP4Tensor, dtype: torch.dtype = torch.float32, add_mea
         rc = L.metis_nvfp4_dequantize(q.codes.data_ptr(), q.scales.data_ptr(), q.unit.data_ptr(), q.sf_layout, R, Cc,
                                       _ptr(rv), out.data_ptr(), _DTYPES[dtype], out.stride(0), _stream())
     cabi.check(rc, "metis_nvfp4_dequantize")
+    LAUNCHES["dequantize"] += 1
     if add_mean and q.col_vec is not None:
         out += q.col_vec.to(dtype)[:, None]
     return out
@@ -180,6 +192,7 @@ def nvfp4_gemv(q: NVFP4Tensor, v: Optional[torch.Tensor] = None) -> torch.Tensor
         rc = L.metis_nvfp4_gemv(q.codes.data_ptr(), q.scales.data_ptr(), q.unit.data_ptr(), q.sf_layout, R, Cc,
                                 _ptr(v), out.data_ptr(), _stream())
     cabi.check(rc, "metis_nvfp4_gemv")
+    LAUNCHES["gemv"] += 1
     return out
 
 
@@ -243,4 +256,5 @@ def nvfp4_gemm(a: NVFP4Tensor, b: NVFP4Tensor, *, lowrank=None, rank1=(), c: Opt
         args.stream = _stream()
         rc = cabi.lib().metis_nvfp4_gemm(C.byref(args))
     cabi.check(rc, "metis_nvfp4_gemm")
+    LAUNCHES["gemm"] += 1
     return out
