@@ -13,6 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libmetis_nvfp4.so"
 DTYPE_BF16, DTYPE_F32 = 0, 1
 SF_ROWMAJOR, SF_MMA = 0, 1
 Q_TRANSPOSE, Q_STOCHASTIC = 1, 2
+STATIC_MAX_ELEMENTS = 16 * 1024 * 1024
 
 STATUS_TEXT = {
     0: "ok", -1: "bad argument", -2: "bad shape", -3: "bad alignment", -4: "workspace too small",
@@ -25,7 +26,7 @@ EXPORTS = (
     "metis_query", "metis_last_error_string", "metis_nvfp4_sf_bytes",
     "metis_nvfp4_quantize_workspace_bytes", "metis_nvfp4_quantize", "metis_rmsnorm_nvfp4_quantize",
     "metis_nvfp4_dequantize", "metis_col_mean_workspace_bytes", "metis_col_mean", "metis_nvfp4_gemv",
-    "metis_nvfp4_gemm",
+    "metis_nvfp4_gemm", "metis_nvfp4_quantize_static",
 )
 
 
@@ -75,6 +76,8 @@ def lib() -> C.CDLL:
     L.metis_nvfp4_quantize_workspace_bytes.restype = i64
     L.metis_nvfp4_quantize.argtypes = [vp, i32, i64, i64, i64, vp, u32, u64, u64, i32, vp, vp, vp, vp, i64, vp]
     L.metis_nvfp4_quantize.restype = i32
+    L.metis_nvfp4_quantize_static.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, vp, vp]
+    L.metis_nvfp4_quantize_static.restype = i32
     L.metis_rmsnorm_nvfp4_quantize.argtypes = [vp, i32, i64, i64, i64, vp, i32, f32, i32, vp, vp, vp, vp, vp, i64, vp]
     L.metis_rmsnorm_nvfp4_quantize.restype = i32
     L.metis_nvfp4_dequantize.argtypes = [vp, vp, vp, i32, i64, i64, vp, vp, i32, i64, vp]

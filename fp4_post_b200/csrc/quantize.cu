@@ -9,6 +9,8 @@
 // consumer wants and publishes the per-tensor unit.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace metis {
 
 constexpr int kQuantThreads = 256;
@@ -454,4 +456,77 @@ extern "C" int32_t metis_col_mean(const void* x, int32_t x_dtype, int64_t rows, 
   col_mean_finish_kernel<<<(unsigned)ceil_div(cols, 256), 256, 0, st>>>(partial, splits, rows, cols, mean);
   METIS_CUDA_OK(cudaGetLastError());
   return METIS_OK;
+}
+
+// ---- quantizer entry point that brings its own scratch -----------------------------------------------
+//
+// metis_nvfp4_quantize needs a caller-provided workspace for the per-block maxima.  Some callers
+// have no way to provide one: a serving loop whose device memory was carved up once at start-up
+// and must not grow, a host binding (cgo, JNI) that holds raw device pointers but no allocator, a
+// latency-critical section in which cudaMalloc's implicit device synchronisation is not acceptable.
+// For them the scratch lives in this translation unit as a fixed-size device array; the price is
+// that every GPU that loads the library keeps these bytes until the process exits, and that the
+// tensor size is capped.
+namespace metis {
+
+constexpr int64_t kStaticMaxElements = METIS_STATIC_MAX_ELEMENTS;                        // 16 Mi elements
+constexpr int64_t kStaticScratchBytes = kWorkspaceHeaderBytes + (kStaticMaxElements / 16) * 4;  // 4 MiB + 256 B
+
+// In device code this name is the array.  In host code it is only a handle for the runtime's symbol
+// table, NOT a device address: the address is looked up below with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+// Device address of the array on the CURRENT device, resolved once per device.
+static int32_t static_scratch_address(void** out) {
+  int dev = -1;
+  METIS_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(METIS_ERR_UNSUPPORTED, "device index %d is outside [0, %d)", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(METIS_ERR_CUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", dev, cudaGetErrorString(e));
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return METIS_OK;
+}
+
+}  // namespace metis
+
+extern "C" int32_t metis_nvfp4_quantize_static(const void* x, int32_t x_dtype, int64_t rows, int64_t cols,
+                                               int64_t ld, int32_t sf_layout, uint8_t* codes,
+                                               uint8_t* scales, float* unit, void* stream) {
+  if (!x) return fail(METIS_ERR_BAD_ARGUMENT, "x is null");
+  if (x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown x_dtype %d", x_dtype);
+  if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)rows, (long long)cols);
+  if (cols % 16 != 0)
+    return fail(METIS_ERR_BAD_SHAPE, "NVFP4 block shape (1, 16) does not divide tensor shape (%lld, %lld)", (long long)rows, (long long)cols);
+  if (rows > kStaticMaxElements / cols)
+    return fail(METIS_ERR_TOO_LARGE, "%lld x %lld elements exceed the built-in scratch (METIS_STATIC_MAX_ELEMENTS = %lld); "
+                "use metis_nvfp4_quantize with a caller workspace", (long long)rows, (long long)cols, (long long)kStaticMaxElements);
+  if (ld < cols) return fail(METIS_ERR_BAD_ARGUMENT, "ld %lld < cols %lld", (long long)ld, (long long)cols);
+  if (sf_layout != METIS_SF_ROWMAJOR && sf_layout != METIS_SF_MMA) return fail(METIS_ERR_BAD_ARGUMENT, "unknown sf_layout %d", sf_layout);
+  if (!codes || !scales || !unit) return fail(METIS_ERR_BAD_ARGUMENT, "null output pointer");
+  if (ld % 8 != 0 || !aligned16(x) || !aligned16(codes) || !aligned16(scales))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "x, codes and scales must be 16-byte aligned and ld a multiple of 8");
+
+  void* scratch = nullptr;
+  if (int32_t rc = static_scratch_address(&scratch)) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const WorkspaceView ws = view_workspace(scratch);
+  // The array keeps whatever the previous call left.  Only the running maximum has to start at
+  // zero; every block maximum this call reads back is written by this call first.
+  METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, sizeof(unsigned int), st));
+  if (x_dtype == METIS_DTYPE_BF16)
+    launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, nullptr, false, 0, 0, reinterpret_cast<uint32_t*>(codes), ws, st);
+  else
+    launch_rows(static_cast<const float*>(x), rows, cols, ld, nullptr, false, 0, 0, reinterpret_cast<uint32_t*>(codes), ws, st);
+  METIS_CUDA_OK(cudaGetLastError());
+  return launch_finalize(ws, rows, cols, sf_layout, scales, unit, st);
 }

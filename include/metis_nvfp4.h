@@ -12,7 +12,8 @@
  *  - extern "C", plain pointers and sizes, no C++ or torch types.
  *  - All data pointers are DEVICE pointers unless stated otherwise.  The caller owns
  *    every buffer, including scratch ("workspace"); the library never allocates device
- *    memory and keeps no pointer after a call returns.
+ *    memory and keeps no pointer after a call returns.  (One exception, stated at its
+ *    declaration: metis_nvfp4_quantize_static keeps its scratch inside the library.)
  *  - Every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL is the
  *    legacy default stream) and returns a host-side status: 0 = launched,
  *    negative = argument rejected (nothing was launched).  metis_last_error_string()
@@ -112,6 +113,30 @@ int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64
                              const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,
                              int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,
                              void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
+ * The same round-to-nearest, row-major quantizer for callers that cannot hand over a workspace
+ * and must not trigger an allocation: a serving process whose device memory was divided up once
+ * at start-up, a host binding that holds raw device pointers but no allocator, code for which
+ * cudaMalloc's implicit synchronisation is unacceptable.  This entry point has no counterpart in
+ * the reference (which allocates freely through PyTorch).
+ *
+ * The scratch is a fixed array inside the library: 4 MiB + 256 bytes of device memory on every GPU
+ * that loads the library, held until the process exits.  Limit: rows * cols <=
+ * METIS_STATIC_MAX_ELEMENTS; larger tensors are rejected with METIS_ERR_TOO_LARGE.  The call
+ * allocates nothing (no cudaMalloc/cudaFree, no allocating library routine).
+ *  - The first call on each device looks the array's address up (cudaGetSymbolAddress) with that
+ *    device current; make that first call before any stream capture begins.
+ *  - All calls on a device share the one array and it keeps the previous call's contents; the call
+ *    clears the part that has to start at zero.  Two calls that overlap on the GPU (different
+ *    streams, or threads) race on it: serialise them.
+ * Arguments and results are those of metis_nvfp4_quantize without col_mean, flags, seed, offset
+ * and workspace; outputs are bit-identical to it.
+ */
+#define METIS_STATIC_MAX_ELEMENTS (16 * 1024 * 1024)
+int32_t metis_nvfp4_quantize_static(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                    int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,
+                                    void* stream);
 
 /*
  * Fused RMSNorm -> NVFP4 quantizer: reads each activation row from HBM once.
