@@ -81,65 +81,105 @@ __device__ __forceinline__ uint8_t float_to_e4m3(float v) {
 }
 
 // Block scale from the block's absolute maximum: amax/6 + 1e-9 with two fp32 roundings
-// (quant.py:19).
+// (quant.py:19).  The division is the correctly rounded one: q0 = a*r, e = fma(-6, q0, a),
+// q = fma(e, r, q0) with r = RN(1/6) equals RN(a/6) for every finite a >= 2^-125 (checked
+// exhaustively against IEEE division); below that the quotient is < 2^-127 and the sum with
+// 1e-9 is 1e-9 either way.
 __device__ __forceinline__ float block_scale_from_amax(float amax) {
-  return __fadd_rn(__fdiv_rn(amax, 6.0f), 1e-9f);
+  const float r6 = 0x1.555556p-3f;
+  const float q0 = __fmul_rn(amax, r6);
+  const float q = __fmaf_rn(__fmaf_rn(-6.0f, q0, amax), r6, q0);
+  return __fadd_rn(q, 1e-9f);
 }
 
-// Exact reference code of one magnitude: |x| / (s/2), folded onto 0..7, round half to even
-// (quant.py:26-31).  relu(q-4)/2 == max(fma(q, .5, -2), 0) because scaling by a power of
-// two commutes with rounding; likewise relu(q-8)/4.
-__device__ __forceinline__ uint32_t e2m1_code_exact(float ax, float half_s) {
-  const float q = __fdiv_rn(ax, half_s);
-  const float a = fmaxf(__fmaf_rn(q, 0.5f, -2.0f), 0.0f);
-  const float b = fmaxf(__fmaf_rn(q, 0.25f, -2.0f), 0.0f);
-  const float q2 = __fsub_rn(q, __fadd_rn(a, b));
-  const float r = fminf(rintf(q2), 7.0f);
-  return (uint32_t)r;
+__device__ __forceinline__ float rcp_approx(float v) {
+  float r;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float min3(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 1.0f if v < 0 else 0.0f, on the multiply pipe: v * -inf is +inf, -inf or (for +-0) NaN, and the
+// saturating multiply maps those to 1, 0 and 0.  This is the reference's sign(x) < 0, for which
+// -0.0 counts as zero.
+__device__ __forceinline__ float is_negative(float v) {
+  float d;
+  asm("mul.sat.f32 %0, %1, 0fFF800000;" : "=f"(d) : "f"(v));
+  return d;
 }
 
-// Two fp32 -> one byte of two e2m1 nibbles, round-to-nearest-even, saturating.
-// `hi` lands in bits 7..4 and `lo` in bits 3..0.
-__device__ __forceinline__ uint32_t cvt_e2m1x2(float hi, float lo) {
-  uint16_t out;
-  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }"
-      : "=h"(out) : "f"(hi), "f"(lo));
-  return (uint32_t)out;
+#define METIS_ROUND_MAGIC 12582912.0f          /* 1.5 * 2^23: adding it leaves rint(v) in the low mantissa bits */
+
+// Index on the folded axis of the reference (quant.py:27-29): q = |x|/(s/2) in [0,12] is mapped
+// to [0,7] by halving the slope above 4 and quartering it above 8, i.e. the pointwise minimum of
+// the three lines q, q/2 + 2, q/4 + 4.  rint of it is the e2m1 magnitude code.
+//
+// With one rounding per line this reproduces the reference's op-by-op sequence
+//   q - (relu(q-4)/2 + relu(q-8)/4)
+// after rint for every q in [0, 12]: up to 4 both are q; on (4, 8] relu(q-4)/2 is exact, so the
+// reference's q - a is the single rounding of q/2 + 2; on (8, 32/3) both relu terms and their sum
+// are exact, so the result is the single rounding of q/4 + 4; from 32/3 on the sum may carry one
+// extra rounding of 2^-22, but there the index is at least 6.66 and rounds to 7 either way.
+__device__ __forceinline__ float folded_index(float q) {
+  return min3(q, __fmaf_rn(q, 0.5f, 2.0f), __fmaf_rn(q, 0.25f, 4.0f));
 }
 
-// Relative half-width of the band around a rounding boundary inside which the fast
-// reciprocal path is not trusted and the exact division is used instead.
-#define METIS_AMBIG_DELTA 1.9073486328125e-06f /* 2^-19 */
+// Correctly rounded a / h for 0 <= a <= 12.1 h from a refined reciprocal r of h: one
+// multiplication, the exact remainder and one correction (Markstein).  A remainder that
+// underflows only occurs for quotients far below the first rounding boundary.
+__device__ __forceinline__ float refine_reciprocal(float h) {
+  const float r = rcp_approx(h);
+  return __fmaf_rn(__fmaf_rn(-h, r, 1.0f), r, r);
+}
+__device__ __forceinline__ float divide_exact(float a, float h, float r) {
+  const float q0 = __fmul_rn(a, r);
+  return __fmaf_rn(__fmaf_rn(-h, q0, a), r, q0);
+}
 
-// Round-to-nearest codes of 8 consecutive values that share the block scale `s`.
-// Returns 4 bytes (element 0 in the low nibble of byte 0).  Fast path: multiply by
-// (1/s)(1 -+ delta) and convert both with the hardware e2m1 conversion; if the two results
-// agree no rounding boundary lies in between, and because the reference's own boundary sits
-// within a few ulps of the ideal one the result equals the reference's.  Otherwise every
-// element is redone with the exact division sequence.
-__device__ __forceinline__ uint32_t quantize8_rn(const float (&x)[8], float s) {
-  const float r = __frcp_rn(s);
-  const float rlo = r * (1.0f - METIS_AMBIG_DELTA);
-  const float rhi = r * (1.0f + METIS_AMBIG_DELTA);
-  uint32_t lo = 0, hi = 0;
+// Round-to-nearest codes of kGroups*8 consecutive values sharing the block scale `s`
+// (kGroups = 1: half a block, 2: a whole block); out[g] holds elements 8g..8g+7, element 0 in
+// the low nibble.  Every element goes through the reference's own arithmetic: the correctly
+// rounded quotient |x|/(s/2), the folded index, round half to even (adding the rounding magic
+// leaves the integer in the low mantissa bits).  There is no approximate fast path because with
+// bf16 inputs exact ties (an element equal to amax/8, 5/24 amax, ...) are common.  The integer
+// codes are summed into nibbles with shifted adds (the magic's own bits are subtracted once at the
+// end); the sign bits, 0/1 floats from a saturating multiply, are summed with multiply-adds.
+template <int kGroups>
+__device__ __forceinline__ void quantize_rn(const float (&x)[8 * kGroups], float s, uint32_t (&out)[kGroups]) {
+  const float h = 0.5f * s;
+  const float r = refine_reciprocal(h);
+  const uint32_t magic_sum = 0x4B400000u * 0x11111111u;   // sum over i of magic bits << 4i, mod 2^32
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    // fma with +0 turns an input of -0.0 into +0.0 (the reference's sign(x) is 0 there)
-    // while keeping the sign of every non-zero input, however small.
-    lo |= cvt_e2m1x2(__fmaf_rn(x[2 * i + 1], rlo, 0.0f), __fmaf_rn(x[2 * i], rlo, 0.0f)) << (8 * i);
-    hi |= cvt_e2m1x2(__fmaf_rn(x[2 * i + 1], rhi, 0.0f), __fmaf_rn(x[2 * i], rhi, 0.0f)) << (8 * i);
-  }
-  if (lo != hi) {
-    const float half_s = 0.5f * s;
-    lo = 0;
+  for (int g = 0; g < kGroups; ++g) {
+    uint32_t acc = 0;
+    float sign_lo = 0.0f, sign_hi = 0.0f;      // 16 bits each, exact in fp32
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const uint32_t mag = e2m1_code_exact(fabsf(x[i]), half_s);
-      const uint32_t nib = mag | (x[i] < 0.0f ? 8u : 0u);
-      lo |= nib << (4 * i);
+      const float v = x[8 * g + i];
+      const float m = folded_index(divide_exact(fabsf(v), h, r));
+      acc += __float_as_uint(__fadd_rn(m, METIS_ROUND_MAGIC)) << (4 * i);
+      const float neg = is_negative(v);
+      if (i < 4) sign_lo = __fmaf_rn(neg, (float)(8u << (4 * i)), sign_lo);
+      else       sign_hi = __fmaf_rn(neg, (float)(8u << (4 * (i - 4))), sign_hi);
     }
+    const uint32_t slo = __float_as_uint(sign_lo + 8388608.0f) & 0xFFFFu;   // 2^23: integer in the low bits
+    const uint32_t shi = __float_as_uint(sign_hi + 8388608.0f) << 16;
+    out[g] = (acc - magic_sum) | slo | shi;
   }
-  return lo;
+}
+
+__device__ __forceinline__ uint32_t quantize8_rn(const float (&x)[8], float s) {
+  uint32_t out[1];
+  quantize_rn<1>(x, s, out);
+  return out[0];
 }
 
 // ---- Philox4x32-10 ---------------------------------------------------------------------------------
@@ -162,25 +202,29 @@ struct Philox {
   }
 };
 
-// Stochastic-rounding codes of 8 values sharing scale s: fold |x|/(s/2) onto the index
-// axis, add u in (-0.5, 0.5) built from 16 random bits, round (quant.py:139-147).
-__device__ __forceinline__ uint32_t quantize8_sr(const float (&x)[8], float s, uint4 rnd) {
-  const float inv_half = __fdividef(2.0f, s);
+// Stochastic-rounding codes of 8 values sharing scale s: the folded index plus u in (-0.5, 0.5)
+// built from 16 random bits, rounded to nearest and clamped to [0, 7] (quant.py:139-147).
+__device__ __forceinline__ uint32_t quantize8_sr(const float* x, float s, uint4 rnd) {
+  const float two_over_s = 2.0f * rcp_approx(s);     // no exactness needed here: checked in distribution
   const uint32_t rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
-  uint32_t out = 0;
+  const uint32_t magic_sum = 0x4B400000u * 0x11111111u;
+  uint32_t acc = 0;
+  float sign_lo = 0.0f, sign_hi = 0.0f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float q = fabsf(x[i]) * inv_half;
-    const float a = fmaxf(__fmaf_rn(q, 0.5f, -2.0f), 0.0f);
-    const float b = fmaxf(__fmaf_rn(q, 0.25f, -2.0f), 0.0f);
-    float q2 = q - (a + b);
-    const uint32_t bits = (rw[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
-    const float u = ((float)bits + 0.5f) * (1.0f / 65536.0f) - 0.5f;
-    q2 = fminf(fmaxf(rintf(q2 + u), 0.0f), 7.0f);
-    const uint32_t nib = (uint32_t)q2 | (x[i] < 0.0f ? 8u : 0u);
-    out |= nib << (4 * i);
+    const float m = folded_index(fabsf(x[i]) * two_over_s);
+    // 16 bits -> [1, 2) by filling the top of the mantissa, then to (-0.5, 0.5)
+    const uint32_t bits = (i & 1) ? (rw[i >> 1] >> 16) : (rw[i >> 1] & 0xFFFFu);
+    const float u = __uint_as_float(0x3F800000u | (bits << 7)) - (1.5f - 0.5f / 65536.0f);
+    const float q = fminf(fmaxf(m + u, 0.0f), 7.0f);
+    acc += __float_as_uint(q + METIS_ROUND_MAGIC) << (4 * i);
+    const float neg = is_negative(x[i]);
+    if (i < 4) sign_lo = __fmaf_rn(neg, (float)(8u << (4 * i)), sign_lo);
+    else       sign_hi = __fmaf_rn(neg, (float)(8u << (4 * (i - 4))), sign_hi);
   }
-  return out;
+  const uint32_t slo = __float_as_uint(sign_lo + 8388608.0f) & 0xFFFFu;
+  const uint32_t shi = __float_as_uint(sign_hi + 8388608.0f) << 16;
+  return (acc - magic_sum) | slo | shi;
 }
 
 // ---- loads ------------------------------------------------------------------------------------------------

@@ -20,69 +20,73 @@ __device__ __forceinline__ void fold_global_max(unsigned int* gmax, float local)
   // amax >= 0, so the IEEE bit pattern orders like the value.
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, o));
-  if ((threadIdx.x & 31) == 0 && local > 0.0f) atomicMax(gmax, __float_as_uint(local));
+  const unsigned tid = threadIdx.y * blockDim.x + threadIdx.x;
+  if ((tid & 31u) == 0 && local > 0.0f) atomicMax(gmax, __float_as_uint(local));
 }
 
 // ---- pass 1, row-major ------------------------------------------------------------------------
-// One thread owns 8 consecutive elements (one 128-bit load for bf16); two neighbouring
-// lanes form a 16-element block and exchange their maxima with one shuffle.  Each thread
-// stores 4 code bytes; the even lane stores the block maximum.
+// One thread owns one 16-element block (two 128-bit loads for bf16): no cross-lane traffic, one
+// 64-bit store of codes and one 32-bit store of the block maximum, both coalesced across the warp.
+// Thread (tx, ty) of a bx x by CTA walks the rows ty, ty + by*gridDim.y, ... of its fixed column
+// block, so there is no division in the loop and the column means stay in registers.
+template <typename T> struct Load16;
+template <> struct Load16<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[16]) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[2 * i] = bf16_lo(w[i]); v[2 * i + 1] = bf16_hi(w[i]); }
+  }
+};
+template <> struct Load16<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(p) + i);
+      v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
+    }
+  }
+};
+
 template <typename T, bool kMean, bool kSR>
 __global__ void __launch_bounds__(kQuantThreads)
-quantize_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int64_t ld,
                      const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
-                     uint32_t* __restrict__ codes, float* __restrict__ amax_out,
+                     uint2* __restrict__ codes, float* __restrict__ amax_out,
                      unsigned int* __restrict__ gmax) {
-  const int64_t chunks_per_row = cols >> 3;
-  const int64_t total = rows * chunks_per_row;
-  const int64_t stride = (int64_t)gridDim.x * kQuantThreads;
+  const int bc = blockIdx.x * blockDim.x + threadIdx.x;     // column block of this thread
+  const int row_step = gridDim.y * blockDim.y;
   float running = 0.0f;
-  const bool flat = (ld == cols) && !kMean;
-  const Philox rng(seed);
-  // total is even (cols % 16 == 0) and stride is even, so both lanes of a pair always run
-  // the same number of iterations; the loop bound is rounded up to keep whole warps inside.
-  const int64_t total_w = (total + 31) & ~(int64_t)31;
-  for (int64_t c = (int64_t)blockIdx.x * kQuantThreads + threadIdx.x; c < total_w; c += stride) {
-    const bool live = c < total;
-    float v[8];
-    int64_t col = 0;
-    if (live) {
-      int64_t src;
-      if (flat) {
-        src = c << 3;
-      } else {
-        const int64_t r = c / chunks_per_row;
-        col = (c - r * chunks_per_row) << 3;
-        src = r * ld + col;
-      }
-      Load8<T>::load(x + src, v);
+  if (bc < blocks_per_row) {
+    float m[16];
+    if (kMean) Load16<float>::load(col_mean + (int64_t)bc * 16, m);
+    const Philox rng(seed);
+    for (int r = blockIdx.y * blockDim.y + threadIdx.y; r < rows; r += row_step) {
+      float v[16];
+      Load16<T>::load(x + (int64_t)r * ld + (int64_t)bc * 16, v);
       if (kMean) {
-        float m[8];
-        Load8<float>::load(col_mean + col, m);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = __fsub_rn(v[i], m[i]);
+        for (int i = 0; i < 16; ++i) v[i] = __fsub_rn(v[i], m[i]);
       }
-    } else {
+      float a = 0.0f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+      for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(v[i]));
+      const float s = block_scale_from_amax(a);
+      const int64_t b = (int64_t)r * blocks_per_row + bc;
+      uint32_t packed[2];
+      if (kSR) {
+        packed[0] = quantize8_sr(v, s, rng((uint64_t)b * 2, offset));
+        packed[1] = quantize8_sr(v + 8, s, rng((uint64_t)b * 2 + 1, offset));
+      } else {
+        quantize_rn<2>(v, s, packed);
+      }
+      codes[b] = make_uint2(packed[0], packed[1]);
+      amax_out[b] = a;
+      running = fmaxf(running, a);
     }
-    float a = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) a = fmaxf(a, fabsf(v[i]));
-    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-    const float s = block_scale_from_amax(a);
-    uint32_t packed;
-    if (kSR) {
-      packed = quantize8_sr(v, s, rng((uint64_t)c, offset));
-    } else {
-      packed = quantize8_rn(v, s);
-    }
-    if (live) {
-      codes[c] = packed;
-      if ((c & 1) == 0) amax_out[c >> 1] = a;
-    }
-    running = fmaxf(running, a);
   }
+  // whole warps reach this point together: a warp never spans the bc bound unevenly in y
   fold_global_max(gmax, running);
 }
 
@@ -304,15 +308,20 @@ template <typename T>
 static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
                         uint64_t seed, uint64_t offset, uint32_t* codes, const WorkspaceView& ws,
                         cudaStream_t st) {
-  const int64_t total = rows * (cols >> 3);
-  int64_t blocks = ceil_div(total, (int64_t)kQuantThreads * 4);   // ~4 chunks per thread
-  const int64_t cap = (int64_t)sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;
-  const dim3 g((unsigned)blocks), b(kQuantThreads);
-#define METIS_LAUNCH_ROWS(MEAN, SR)                                                          \
-  quantize_rows_kernel<T, MEAN, SR><<<g, b, 0, st>>>(x, rows, cols, ld, mean, seed, offset,  \
-                                                     codes, ws.amax, ws.gmax)
+  const int bpr = (int)(cols >> 4);
+  int bx = 1;                                      // threads along the row: a power of two <= 256
+  while (bx < bpr && bx < kQuantThreads) bx <<= 1;
+  const int by = kQuantThreads / bx;
+  const int gx = (bpr + bx - 1) / bx;
+  int64_t gy = ceil_div(rows, by);
+  const int64_t cap = ceil_div((int64_t)sm_count() * 16, gx);   // ~16 CTAs per SM in total
+  if (gy > cap) gy = cap;
+  if (gy > 65535) gy = 65535;
+  if (gy < 1) gy = 1;
+  const dim3 g((unsigned)gx, (unsigned)gy), b((unsigned)bx, (unsigned)by);
+#define METIS_LAUNCH_ROWS(MEAN, SR)                                                              \
+  quantize_rows_kernel<T, MEAN, SR><<<g, b, 0, st>>>(x, (int)rows, bpr, ld, mean, seed, offset,  \
+                                                     reinterpret_cast<uint2*>(codes), ws.amax, ws.gmax)
   if (mean) { if (sr) METIS_LAUNCH_ROWS(true, true); else METIS_LAUNCH_ROWS(true, false); }
   else      { if (sr) METIS_LAUNCH_ROWS(false, true); else METIS_LAUNCH_ROWS(false, false); }
 #undef METIS_LAUNCH_ROWS
@@ -407,7 +416,7 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   if (cols % need != 0 || ld % need != 0 || !aligned16(x))
     return fail(METIS_ERR_BAD_ALIGNMENT, "x must be 16-byte aligned with cols and ld multiples of %lld", (long long)need);
   if (col_mean && !aligned16(col_mean)) return fail(METIS_ERR_BAD_ALIGNMENT, "col_mean must be 16-byte aligned");
-  if (R * (C / 16) >= ((int64_t)1 << 40)) return fail(METIS_ERR_TOO_LARGE, "tensor too large");
+  if (rows >= ((int64_t)1 << 31) || cols >= ((int64_t)1 << 31)) return fail(METIS_ERR_TOO_LARGE, "tensor too large");
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const WorkspaceView ws = view_workspace(workspace);

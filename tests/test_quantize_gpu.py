@@ -85,6 +85,27 @@ def test_mean_subtraction_matches_oracle(transpose, dtype):
         assert_packed_equal(q, x.float().numpy(), cabi.SF_ROWMAJOR, mean=mean.numpy(), what="row mean")
 
 
+def test_bf16_inputs_sitting_exactly_on_rounding_ties():
+    # With bf16 data an element is often an exact fraction of the block maximum that lands on a
+    # rounding boundary of the reference (x = amax/8 gives |x|/(s/2) = 1.5 up to the rounding of
+    # amax/6); the answer then hangs on the reference's exact division.  Every block here holds its
+    # maximum plus the boundary ratios and their bf16 neighbours.
+    g = torch.Generator().manual_seed(7)
+    amax = (torch.rand(20480, 1, generator=g) * 8 + 0.01).to(torch.bfloat16).float() * (2.0 ** torch.randint(-6, 6, (20480, 1), generator=g))
+    ratios = torch.tensor([1 / 24, 1 / 8, 5 / 24, 7 / 24, 5 / 12, 7 / 12, 5 / 6])
+    near = (amax * ratios).to(torch.bfloat16)                       # [blocks, 7], rounded to bf16
+    up = (near.view(torch.int16) + 1).view(torch.bfloat16)
+    down = (near.view(torch.int16) - 1).view(torch.bfloat16)
+    sign = torch.where(torch.rand(20480, 16, generator=g) < 0.5, -1.0, 1.0)
+    x = torch.cat([amax.to(torch.bfloat16), near, up[:, :4], down[:, :4]], dim=1) * sign.to(torch.bfloat16)
+    x = x.reshape(-1, 64 * 16)                                       # 64 blocks per row
+    for layout in (cabi.SF_ROWMAJOR,):
+        q = ops.nvfp4_quantize(x.to(DEV), sf_layout=layout)
+        assert_packed_equal(q, x.float().numpy(), layout, what="ties")
+    qt = ops.nvfp4_quantize(x.t().contiguous().to(DEV), transpose=True, sf_layout=cabi.SF_ROWMAJOR)
+    assert_packed_equal(qt, x.float().numpy(), cabi.SF_ROWMAJOR, what="ties, transposed")
+
+
 def test_strided_rows():
     wide = synthetic(100, 512, "normal", seed=9, dtype=torch.bfloat16).to(DEV)
     view = wide[:, 128:384]                 # leading dimension 512, 256 columns
