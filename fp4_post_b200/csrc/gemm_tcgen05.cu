@@ -26,7 +26,7 @@ constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kSfaCol = 448;         // tensor-memory columns [448,464): scales of A for one stage
 constexpr int kSfbCol = 464;         // tensor-memory columns [464,496): scales of B for one stage
-constexpr uint32_t kSpinLimit = 4u << 20;
+constexpr uint64_t kWaitLimitNs = 400ull * 1000 * 1000;   // every device-side wait gives up after 0.4 s
 
 // debug knob carried in metis_gemm_args.reserved: the producer arms the first stage's barrier
 // for the scale bytes of A but never issues that copy, so the consumer's bounded wait expires.
@@ -34,7 +34,11 @@ constexpr int kDebugDropFirstSfa = 1;
 
 template <int BN> struct GemmCfg {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kAccStages = (BN == 256) ? 1 : 2;
+  // Two accumulators.  256 + 256 columns do not fit beside the scale columns, so for BN = 256 the
+  // second one starts at column 192: columns [192,256) belong to both.  The epilogue drains those
+  // columns first and then lets the next tile's MMAs start while it drains the rest.
+  static constexpr int kAccStride = (BN == 256) ? 192 : BN;
+  static constexpr int kSharedChunks = (BN == 256) ? 2 : 0;     // 32-column chunks in the overlap
   static constexpr int kABytes = kBM * kBKBytes;                   // 16 KiB
   static constexpr int kBBytes = BN * kBKBytes;                    // 16 or 32 KiB
   static constexpr int kSfaBytes = 4 * 512;                        // 4 scale tiles (256 elements)
@@ -78,14 +82,29 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within the limit or another role aborted.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  // may suspend the thread in hardware for up to the hinted time (ns) before it answers
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(2000u) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false if the phase did not complete within kWaitLimitNs or another role aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 32) __nanosleep(64);
-    if ((i & 255u) == 255u && *abort_flag) return false;
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if ((i & 15u) == 0) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitLimitNs) return false;
+    }
   }
-  return false;
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {
@@ -169,17 +188,16 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                   const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int kStages = Cfg::kStages;
-  constexpr int kAccStages = Cfg::kAccStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
   uint64_t* full = bars;                                   // [kStages]  TMA bytes landed
   uint64_t* empty = bars + kStages;                        // [kStages]  MMAs finished reading the stage
-  uint64_t* acc_full = bars + 2 * kStages;                 // [kAccStages] accumulator complete
-  uint64_t* acc_empty = bars + 2 * kStages + kAccStages;   // [kAccStages] accumulator drained
-  uint64_t* drain = bars + 2 * kStages + 2 * kAccStages;   // error path only
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccStages + 1);
+  uint64_t* acc_full = bars + 2 * kStages;                 // accumulator of the current tile complete
+  uint64_t* acc_release = bars + 2 * kStages + 1;          // columns the next tile needs are drained
+  uint64_t* drain = bars + 2 * kStages + 2;                // error path only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -196,7 +214,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < kAccStages; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_release, 4);
     mbar_init(drain, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -261,18 +280,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
+      uint32_t local_tile = 0;
       bool ok = true;
       bool issued = false;
-      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag)) {
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        // Tile j may start once the epilogue of tile j-1 has drained the columns the two
+        // accumulators share (release number j-1, i.e. phase parity (j-1)&1).  That also covers
+        // tile j-2, whose accumulator this one reuses: the epilogue finished it before it began j-1.
+        if (local_tile > 0 && !mbar_wait(acc_release, (local_tile - 1u) & 1u, abort_flag)) {
           report(p.status, abort_flag, METIS_DEV_TIMEOUT_EPI);
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t d_tmem = tmem_base + (local_tile & 1u) * Cfg::kAccStride;
         for (int it = 0; it < iters; ++it) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             report(p.status, abort_flag, METIS_DEV_TIMEOUT_TMA);
@@ -315,35 +336,47 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(&acc_full[acc]);           // accumulator complete
-        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
+        tc_commit(acc_full);                 // accumulator complete
       }
       if (!ok && issued) {
         // error path: let the tensor core finish what was issued before tensor memory is freed
         tc_commit(drain);
-        for (uint32_t i = 0; i < kSpinLimit && !mbar_test(drain, 0); ++i) __nanosleep(64);
+        const uint64_t t0 = global_ns();
+        while (!mbar_try(drain, 0) && global_ns() - t0 < kWaitLimitNs) {}
       }
     }
   } else {
     // ===== epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 =====
     const int q = warp & 3;
     const float g = p.alpha * __ldg(p.a_unit) * __ldg(p.b_unit);
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    uint32_t local_tile = 0;
+    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
       const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
       const int64_t row = tm * kBM + q * 32 + lane;
       const int64_t n0 = tn * BN;
-      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) {
+      if (!mbar_wait(acc_full, local_tile & 1u, abort_flag)) {
         if (lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_MMA);
         break;
       }
       tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      const uint32_t odd = local_tile & 1u;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + odd * Cfg::kAccStride;
+      // chunk order: the columns shared with the other accumulator first.  For the even
+      // accumulator [0,256) they are its last two chunks, for the odd one [192,448) its first two.
+      constexpr int kChunks = BN / 32;
+      const int first_chunk = (Cfg::kSharedChunks > 0 && !odd) ? kChunks - Cfg::kSharedChunks : 0;
       const float c0 = p.rvec0 ? (p.cvec0 ? (row < p.M ? __ldg(p.cvec0 + row) : 0.f) : 1.0f) : 0.0f;
       const float c1 = p.rvec1 ? (p.cvec1 ? (row < p.M ? __ldg(p.cvec1 + row) : 0.f) : 1.0f) : 0.0f;
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
+      for (int step = 0; step < kChunks; ++step) {
+        int ch = first_chunk + step;
+        if (ch >= kChunks) ch -= kChunks;
+        if (step == Cfg::kSharedChunks) {
+          // everything the next tile's accumulator overlaps has been read out of tensor memory
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_release);
+        }
         uint32_t r[32];
         tc_load32(t_row + ch * 32, r);
         tc_wait_ld();
@@ -406,10 +439,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
-      if (++acc == kAccStages) { acc = 0; acc_phase ^= 1u; }
     }
   }
 
