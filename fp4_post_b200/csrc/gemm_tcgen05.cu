@@ -121,20 +121,25 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tc_copy_scales(uint32_t taddr, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+// Descriptors are passed as two 32-bit halves: only the low half (the address field) changes
+// from stage to stage, so the issuing thread advances it with one 32-bit add.
+__device__ __forceinline__ void tc_copy_scales(uint32_t taddr, uint32_t desc_lo, uint32_t desc_hi) {
+  asm volatile("{ .reg .b64 d; mov.b64 d, {%1, %2}; tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d; }"
+               ::"r"(taddr), "r"(desc_lo), "r"(desc_hi) : "memory");
 }
-__device__ __forceinline__ void tc_mma_fp4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t acc) {
+__device__ __forceinline__ void tc_mma_fp4(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                           uint32_t sfa, uint32_t sfb, uint32_t acc) {
   asm volatile(
-      "{ .reg .pred p; setp.ne.b32 p, %6, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p; }"
-      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc) : "memory");
+      "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %7, 0; mov.b64 da, {%1, %3}; mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p; }"
+      ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc) : "memory");
 }
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                            uint32_t acc) {
   asm volatile(
-      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
-      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+      "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %5, 0; mov.b64 da, {%1, %3}; mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p; }"
+      ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc) : "memory");
 }
 __device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -153,15 +158,12 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 // >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in [46,48), swizzle
 // mode in [61,64) (0 none, 2 = 128-byte).
 // K-major operand tile stored as rows of 128 bytes, 128-byte swizzled: groups of 8 rows are
-// 1024 bytes apart.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
+// 1024 bytes apart (stride field 64), leading field 1, version 1, swizzle mode 2.
+constexpr uint32_t kOperandDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t operand_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
 // One 512-byte scale tile: 32 rows of 16 bytes, not swizzled; groups of 8 rows are 128 bytes apart.
-__device__ __forceinline__ uint64_t scale_tile_desc(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-}
+constexpr uint32_t kScaleDescHi = (128u >> 4) | (1u << 14);
+__device__ __forceinline__ uint32_t scale_desc_lo(uint32_t saddr) { return (saddr & 0x3FFFFu) >> 4; }
 
 // Instruction descriptors (32-bit): formats of A [7,10) and B [10,13), N>>3 in [17,23),
 // M>>4 in [24,29); both operands K-major.
@@ -240,30 +242,32 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
         const int32_t m0 = (int32_t)(tm * kBM), n0 = (int32_t)(tn * BN);
+        // scale tiles: 4 per stage (2 KiB) and per 128 rows, contiguous along K; those of B exist
+        // only for whole 128-row blocks of N
+        const uint8_t* sfa_src = p.a_scales + ((int64_t)m0 >> 7) * sf_tiles_a * 512;
+        const int64_t rb0 = (int64_t)n0 >> 7;
+        const uint8_t* sfb_src = p.b_scales + rb0 * sf_tiles_a * 512;
+        int sfb_blocks = 0;
+        for (int b = 0; b < BN / 128; ++b) sfb_blocks += (rb0 + b < b_row_blocks) ? 1 : 0;
+        const uint32_t k_bytes = Cfg::kABytes + Cfg::kBBytes + Cfg::kSfaBytes + sfb_blocks * 2048;
         for (int it = 0; it < iters; ++it) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
             report(p.status, abort_flag, METIS_DEV_TIMEOUT_MMA);
             ok = false;
             break;
           }
-          uint8_t* st = smem + stage * Cfg::kStageBytes;
-          uint8_t* sa = st;
-          uint8_t* sb = st + Cfg::kABytes;
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
           uint8_t* ssfa = sb + Cfg::kBBytes;
           uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
           if (it < k_iters) {
-            // scale tiles of B exist only for whole 128-row blocks of N
-            const int64_t rb0 = (int64_t)n0 >> 7;
-            int sfb_blocks = 0;
-            for (int b = 0; b < BN / 128; ++b) sfb_blocks += (rb0 + b < b_row_blocks) ? 1 : 0;
-            mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes + Cfg::kSfaBytes + sfb_blocks * 2048);
+            mbar_expect_tx(&full[stage], k_bytes);
             tma_load_2d(sa, &map_a, it * kBKBytes, m0, &full[stage]);
             tma_load_2d(sb, &map_b, it * kBKBytes, n0, &full[stage]);
             const bool drop = first && (p.debug & kDebugDropFirstSfa);
-            if (!drop)
-              bulk_load(ssfa, p.a_scales + (((int64_t)m0 >> 7) * sf_tiles_a + (int64_t)it * 4) * 512, 2048, &full[stage]);
+            if (!drop) bulk_load(ssfa, sfa_src + (int64_t)it * 2048, 2048, &full[stage]);
             for (int b = 0; b < sfb_blocks; ++b)
-              bulk_load(ssfb + b * 2048, p.b_scales + ((rb0 + b) * sf_tiles_a + (int64_t)it * 4) * 512, 2048, &full[stage]);
+              bulk_load(ssfb + b * 2048, sfb_src + (b * sf_tiles_a + (int64_t)it * 4) * 512, 2048, &full[stage]);
             first = false;
           } else {
             const int j = it - k_iters;   // 64-column panel of the rank-r factors
@@ -283,6 +287,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t local_tile = 0;
       bool ok = true;
       bool issued = false;
+      const uint32_t stage0_lo = operand_desc_lo(smem_u32(smem));
+      uint32_t stage_lo = stage0_lo;
+      const uint32_t t_sfa = tmem_base + kSfaCol, t_sfb = tmem_base + kSfbCol;
       for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
         // Tile j may start once the epilogue of tile j-1 has drained the columns the two
         // accumulators share (release number j-1, i.e. phase parity (j-1)&1).  That also covers
@@ -301,39 +308,37 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             break;
           }
           tc_fence_after();
-          uint8_t* st = smem + stage * Cfg::kStageBytes;
-          const uint32_t sa = smem_u32(st);
-          const uint32_t sb = sa + Cfg::kABytes;
-          const uint32_t ssfa = sb + Cfg::kBBytes;
-          const uint32_t ssfb = ssfa + Cfg::kSfaBytes;
+          // descriptor address fields (16-byte units) of this stage's A, B and scale tiles
+          const uint32_t a_lo = stage_lo;
+          const uint32_t b_lo = stage_lo + (Cfg::kABytes >> 4);
+          const uint32_t sfa_lo = b_lo + (Cfg::kBBytes >> 4) - (1u << 16);    // scale descriptors carry no leading field
+          const uint32_t sfb_lo = sfa_lo + (Cfg::kSfaBytes >> 4);
           if (it < k_iters) {
             // scale tile j of this stage serves MMA j: 4 tensor-memory columns per 128 rows
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              tc_copy_scales(tmem_base + kSfaCol + 4 * j, scale_tile_desc(ssfa + j * 512));
+              tc_copy_scales(t_sfa + 4 * j, sfa_lo + j * 32, kScaleDescHi);
 #pragma unroll
               for (int b = 0; b < BN / 128; ++b)
-                tc_copy_scales(tmem_base + kSfbCol + (BN / 128) * 4 * j + 4 * b,
-                               scale_tile_desc(ssfb + b * 2048 + j * 512));
+                tc_copy_scales(t_sfb + (BN / 128) * 4 * j + 4 * b, sfb_lo + b * 128 + j * 32, kScaleDescHi);
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              // 64 elements of K = 32 bytes inside the 128-byte swizzled row
-              tc_mma_fp4(d_tmem, operand_desc(sa + j * 32), operand_desc(sb + j * 32), idesc_fp4(BN),
-                         tmem_base + kSfaCol + 4 * j, tmem_base + kSfbCol + (BN / 128) * 4 * j,
-                         (it > 0 || j > 0) ? 1u : 0u);
+              // 64 elements of K = 32 bytes (2 units) inside the 128-byte swizzled row
+              tc_mma_fp4(d_tmem, a_lo + 2 * j, b_lo + 2 * j, kOperandDescHi, idesc_fp4(BN), t_sfa + 4 * j,
+                         t_sfb + (BN / 128) * 4 * j, (it > 0 || j > 0) ? 1u : 0u);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               // 16 bf16 of the rank dimension = 32 bytes
-              tc_mma_bf16(d_tmem, operand_desc(sa + j * 32), operand_desc(sb + j * 32), idesc_bf16(BN),
-                          (it > 0 || j > 0) ? 1u : 0u);
+              tc_mma_bf16(d_tmem, a_lo + 2 * j, b_lo + 2 * j, kOperandDescHi, idesc_bf16(BN), (it > 0 || j > 0) ? 1u : 0u);
             }
           }
           issued = true;
           tc_commit(&empty[stage]);          // frees the stage once these MMAs have read it
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          stage_lo += Cfg::kStageBytes >> 4;
+          if (++stage == kStages) { stage = 0; phase ^= 1u; stage_lo = stage0_lo; }
         }
         if (!ok) break;
         tc_commit(acc_full);                 // accumulator complete
