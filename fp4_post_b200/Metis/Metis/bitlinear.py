@@ -444,7 +444,17 @@ class LinearLowbitFunction(torch.autograd.Function):
         return grad_input, grad_weight, grad_bias, None, None
 
 
-def _packed_backward(da: PackedOperand, xa: PackedOperand, wq: PackedOperand, M: int, N: int, K: int):
+def _row_sums(q):
+    """Row sums of the quantized matrix, computed once per tensor (the activation's are needed by
+    both weight-gradient products of a fused layer)."""
+    cached = getattr(q, "_row_sums", None)
+    if cached is None:
+        cached = ops.nvfp4_gemv(q)
+        q._row_sums = cached
+    return cached
+
+
+def _packed_backward(da: PackedOperand, xa: PackedOperand, wq: PackedOperand, M: int, N: int, K: int, addend=None):
     """dX = D^ @ W^ and dW = D^T @ x^ on the FP4 GEMM (bitlinear.py:502-508), where
     D^ = 1 mu_D^T + Q(D - mu_D) and x^ = 1 mu_x^T + Q(x - mu_x).
 
@@ -457,16 +467,16 @@ def _packed_backward(da: PackedOperand, xa: PackedOperand, wq: PackedOperand, M:
     rank1 = []
     if da.mean is not None:
         rank1.append((None, ops.nvfp4_gemv(w_t, da.mean)))
-    grad_input = _packed_matmul(da.q, w_t, rank1=rank1, out_dtype=out_dtype)
+    grad_input = _packed_matmul(da.q, w_t, rank1=rank1, c=addend, out_dtype=out_dtype)   # (+ addend) in the epilogue
 
     d_t = da.transposed()                                   # [N, M], col_vec = mu_D
     x_t = xa.transposed()                                   # [K, M], col_vec = mu_x
     rank1 = []
     mu_x, mu_d = x_t.col_vec, d_t.col_vec
     if mu_x is not None:
-        rank1.append((ops.nvfp4_gemv(d_t), mu_x))
+        rank1.append((_row_sums(d_t), mu_x))
     if mu_d is not None:
-        tail = ops.nvfp4_gemv(x_t)
+        tail = _row_sums(x_t)
         if mu_x is not None:
             tail = tail + float(M) * mu_x
         rank1.append((mu_d, tail))
@@ -598,8 +608,8 @@ class MetisFusedFunction(torch.autograd.Function):
         gx_v, grad_v = _packed_backward(dv, xa, vq, M, r, K)
         # warmup_linear (the residual): quantized backward with grad_output = g
         dg = F._pack_centred(g, quantizer, centred)
-        gx_r, grad_r = _packed_backward(dg, xa, rq, M, N, K)
-        grad_x = (gx_v + gx_r).reshape(xa.shape)
+        gx, grad_r = _packed_backward(dg, xa, rq, M, N, K, addend=gx_v)      # dX of both branches summed in the epilogue
+        grad_x = gx.reshape(xa.shape)
         return grad_x, None, grad_v, None, grad_s, grad_u, grad_r, None, grad_bias
 
 

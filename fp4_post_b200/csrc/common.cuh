@@ -249,6 +249,27 @@ template <> struct Load8<float> {
   }
 };
 
+// 16 consecutive elements (one quantization block) starting at p, 16-byte aligned.
+template <typename T> struct Load16;
+template <> struct Load16<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[16]) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[2 * i] = bf16_lo(w[i]); v[2 * i + 1] = bf16_hi(w[i]); }
+  }
+};
+template <> struct Load16<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(p) + i);
+      v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
+    }
+  }
+};
+
 #endif  // __CUDACC__
 
 }  // namespace metis

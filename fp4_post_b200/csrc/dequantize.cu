@@ -51,35 +51,58 @@ dequantize_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict_
   }
 }
 
-// out[r] = sum_c v[c] * value(Q[r][c]).  One warp per row; a lane walks chunks of 8 elements.
-// Per block of 16 the inner sum of v * e2m1 is formed first, then scaled once.
+// out[r] = sum_c v[c] * value(Q[r][c]).  One warp per row; per step a lane takes one block (16
+// elements: one 64-bit load of codes, one scale byte), so a warp reads 512 consecutive elements and
+// the matching stretch of v with 128-bit loads.  Twice the e2m1 magnitude comes from a nibble table
+// held in one 32-bit constant; a block's partial sum is formed in integers (v == NULL) or with one
+// multiply-add per element, then scaled once.
+__device__ __forceinline__ int twice_e2m1(uint32_t nib) {
+  const int mag = (int)((0xC8643210u >> ((nib & 7u) * 4u)) & 15u);     // {0,1,2,3,4,6,8,12}
+  return (nib & 8u) ? -mag : mag;
+}
+
+template <bool kHasV>
 __global__ void __launch_bounds__(256)
-gemv_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+gemv_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
             const float* __restrict__ unit_ptr, int32_t sf_layout, int64_t R, int64_t C,
             const float* __restrict__ v, float* __restrict__ out) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= R) return;
-  const int64_t chunks_per_row = C >> 3;
-  const int64_t sf_cols = C >> 4;
+  const int64_t sf_cols = C >> 4;               // blocks per row
   const int64_t tiles = sf_tiles_per_row(C);
+  const uint2* row_codes = codes + row * sf_cols;
   float acc = 0.0f;
-  for (int64_t ch = lane; ch < chunks_per_row; ch += 32) {
-    const uint32_t w = __ldg(codes + row * chunks_per_row + ch);
-    const float sc = scale_at(scales, sf_layout, row, ch >> 1, sf_cols, tiles);
-    float part = 0.0f;
+#pragma unroll 4
+  for (int64_t k = lane; k < sf_cols; k += 32) {
+    const uint2 w2 = __ldg(row_codes + k);
+    const int64_t off = (sf_layout == METIS_SF_MMA) ? sf_mma_offset(row, k, tiles) : row * sf_cols + k;
+    const float sc = e4m3_to_float(__ldg(scales + off));
+    const uint32_t w[2] = {w2.x, w2.y};
+    float part;
+    if (kHasV) {
+      part = 0.0f;
+      const float4* v4 = reinterpret_cast<const float4*>(v + k * 16);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t nib = (w >> (4 * i)) & 15u;
-      float val = e2m1_value(nib & 7u);
-      if (nib & 8u) val = -val;
-      part = fmaf(val, v ? __ldg(v + ch * 8 + i) : 1.0f, part);
+      for (int j = 0; j < 4; ++j) {
+        const float4 f = __ldg(v4 + j);
+        const uint32_t n4 = w[j >> 1] >> (16 * (j & 1));
+        part = fmaf((float)twice_e2m1(n4), f.x, part);
+        part = fmaf((float)twice_e2m1(n4 >> 4), f.y, part);
+        part = fmaf((float)twice_e2m1(n4 >> 8), f.z, part);
+        part = fmaf((float)twice_e2m1(n4 >> 12), f.w, part);
+      }
+    } else {
+      int isum = 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) isum += twice_e2m1(w[i >> 3] >> (4 * (i & 7)));
+      part = (float)isum;
     }
     acc = fmaf(part, sc, acc);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) out[row] = acc * __ldg(unit_ptr);
+  if (lane == 0) out[row] = acc * (0.5f * __ldg(unit_ptr));
 }
 
 }  // namespace metis
@@ -117,8 +140,11 @@ extern "C" int32_t metis_nvfp4_gemv(const uint8_t* codes, const uint8_t* scales,
   if (R <= 0 || C <= 0 || C % 16 != 0) return fail(METIS_ERR_BAD_SHAPE, "bad shape [%lld, %lld]", (long long)R, (long long)C);
   if (sf_layout != METIS_SF_ROWMAJOR && sf_layout != METIS_SF_MMA) return fail(METIS_ERR_BAD_ARGUMENT, "unknown sf_layout %d", sf_layout);
   if (!aligned16(codes)) return fail(METIS_ERR_BAD_ALIGNMENT, "codes must be 16-byte aligned");
+  if (v && !aligned16(v)) return fail(METIS_ERR_BAD_ALIGNMENT, "v must be 16-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  gemv_kernel<<<(unsigned)ceil_div(R, 8), 256, 0, st>>>(reinterpret_cast<const uint32_t*>(codes), scales, unit, sf_layout, R, C, v, out);
+  const uint2* c4 = reinterpret_cast<const uint2*>(codes);
+  if (v) gemv_kernel<true><<<(unsigned)ceil_div(R, 8), 256, 0, st>>>(c4, scales, unit, sf_layout, R, C, v, out);
+  else   gemv_kernel<false><<<(unsigned)ceil_div(R, 8), 256, 0, st>>>(c4, scales, unit, sf_layout, R, C, v, out);
   METIS_CUDA_OK(cudaGetLastError());
   return METIS_OK;
 }

@@ -8,6 +8,7 @@
 // touches 1/16 of the elements: it turns the block maxima into E4M3 bytes in the layout the
 // consumer wants and publishes the per-tensor unit.
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <mutex>
 
@@ -29,26 +30,6 @@ __device__ __forceinline__ void fold_global_max(unsigned int* gmax, float local)
 // 64-bit store of codes and one 32-bit store of the block maximum, both coalesced across the warp.
 // Thread (tx, ty) of a bx x by CTA walks the rows ty, ty + by*gridDim.y, ... of its fixed column
 // block, so there is no division in the loop and the column means stay in registers.
-template <typename T> struct Load16;
-template <> struct Load16<__nv_bfloat16> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[16]) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
-    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { v[2 * i] = bf16_lo(w[i]); v[2 * i + 1] = bf16_hi(w[i]); }
-  }
-};
-template <> struct Load16<float> {
-  static __device__ __forceinline__ void load(const float* p, float (&v)[16]) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 a = __ldg(reinterpret_cast<const float4*>(p) + i);
-      v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
-    }
-  }
-};
-
 template <typename T, bool kMean, bool kSR>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int64_t ld,
@@ -91,107 +72,128 @@ quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int6
 }
 
 // ---- pass 1, transposed ---------------------------------------------------------------------------
-// Output Q = quantize(x^T): blocks of 16 run along the rows of x.  A CTA owns a tile of
-// kTileRows x kTileCols of x.  A thread loads 16 rows x kCpt columns (kCpt columns = one
-// 128-bit load), so it holds kCpt complete blocks, one per column.  Codes and maxima are
-// staged in shared memory and written out as contiguous runs along the output rows.
+// Output Q = quantize(x^T): blocks of 16 run along the rows of x.  A CTA walks tiles of 256 rows x
+// 128 bytes of x (64 bf16 or 32 fp32 columns).  One thread issues the TMA load of the next tile
+// into the other shared-memory stage while all threads work on the current one: a thread reads a
+// column block (16 rows of one column) from shared memory -- consecutive lanes read consecutive
+// columns, so the reads are conflict free -- quantizes it exactly like a row block, and parks 8 code
+// bytes and one maximum in a staging area from which whole 128-byte runs of the output rows are
+// written.  A tile load that does not arrive within the wait limit raises the error word of the
+// workspace header (the scale pass then publishes NaN as the unit) instead of hanging.
 template <typename T> struct TransposeTile {
-  static constexpr int kCpt = 16 / sizeof(T);          // columns per thread (8 bf16, 4 fp32)
-  static constexpr int kColGroups = 8;                   // threads along the columns
-  static constexpr int kRowGroups = kQuantThreads / kColGroups;  // 32 groups of 16 rows
-  static constexpr int kTileCols = kCpt * kColGroups;    // 64 (bf16) or 32 (fp32)
-  static constexpr int kTileRows = 16 * kRowGroups;      // 512
+  static constexpr int kCols = 128 / sizeof(T);           // 64 (bf16) or 32 (fp32): 128 bytes per row
+  static constexpr int kRows = 256;
+  static constexpr int kRowBlocks = kRows / 16;           // 16
+  static constexpr int kUnits = kCols * kRowBlocks / kQuantThreads;   // column blocks per thread: 4 or 2
+  static constexpr int kStageBytes = kRows * 128;         // 32 KiB
+  static constexpr int kCodePitch = kRows / 2 + 8;        // staged code bytes per output row (+8: bank spread)
+  static constexpr int kSmemBytes = 2 * kStageBytes + kCols * kCodePitch + kCols * kRowBlocks * 4 + 64 + 128;
 };
 
 template <typename T, bool kMean, bool kSR>
 __global__ void __launch_bounds__(kQuantThreads)
-quantize_cols_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
+quantize_cols_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, int64_t cols,
                      const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
                      uint8_t* __restrict__ codes, float* __restrict__ amax_out,
                      unsigned int* __restrict__ gmax) {
   using TT = TransposeTile<T>;
-  constexpr int kCpt = TT::kCpt;
-  // +16 bytes of padding per staged row keeps the 8-byte stores of a warp off the same banks
-  __shared__ __align__(16) uint8_t s_codes[TT::kTileCols][TT::kTileRows / 2 + 16];
-  __shared__ float s_amax[TT::kTileCols][TT::kRowGroups + 1];
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+  uint8_t* s_codes = smem + 2 * TT::kStageBytes;                               // [kCols][kCodePitch]
+  float* s_amax = reinterpret_cast<float*>(s_codes + TT::kCols * TT::kCodePitch);   // [kCols][kRowBlocks]
+  uint64_t* full = reinterpret_cast<uint64_t*>(s_amax + TT::kCols * TT::kRowBlocks);   // [2]
+  __shared__ int s_failed;
 
-  const int cg = threadIdx.x % TT::kColGroups;
-  const int rg = threadIdx.x / TT::kColGroups;
-  const int64_t col0 = (int64_t)blockIdx.x * TT::kTileCols + cg * kCpt;
-  const int64_t row_tiles = (rows + TT::kTileRows - 1) / TT::kTileRows;
+  const int tid = threadIdx.x;
+  const int64_t row_tiles = (rows + TT::kRows - 1) / TT::kRows;
+  const int64_t col_tiles = (cols + TT::kCols - 1) / TT::kCols;
+  const int64_t tiles = row_tiles * col_tiles;      // tile id = column tile * row_tiles + row tile
+
+  if (tid == 0) {
+    mbar_init(&full[0], 1);
+    mbar_init(&full[1], 1);
+    s_failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](int64_t tile, int stage) {
+    const int64_t ct = tile / row_tiles, rt = tile - ct * row_tiles;
+    mbar_expect_tx(&full[stage], TT::kStageBytes);
+    tma_load_2d(smem + stage * TT::kStageBytes, &map_x, (int32_t)(ct * TT::kCols), (int32_t)(rt * TT::kRows), &full[stage]);
+  };
+
+  const int c = tid % TT::kCols;                    // column of this thread inside the tile
+  const int rb0 = tid / TT::kCols;                  // its first row block; the others follow every kQuantThreads/kCols
   const Philox rng(seed);
   float running = 0.0f;
+  int stage = 0;
+  uint32_t phases = 0;                              // bit s: parity to wait for on full[s]
+  int64_t tile = blockIdx.x;
+  if (tid == 0 && tile < tiles) issue(tile, 0);
 
-  for (int64_t rt = blockIdx.y; rt < row_tiles; rt += gridDim.y) {
-    const int64_t row0 = rt * TT::kTileRows + rg * 16;
-    const bool live = (row0 < rows) && (col0 < cols);   // rows % 16 == 0, cols % kCpt == 0
-    float v[16][kCpt];
-    if (live) {
-#pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        const T* p = x + (row0 + r) * ld + col0;
-        if constexpr (sizeof(T) == 2) {
-          const uint4 w = __ldg(reinterpret_cast<const uint4*>(p));
-          v[r][0] = bf16_lo(w.x); v[r][1] = bf16_hi(w.x); v[r][2] = bf16_lo(w.y); v[r][3] = bf16_hi(w.y);
-          v[r][4] = bf16_lo(w.z); v[r][5] = bf16_hi(w.z); v[r][6] = bf16_lo(w.w); v[r][7] = bf16_hi(w.w);
-        } else {
-          const float4 w = __ldg(reinterpret_cast<const float4*>(p));
-          v[r][0] = w.x; v[r][1] = w.y; v[r][2] = w.z; v[r][3] = w.w;
-        }
-      }
+  for (; tile < tiles; tile += gridDim.x) {
+    const int64_t next = tile + gridDim.x;
+    if (tid == 0 && next < tiles) issue(next, stage ^ 1);     // that stage was released by the barrier below
+    volatile int* failed = &s_failed;
+    if (!mbar_wait(&full[stage], (phases >> stage) & 1u, failed)) {
+      *failed = 1;
     }
+    phases ^= 1u << stage;
+    if (*failed) break;                                       // uniform: every thread sees the same barrier outcome or flag
+
+    const int64_t ct = tile / row_tiles, rt = tile - ct * row_tiles;
+    const int64_t out_row = ct * TT::kCols + c;               // row of Q = column of x
+    const int64_t row0 = rt * TT::kRows;
+    const bool col_live = out_row < cols;
+    const float m = (kMean && col_live) ? __ldg(col_mean + out_row) : 0.0f;
+    const T* tile_smem = reinterpret_cast<const T*>(smem + stage * TT::kStageBytes);
 #pragma unroll
-    for (int j = 0; j < kCpt; ++j) {
-      float blk[2][8];
+    for (int u = 0; u < TT::kUnits; ++u) {
+      const int rb = rb0 + u * (kQuantThreads / TT::kCols);
+      float v[16];
       float a = 0.0f;
-      float m = 0.0f;
-      if (kMean && live) m = __ldg(col_mean + col0 + j);
 #pragma unroll
       for (int r = 0; r < 16; ++r) {
-        float e = live ? v[r][j] : 0.0f;
+        float e = (float)tile_smem[(rb * 16 + r) * TT::kCols + c];
         if (kMean) e = __fsub_rn(e, m);
-        blk[r >> 3][r & 7] = e;
+        v[r] = e;
         a = fmaxf(a, fabsf(e));
       }
       const float s = block_scale_from_amax(a);
-      uint32_t p0, p1;
+      uint32_t packed[2];
       if (kSR) {
-        // one counter per 8 output elements: output row (col0+j), output column row0 (+8)
-        const uint64_t e0 = (uint64_t)(col0 + j) * (uint64_t)rows + (uint64_t)row0;
-        p0 = quantize8_sr(blk[0], s, rng(e0 >> 3, offset));
-        p1 = quantize8_sr(blk[1], s, rng((e0 >> 3) + 1, offset));
+        // one counter per 8 output elements: output row out_row, output column row0 + 16 rb (+8)
+        const uint64_t e0 = ((uint64_t)out_row * (uint64_t)rows + (uint64_t)(row0 + rb * 16)) >> 3;
+        packed[0] = quantize8_sr(v, s, rng(e0, offset));
+        packed[1] = quantize8_sr(v + 8, s, rng(e0 + 1, offset));
       } else {
-        p0 = quantize8_rn(blk[0], s);
-        p1 = quantize8_rn(blk[1], s);
+        quantize_rn<2>(v, s, packed);
       }
-      *reinterpret_cast<uint2*>(&s_codes[cg * kCpt + j][rg * 8]) = make_uint2(p0, p1);
-      s_amax[cg * kCpt + j][rg] = a;
-      running = fmaxf(running, a);
+      *reinterpret_cast<uint2*>(s_codes + c * TT::kCodePitch + rb * 8) = make_uint2(packed[0], packed[1]);
+      s_amax[c * TT::kRowBlocks + rb] = a;
+      if (col_live && row0 + rb * 16 < rows) running = fmaxf(running, a);
     }
     __syncthreads();
-    // write-out: tile column c (an output row) owns kTileRows/2 = 256 code bytes and
-    // kRowGroups = 32 maxima, both contiguous in the output.
-    const int64_t tile_row0 = rt * TT::kTileRows;
-    const int64_t valid_rows = min((int64_t)TT::kTileRows, rows - tile_row0);  // multiple of 16
-    const int code_bytes = (int)(valid_rows >> 1);                              // multiple of 8
-    for (int i = threadIdx.x; i < TT::kTileCols * (TT::kTileRows / 2 / 8); i += kQuantThreads) {
-      const int c = i / (TT::kTileRows / 2 / 8);
-      const int b = (i % (TT::kTileRows / 2 / 8)) * 8;
-      const int64_t oc = (int64_t)blockIdx.x * TT::kTileCols + c;
-      if (oc < cols && b < code_bytes) {
-        const uint2 w = *reinterpret_cast<const uint2*>(&s_codes[c][b]);
-        *reinterpret_cast<uint2*>(codes + oc * (rows >> 1) + (tile_row0 >> 1) + b) = w;
-      }
+    // write-out: output row (tile column) j owns kRows/2 = 128 contiguous code bytes and 16 maxima
+    const int64_t valid_rows = min((int64_t)TT::kRows, rows - row0);            // multiple of 16
+    for (int i = tid; i < TT::kCols * 16; i += kQuantThreads) {                 // 8-byte pieces: 16 per output row
+      const int j = i >> 4, piece = i & 15;
+      const int64_t orow = ct * TT::kCols + j;
+      if (orow < cols && piece * 16 < valid_rows)
+        *reinterpret_cast<uint2*>(codes + orow * (rows >> 1) + (row0 >> 1) + piece * 8) =
+            *reinterpret_cast<const uint2*>(s_codes + j * TT::kCodePitch + piece * 8);
     }
-    for (int i = threadIdx.x; i < TT::kTileCols * TT::kRowGroups; i += kQuantThreads) {
-      const int c = i / TT::kRowGroups;
-      const int g = i % TT::kRowGroups;
-      const int64_t oc = (int64_t)blockIdx.x * TT::kTileCols + c;
-      if (oc < cols && g * 16 < valid_rows)
-        amax_out[oc * (rows >> 4) + (tile_row0 >> 4) + g] = s_amax[c][g];
+    for (int i = tid; i < TT::kCols * TT::kRowBlocks; i += kQuantThreads) {
+      const int j = i / TT::kRowBlocks, g = i % TT::kRowBlocks;
+      const int64_t orow = ct * TT::kCols + j;
+      if (orow < cols && g * 16 < valid_rows) amax_out[orow * (rows >> 4) + (row0 >> 4) + g] = s_amax[j * TT::kRowBlocks + g];
     }
-    __syncthreads();
+    __syncthreads();          // staging and this tile's stage may be overwritten from here on
+    stage ^= 1;
   }
+  if (s_failed && tid == 0) gmax[1] = 1u;           // error word of the workspace header
   fold_global_max(gmax, running);
 }
 
@@ -203,7 +205,8 @@ finalize_scales_kernel(const float* __restrict__ amax, const unsigned int* __res
                        int64_t R, int64_t sf_cols, int32_t sf_layout, uint8_t* __restrict__ scales,
                        float* __restrict__ unit_out) {
   const float smax = block_scale_from_amax(__uint_as_float(*gmax));
-  const float unit = __fdiv_rn(smax, 448.0f);           // quant.py:21-22
+  // quant.py:21-22; a pass-1 kernel that gave up on a load raises gmax[1]: publish NaN so that it shows
+  const float unit = gmax[1] ? __uint_as_float(0x7FC00000u) : __fdiv_rn(smax, 448.0f);
   if (blockIdx.x == 0 && threadIdx.x == 0) *unit_out = unit;
   const int64_t elem_cols = sf_cols * 16;
   const int64_t tiles = sf_tiles_per_row(elem_cols);
@@ -328,23 +331,28 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
 }
 
 template <typename T>
-static void launch_cols(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
-                        uint64_t seed, uint64_t offset, uint8_t* codes, const WorkspaceView& ws,
-                        cudaStream_t st) {
+static int32_t launch_cols(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
+                           uint64_t seed, uint64_t offset, uint8_t* codes, const WorkspaceView& ws,
+                           cudaStream_t st) {
   using TT = TransposeTile<T>;
-  const int64_t col_tiles = ceil_div(cols, TT::kTileCols);
-  const int64_t row_tiles = ceil_div(rows, TT::kTileRows);
-  int64_t gy = ceil_div((int64_t)sm_count() * 4, col_tiles);
-  if (gy > row_tiles) gy = row_tiles;
-  if (gy < 1) gy = 1;
-  if (gy > 65535) gy = 65535;
-  const dim3 g((unsigned)col_tiles, (unsigned)gy), b(kQuantThreads);
-#define METIS_LAUNCH_COLS(MEAN, SR)                                                          \
-  quantize_cols_kernel<T, MEAN, SR><<<g, b, 0, st>>>(x, rows, cols, ld, mean, seed, offset,  \
-                                                     codes, ws.amax, ws.gmax)
+  CUtensorMap map;
+  const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  if (int32_t rc = make_map(&map, dt, sizeof(T), x, cols, rows, ld * (int64_t)sizeof(T), TT::kCols, TT::kRows, "x", false))
+    return rc;
+  const int64_t tiles = ceil_div(cols, TT::kCols) * ceil_div(rows, TT::kRows);
+  int64_t grid = (int64_t)sm_count() * 2;          // two CTAs of ~78 KiB per SM
+  if (grid > tiles) grid = tiles;
+#define METIS_LAUNCH_COLS(MEAN, SR)                                                                         \
+  do {                                                                                                      \
+    auto kern = quantize_cols_kernel<T, MEAN, SR>;                                                          \
+    METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TT::kSmemBytes)); \
+    kern<<<(unsigned)grid, kQuantThreads, TT::kSmemBytes, st>>>(map, rows, cols, mean, seed, offset, codes,  \
+                                                                ws.amax, ws.gmax);                          \
+  } while (0)
   if (mean) { if (sr) METIS_LAUNCH_COLS(true, true); else METIS_LAUNCH_COLS(true, false); }
   else      { if (sr) METIS_LAUNCH_COLS(false, true); else METIS_LAUNCH_COLS(false, false); }
 #undef METIS_LAUNCH_COLS
+  return METIS_OK;
 }
 
 int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t sf_layout,
@@ -420,7 +428,7 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const WorkspaceView ws = view_workspace(workspace);
-  METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, sizeof(unsigned int), st));
+  METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, 2 * sizeof(unsigned int), st));   // running maximum and error word
   if (!transpose) {
     if (x_dtype == METIS_DTYPE_BF16)
       launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset,
@@ -429,10 +437,10 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
       launch_rows(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset,
                   reinterpret_cast<uint32_t*>(codes), ws, st);
   } else {
-    if (x_dtype == METIS_DTYPE_BF16)
-      launch_cols(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, codes, ws, st);
-    else
-      launch_cols(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, codes, ws, st);
+    const int32_t rc = x_dtype == METIS_DTYPE_BF16
+        ? launch_cols(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, codes, ws, st)
+        : launch_cols(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, codes, ws, st);
+    if (rc) return rc;
   }
   METIS_CUDA_OK(cudaGetLastError());
   return launch_finalize(ws, R, C, sf_layout, scales, unit, st);
@@ -529,9 +537,9 @@ extern "C" int32_t metis_nvfp4_quantize_static(const void* x, int32_t x_dtype, i
   if (int32_t rc = static_scratch_address(&scratch)) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const WorkspaceView ws = view_workspace(scratch);
-  // The array keeps whatever the previous call left.  Only the running maximum has to start at
-  // zero; every block maximum this call reads back is written by this call first.
-  METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, sizeof(unsigned int), st));
+  // The array keeps whatever the previous call left.  Only the running maximum and the error word
+  // have to start at zero; every block maximum this call reads back is written by this call first.
+  METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, 2 * sizeof(unsigned int), st));   // running maximum and error word
   if (x_dtype == METIS_DTYPE_BF16)
     launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, nullptr, false, 0, 0, reinterpret_cast<uint32_t*>(codes), ws, st);
   else

@@ -11,87 +11,100 @@ namespace metis {
 
 constexpr int kNormThreads = 256;
 
-template <typename TX, typename TG, int kChunks, bool kWriteNorm>
+// Rounds two floats to bf16 and back (one packed conversion).
+__device__ __forceinline__ void round_bf16x2(float& a, float& b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+  a = bf16_lo(w);
+  b = bf16_hi(w);
+}
+
+// A CTA is bx x by threads: bx threads (a power of two) share a row, each owning kBlocks
+// 16-element blocks tx, tx + bx, ...; by rows are in flight per CTA.  Row sums of squares are
+// reduced with shuffles inside a warp and through shared memory across the warps of a row.
+template <typename TX, typename TG, int kBlocks, bool kWriteNorm>
 __global__ void __launch_bounds__(kNormThreads)
-rmsnorm_quantize_kernel(const TX* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
-                        const TG* __restrict__ gamma, float eps, uint32_t* __restrict__ codes,
+rmsnorm_quantize_kernel(const TX* __restrict__ x, int rows, int blocks_per_row, int64_t ld,
+                        const TG* __restrict__ gamma, float eps, uint2* __restrict__ codes,
                         float* __restrict__ amax_out, unsigned int* __restrict__ gmax,
                         void* __restrict__ norm_out) {
   // The product normalised(x) * gamma has the promoted dtype: bf16 only if both are bf16.
   constexpr bool kProductBf16 = (sizeof(TX) == 2) && (sizeof(TG) == 2);
   __shared__ float s_red[kNormThreads / 32];
-  const int chunks_per_row = (int)(cols >> 3);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const float inv_cols_den = (float)cols;
-
-  // gamma is the same for every row: keep it in registers
-  float g[kChunks][8];
-#pragma unroll
-  for (int j = 0; j < kChunks; ++j) {
-    const int ch = threadIdx.x + j * kNormThreads;
-    if (ch < chunks_per_row) Load8<TG>::load(gamma + (int64_t)ch * 8, g[j]);
-  }
-
+  const int bx = blockDim.x, by = blockDim.y;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int tid = ty * bx + tx;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int seg = bx < 32 ? bx : 32;                 // lanes of one row inside a warp
+  const int warps_per_row = bx >> 5;                 // 0 when a warp holds several rows
+  const float n_cols = (float)(blocks_per_row * 16);
   float running = 0.0f;
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-    float v[kChunks][8];
+
+  for (int r0 = blockIdx.x * by; r0 < rows; r0 += gridDim.x * by) {
+    const int r = r0 + ty;
+    const bool row_live = r < rows;
+    float v[kBlocks][16];
     float ss = 0.0f;
 #pragma unroll
-    for (int j = 0; j < kChunks; ++j) {
-      const int ch = threadIdx.x + j * kNormThreads;
-      if (ch < chunks_per_row) {
-        Load8<TX>::load(x + r * ld + (int64_t)ch * 8, v[j]);
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (row_live && bc < blocks_per_row) {
+        Load16<TX>::load(x + (int64_t)r * ld + (int64_t)bc * 16, v[j]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss = __fmaf_rn(v[j][i], v[j][i], ss);
+        for (int i = 0; i < 16; ++i) ss = __fmaf_rn(v[j][i], v[j][i], ss);
       }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (lane == 0) s_red[warp] = ss;
-    __syncthreads();
-    float tot = 0.0f;
-#pragma unroll
-    for (int w = 0; w < kNormThreads / 32; ++w) tot += s_red[w];
-    __syncthreads();   // s_red is rewritten by the next row
+    for (int o = seg >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    float tot = ss;
+    if (warps_per_row > 1) {                           // uniform over the CTA
+      if (lane == 0) s_red[warp] = ss;
+      __syncthreads();
+      tot = 0.0f;
+      for (int w = 0; w < warps_per_row; ++w) tot += s_red[ty * warps_per_row + w];
+      __syncthreads();                                 // s_red is rewritten by the next row
+    }
     // x * rsqrt(mean(x^2) + eps) with the IEEE operations the CPU reference uses:
     // correctly rounded division, square root and reciprocal (llama.py:23-24).
-    const float rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, inv_cols_den), eps)));
+    const float rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, n_cols), eps)));
 
 #pragma unroll
-    for (int j = 0; j < kChunks; ++j) {
-      const int ch = threadIdx.x + j * kNormThreads;
-      const bool live = ch < chunks_per_row;   // uniform over a lane pair (chunks_per_row is even)
-      float y[8];
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (!(row_live && bc < blocks_per_row)) continue;
+      float g[16];
+      Load16<TG>::load(gamma + (int64_t)bc * 16, g);
+      float y[16];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float n = live ? __fmul_rn(v[j][i], rs) : 0.0f;
-        if (sizeof(TX) == 2) n = __bfloat162float(__float2bfloat16_rn(n));   // .type_as(x), llama.py:28
-        float p = __fmul_rn(n, live ? g[j][i] : 0.0f);                       // * weight, llama.py:31
-        if (kProductBf16) p = __bfloat162float(__float2bfloat16_rn(p));
-        y[i] = p;
+      for (int i = 0; i < 16; i += 2) {
+        float n0 = __fmul_rn(v[j][i], rs), n1 = __fmul_rn(v[j][i + 1], rs);
+        if (sizeof(TX) == 2) round_bf16x2(n0, n1);                      // .type_as(x), llama.py:28
+        float p0 = __fmul_rn(n0, g[i]), p1 = __fmul_rn(n1, g[i + 1]);   // * weight, llama.py:31
+        if (kProductBf16) round_bf16x2(p0, p1);
+        y[i] = p0;
+        y[i + 1] = p1;
       }
       float a = 0.0f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) a = fmaxf(a, fabsf(y[i]));
-      a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-      const uint32_t packed = quantize8_rn(y, block_scale_from_amax(a));
-      if (live) {
-        const int64_t c = r * chunks_per_row + ch;
-        codes[c] = packed;
-        if ((ch & 1) == 0) amax_out[c >> 1] = a;
-        if (kWriteNorm) {
-          if (kProductBf16) {
-            __nv_bfloat162 o[4];
+      for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(y[i]));
+      uint32_t packed[2];
+      quantize_rn<2>(y, block_scale_from_amax(a), packed);
+      const int64_t b = (int64_t)r * blocks_per_row + bc;
+      codes[b] = make_uint2(packed[0], packed[1]);
+      amax_out[b] = a;
+      running = fmaxf(running, a);
+      if (kWriteNorm) {
+        if (kProductBf16) {
+          __nv_bfloat162 o[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
-            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(norm_out) + c * 8) = *reinterpret_cast<uint4*>(o);
-          } else {
-            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(norm_out) + c * 8);
-            dst[0] = make_float4(y[0], y[1], y[2], y[3]);
-            dst[1] = make_float4(y[4], y[5], y[6], y[7]);
-          }
+          for (int i = 0; i < 8; ++i) o[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);   // exact: already bf16 values
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(norm_out) + b * 16);
+          dst[0] = reinterpret_cast<uint4*>(o)[0];
+          dst[1] = reinterpret_cast<uint4*>(o)[1];
+        } else {
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(norm_out) + b * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
         }
-        running = fmaxf(running, a);
       }
     }
   }
@@ -100,30 +113,37 @@ rmsnorm_quantize_kernel(const TX* __restrict__ x, int64_t rows, int64_t cols, in
   if (lane == 0 && running > 0.0f) atomicMax(gmax, __float_as_uint(running));
 }
 
-template <typename TX, typename TG, int kChunks>
-static void launch_norm(const TX* x, int64_t rows, int64_t cols, int64_t ld, const TG* gamma, float eps,
+template <typename TX, typename TG, int kBlocks>
+static void launch_norm(const TX* x, int64_t rows, int bpr, int bx, int64_t ld, const TG* gamma, float eps,
                         uint32_t* codes, const WorkspaceView& ws, void* norm_out, int sms, cudaStream_t st) {
-  int64_t blocks = (int64_t)sms * (kChunks <= 2 ? 8 : (kChunks <= 4 ? 4 : 2));
-  if (blocks > rows) blocks = rows;
+  const int by = kNormThreads / bx;
+  int64_t blocks = (int64_t)sms * (kBlocks <= 1 ? 6 : (kBlocks <= 2 ? 4 : 2));
+  const int64_t need = ceil_div(rows, by);
+  if (blocks > need) blocks = need;
+  const dim3 b((unsigned)bx, (unsigned)by);
+  uint2* c2 = reinterpret_cast<uint2*>(codes);
   if (norm_out)
-    rmsnorm_quantize_kernel<TX, TG, kChunks, true><<<(unsigned)blocks, kNormThreads, 0, st>>>(
-        x, rows, cols, ld, gamma, eps, codes, ws.amax, ws.gmax, norm_out);
+    rmsnorm_quantize_kernel<TX, TG, kBlocks, true><<<(unsigned)blocks, b, 0, st>>>(
+        x, (int)rows, bpr, ld, gamma, eps, c2, ws.amax, ws.gmax, norm_out);
   else
-    rmsnorm_quantize_kernel<TX, TG, kChunks, false><<<(unsigned)blocks, kNormThreads, 0, st>>>(
-        x, rows, cols, ld, gamma, eps, codes, ws.amax, ws.gmax, norm_out);
+    rmsnorm_quantize_kernel<TX, TG, kBlocks, false><<<(unsigned)blocks, b, 0, st>>>(
+        x, (int)rows, bpr, ld, gamma, eps, c2, ws.amax, ws.gmax, norm_out);
 }
 
 template <typename TX, typename TG>
 static int32_t dispatch_chunks(const TX* x, int64_t rows, int64_t cols, int64_t ld, const TG* gamma,
                                float eps, uint32_t* codes, const WorkspaceView& ws, void* norm_out,
                                int sms, cudaStream_t st) {
-  const int64_t per_thread = ceil_div(cols >> 3, kNormThreads);
-  if (per_thread <= 1) launch_norm<TX, TG, 1>(x, rows, cols, ld, gamma, eps, codes, ws, norm_out, sms, st);
-  else if (per_thread <= 2) launch_norm<TX, TG, 2>(x, rows, cols, ld, gamma, eps, codes, ws, norm_out, sms, st);
-  else if (per_thread <= 4) launch_norm<TX, TG, 4>(x, rows, cols, ld, gamma, eps, codes, ws, norm_out, sms, st);
-  else if (per_thread <= 8) launch_norm<TX, TG, 8>(x, rows, cols, ld, gamma, eps, codes, ws, norm_out, sms, st);
-  else if (per_thread <= 12) launch_norm<TX, TG, 12>(x, rows, cols, ld, gamma, eps, codes, ws, norm_out, sms, st);
-  else return fail(METIS_ERR_TOO_LARGE, "rmsnorm rows longer than %d elements are not supported", 12 * kNormThreads * 8);
+  const int bpr = (int)(cols >> 4);
+  int bx = 1;
+  while (bx < bpr && bx < kNormThreads) bx <<= 1;
+  const int per_thread = (bpr + bx - 1) / bx;
+  if (per_thread <= 1) launch_norm<TX, TG, 1>(x, rows, bpr, bx, ld, gamma, eps, codes, ws, norm_out, sms, st);
+  else if (per_thread <= 2) launch_norm<TX, TG, 2>(x, rows, bpr, bx, ld, gamma, eps, codes, ws, norm_out, sms, st);
+  else if (per_thread <= 3) launch_norm<TX, TG, 3>(x, rows, bpr, bx, ld, gamma, eps, codes, ws, norm_out, sms, st);
+  else if (per_thread <= 5) launch_norm<TX, TG, 5>(x, rows, bpr, bx, ld, gamma, eps, codes, ws, norm_out, sms, st);
+  else if (per_thread <= 8) launch_norm<TX, TG, 8>(x, rows, bpr, bx, ld, gamma, eps, codes, ws, norm_out, sms, st);
+  else return fail(METIS_ERR_TOO_LARGE, "rmsnorm rows longer than %d elements are not supported", 8 * kNormThreads * 16);
   return METIS_OK;
 }
 
@@ -148,7 +168,7 @@ extern "C" int32_t metis_rmsnorm_nvfp4_quantize(const void* x, int32_t x_dtype, 
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const WorkspaceView ws = view_workspace(workspace);
-  METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, sizeof(unsigned int), st));
+  METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, 2 * sizeof(unsigned int), st));   // running maximum and error word
   const int sms = device_sm_count();
   uint32_t* c32 = reinterpret_cast<uint32_t*>(codes);
   int32_t rc;
