@@ -2,17 +2,20 @@
 //
 //   D[M,N] = g * ( sum_k A[m,k] B[n,k] + sum_j T[m,j] U[n,j] ) + rank-1 terms (+ C)
 //
-// One persistent CTA per SM, 192 threads in three roles:
+// One persistent CTA per SM, 320 threads in four roles:
 //   warp 0     TMA producer: per pipeline stage one 128 x 128-byte box of A codes, one
 //              BN x 128-byte box of B codes (both 128-byte swizzled) and the matching E4M3
 //              scale tiles (plain bulk copies: the scale layout makes them contiguous).
-//   warp 1     tensor-core issuer: copies the scale tiles shared memory -> tensor memory
-//              (tcgen05.cp), then issues four K=64 tcgen05.mma.kind::mxf4nvf4.block_scale per
-//              stage into the fp32 accumulator in tensor memory; the rank-r product runs as extra
+//   warp 1     tensor-core issuer: four K=64 tcgen05.mma.kind::mxf4nvf4.block_scale per stage
+//              into the fp32 accumulator in tensor memory; the rank-r product runs as extra
 //              pipeline iterations whose stages hold 64-column bf16 panels of T and U and are
 //              consumed by tcgen05.mma.kind::f16 into the same accumulator.
 //   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32 lanes), apply the
 //              scalar, the rank-1 terms and the optional addend, store bf16 or fp32.
+//   warps 6-9  scale movers: carry each stage's E4M3 scale tiles shared memory -> registers ->
+//              tensor memory (tcgen05.st, each warp its own 32 lanes: the four copies the
+//              block-scale layout wants).  A tcgen05.cp issued by warp 1 would do the same, but it
+//              runs in the MMA pipe and cost about as much time there as the MMAs themselves.
 // Hand-offs are mbarriers; every wait is bounded and reports through the status word.
 #include "common.cuh"
 #include "tma.cuh"
@@ -21,22 +24,28 @@ namespace metis {
 
 constexpr int kBM = 128;             // rows of A per tile (the MMA M)
 constexpr int kBKBytes = 128;        // bytes of packed codes per row per stage = 256 elements
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;     // producer, issuer, 4 epilogue warps, 4 scale-mover warps
 constexpr int kTmemCols = 512;
-constexpr int kSfaCol = 448;         // tensor-memory columns [448,464): scales of A for one stage
-constexpr int kSfbCol = 464;         // tensor-memory columns [464,496): scales of B for one stage
+// Scale columns in tensor memory: two buffers of 48 columns (16 for A, 32 for B), used by
+// alternate pipeline iterations so that the copy for one iteration never has to wait for the
+// MMAs of the previous one to finish reading.
+constexpr int kSfCol = 416;
+constexpr int kSfBufCols = 48;
 
 // debug knob carried in metis_gemm_args.reserved: the producer arms the first stage's barrier
 // for the scale bytes of A but never issues that copy, so the consumer's bounded wait expires.
 constexpr int kDebugDropFirstSfa = 1;
+// timing experiments (results are meaningless): issue no MMAs / request no data
+constexpr int kDebugNoMma = 2;
+constexpr int kDebugNoLoad = 4;
 
 template <int BN> struct GemmCfg {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   // Two accumulators.  256 + 256 columns do not fit beside the scale columns, so for BN = 256 the
-  // second one starts at column 192: columns [192,256) belong to both.  The epilogue drains those
+  // second one starts at column 160: columns [160,256) belong to both.  The epilogue drains those
   // columns first and then lets the next tile's MMAs start while it drains the rest.
-  static constexpr int kAccStride = (BN == 256) ? 192 : BN;
-  static constexpr int kSharedChunks = (BN == 256) ? 2 : 0;     // 32-column chunks in the overlap
+  static constexpr int kAccStride = (BN == 256) ? 160 : BN;
+  static constexpr int kSharedChunks = (BN == 256) ? 3 : 0;     // 32-column chunks in the overlap
   static constexpr int kABytes = kBM * kBKBytes;                   // 16 KiB
   static constexpr int kBBytes = BN * kBKBytes;                    // 16 or 32 KiB
   static constexpr int kSfaBytes = 4 * 512;                        // 4 scale tiles (256 elements)
@@ -68,12 +77,8 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Descriptors are passed as two 32-bit halves: only the low half (the address field) changes
-// from stage to stage, so the issuing thread advances it with one 32-bit add.
-__device__ __forceinline__ void tc_copy_scales(uint32_t taddr, uint32_t desc_lo, uint32_t desc_hi) {
-  asm volatile("{ .reg .b64 d; mov.b64 d, {%1, %2}; tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d; }"
-               ::"r"(taddr), "r"(desc_lo), "r"(desc_hi) : "memory");
-}
+// Operand descriptors are passed as two 32-bit halves: only the low half (the address field)
+// changes from stage to stage, so the issuing thread advances it with one 32-bit add.
 __device__ __forceinline__ void tc_mma_fp4(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
                                            uint32_t sfa, uint32_t sfb, uint32_t acc) {
   asm volatile(
@@ -99,6 +104,13 @@ __device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_store16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptors (64-bit): start address >> 4 in [0,14), leading byte offset
@@ -108,10 +120,6 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 // 1024 bytes apart (stride field 64), leading field 1, version 1, swizzle mode 2.
 constexpr uint32_t kOperandDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t operand_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
-// One 512-byte scale tile: 32 rows of 16 bytes, not swizzled; groups of 8 rows are 128 bytes apart.
-constexpr uint32_t kScaleDescHi = (128u >> 4) | (1u << 14);
-__device__ __forceinline__ uint32_t scale_desc_lo(uint32_t saddr) { return (saddr & 0x3FFFFu) >> 4; }
-
 // Instruction descriptors (32-bit): formats of A [7,10) and B [10,13), N>>3 in [17,23),
 // M>>4 in [24,29); both operands K-major.
 __host__ __device__ constexpr uint32_t idesc_fp4(int bn) {
@@ -146,7 +154,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint64_t* acc_full = bars + 2 * kStages;                 // accumulator of the current tile complete
   uint64_t* acc_release = bars + 2 * kStages + 1;          // columns the next tile needs are drained
   uint64_t* drain = bars + 2 * kStages + 2;                // error path only
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 3);
+  uint64_t* sf_ready = bars + 2 * kStages + 3;             // [2] scale buffer written by the four movers
+  uint64_t* sf_free = bars + 2 * kStages + 5;              // [2] MMAs that read the scale buffer are done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -165,6 +175,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(acc_full, 1);
     mbar_init(acc_release, 4);
+    for (int b = 0; b < 2; ++b) { mbar_init(&sf_ready[b], 4); mbar_init(&sf_free[b], 1); }
     mbar_init(drain, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -207,7 +218,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           uint8_t* sb = sa + Cfg::kABytes;
           uint8_t* ssfa = sb + Cfg::kBBytes;
           uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
-          if (it < k_iters) {
+          if (p.debug & kDebugNoLoad) {
+            mbar_arrive(&full[stage]);
+          } else if (it < k_iters) {
             mbar_expect_tx(&full[stage], k_bytes);
             tma_load_2d(sa, &map_a, it * kBKBytes, m0, &full[stage]);
             tma_load_2d(sb, &map_b, it * kBKBytes, n0, &full[stage]);
@@ -236,7 +249,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       bool issued = false;
       const uint32_t stage0_lo = operand_desc_lo(smem_u32(smem));
       uint32_t stage_lo = stage0_lo;
-      const uint32_t t_sfa = tmem_base + kSfaCol, t_sfb = tmem_base + kSfbCol;
+      uint32_t sf_buf = 0, sf_phase = 0;
       for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
         // Tile j may start once the epilogue of tile j-1 has drained the columns the two
         // accumulators share (release number j-1, i.e. phase parity (j-1)&1).  That also covers
@@ -258,17 +271,17 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           // descriptor address fields (16-byte units) of this stage's A, B and scale tiles
           const uint32_t a_lo = stage_lo;
           const uint32_t b_lo = stage_lo + (Cfg::kABytes >> 4);
-          const uint32_t sfa_lo = b_lo + (Cfg::kBBytes >> 4) - (1u << 16);    // scale descriptors carry no leading field
-          const uint32_t sfb_lo = sfa_lo + (Cfg::kSfaBytes >> 4);
-          if (it < k_iters) {
-            // scale tile j of this stage serves MMA j: 4 tensor-memory columns per 128 rows
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              tc_copy_scales(t_sfa + 4 * j, sfa_lo + j * 32, kScaleDescHi);
-#pragma unroll
-              for (int b = 0; b < BN / 128; ++b)
-                tc_copy_scales(t_sfb + (BN / 128) * 4 * j + 4 * b, sfb_lo + b * 128 + j * 32, kScaleDescHi);
+          if (p.debug & kDebugNoMma) {
+          } else if (it < k_iters) {
+            // the movers have put this iteration's scales into buffer sf_buf: 4 columns per MMA
+            // and 128 rows for A, then for B
+            const uint32_t t_sfa = tmem_base + kSfCol + sf_buf * kSfBufCols, t_sfb = t_sfa + 16;
+            if (!mbar_wait(&sf_ready[sf_buf], sf_phase, abort_flag)) {
+              report(p.status, abort_flag, METIS_DEV_TIMEOUT_TMA);
+              ok = false;
+              break;
             }
+            tc_fence_after();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               // 64 elements of K = 32 bytes (2 units) inside the 128-byte swizzled row
@@ -284,6 +297,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
           issued = true;
           tc_commit(&empty[stage]);          // frees the stage once these MMAs have read it
+          if (it < k_iters) {
+            tc_commit(&sf_free[sf_buf]);     // and the scale buffer
+            if ((sf_buf ^= 1u) == 0) sf_phase ^= 1u;
+          }
           stage_lo += Cfg::kStageBytes >> 4;
           if (++stage == kStages) { stage = 0; phase ^= 1u; stage_lo = stage0_lo; }
         }
@@ -297,6 +314,51 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         while (!mbar_try(drain, 0) && global_ns() - t0 < kWaitLimitNs) {}
       }
     }
+  } else if (warp >= 6) {
+    // ===== scale movers: warps 6..9 own tensor-memory lanes 32*(warp%4) .. +31 =====
+    // Lane l of every mover reads bytes [16 l, 16 l + 16) of a 512-byte scale tile: the scales of
+    // rows l, l+32, l+64, l+96 for 4 scale columns, i.e. exactly the 4 tensor-memory columns that
+    // lane l holds for that tile.
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    int stage = 0;
+    uint32_t phase = 0, sf_buf = 0, sf_phase = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int it = 0; it < iters; ++it) {
+        if (it < k_iters && !(p.debug & kDebugNoMma)) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          const uint4* sf = reinterpret_cast<const uint4*>(smem + stage * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes) + lane;
+          uint32_t ra[16], rb[(BN / 128) * 16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 w = sf[j * 32];                                  // tile j of A: 512 bytes = 32 uint4
+            ra[4 * j] = w.x; ra[4 * j + 1] = w.y; ra[4 * j + 2] = w.z; ra[4 * j + 3] = w.w;
+#pragma unroll
+            for (int b = 0; b < BN / 128; ++b) {                         // tile j of each 128-row block of B
+              const uint4 u = sf[(4 + b * 4 + j) * 32];
+              uint32_t* dst = rb + ((BN / 128) * 4 * j + 4 * b);
+              dst[0] = u.x; dst[1] = u.y; dst[2] = u.z; dst[3] = u.w;
+            }
+          }
+          if (!mbar_wait(&sf_free[sf_buf], sf_phase ^ 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t t_sfa = tmem_base + lane_base + kSfCol + sf_buf * kSfBufCols;
+          tc_store16(t_sfa, ra);
+#pragma unroll
+          for (int h = 0; h < BN / 128; ++h) {
+            const uint32_t (&half)[16] = *reinterpret_cast<const uint32_t (*)[16]>(rb + 16 * h);
+            tc_store16(t_sfa + 16 + 16 * h, half);
+          }
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sf_ready[sf_buf]);
+          if ((sf_buf ^= 1u) == 0) sf_phase ^= 1u;
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    if (!ok && lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_TMA);
   } else {
     // ===== epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 =====
     const int q = warp & 3;
@@ -314,7 +376,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint32_t odd = local_tile & 1u;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + odd * Cfg::kAccStride;
       // chunk order: the columns shared with the other accumulator first.  For the even
-      // accumulator [0,256) they are its last two chunks, for the odd one [192,448) its first two.
+      // accumulator [0,256) they are its last chunks, for the odd one [160,416) its first ones.
       constexpr int kChunks = BN / 32;
       const int first_chunk = (Cfg::kSharedChunks > 0 && !odd) ? kChunks - Cfg::kSharedChunks : 0;
       const float c0 = p.rvec0 ? (p.cvec0 ? (row < p.M ? __ldg(p.cvec0 + row) : 0.f) : 1.0f) : 0.0f;
@@ -443,7 +505,7 @@ extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
       return fail(METIS_ERR_BAD_ALIGNMENT, "lr_t and lr_u must be 16-byte aligned with leading dimensions that are multiples of 8");
   }
   if ((a->cvec0 && !a->rvec0) || (a->cvec1 && !a->rvec1)) return fail(METIS_ERR_BAD_ARGUMENT, "a cvec needs its rvec");
-  if (a->reserved & ~kDebugDropFirstSfa) return fail(METIS_ERR_BAD_ARGUMENT, "reserved must be 0");
+  if (a->reserved & ~(kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad)) return fail(METIS_ERR_BAD_ARGUMENT, "reserved must be 0");
 
   const int bn = (a->N > 128) ? 256 : 128;
   CUtensorMap ma, mb, mt, mu;
