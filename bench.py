@@ -72,7 +72,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -169,7 +169,7 @@ def workload_config(n_gpus):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     args = ap.parse_args()
@@ -250,9 +250,10 @@ def main():
             ms = float(t.item())
         return ms
 
-    for _ in range(warmup):
-        step(x_dev, g_dev)
     with ClockSampler(local) as clocks:
+        time.sleep(0.3)                            # let the sampler start before the GPU gets busy
+        for _ in range(warmup):
+            step(x_dev, g_dev)
         launches0 = ops.launch_count()
         ms_step = timed(lambda: step(x_dev, g_dev), args.steps)
         launches = ops.launch_count() - launches0

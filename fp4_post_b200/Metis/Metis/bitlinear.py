@@ -444,6 +444,17 @@ class LinearLowbitFunction(torch.autograd.Function):
         return grad_input, grad_weight, grad_bias, None, None
 
 
+_ONES = {}
+
+
+def _one(like: torch.Tensor) -> torch.Tensor:
+    """A cached fp32 1.0 on the device of `like`."""
+    t = _ONES.get(like.device)
+    if t is None:
+        t = _ONES[like.device] = torch.ones(1, dtype=torch.float32, device=like.device)
+    return t
+
+
 def _row_sums(q):
     """Row sums of the quantized matrix, computed once per tensor (the activation's are needed by
     both weight-gradient products of a fused layer)."""
@@ -454,21 +465,27 @@ def _row_sums(q):
     return cached
 
 
-def _packed_backward(da: PackedOperand, xa: PackedOperand, wq: PackedOperand, M: int, N: int, K: int, addend=None):
-    """dX = D^ @ W^ and dW = D^T @ x^ on the FP4 GEMM (bitlinear.py:502-508), where
-    D^ = 1 mu_D^T + Q(D - mu_D) and x^ = 1 mu_x^T + Q(x - mu_x).
-
-    dX contracts over N: A = Q(D) [M, N], B = W quantized along N ([K, N], transposed quantizer),
-    plus the row vector mu_D @ W^.  dW contracts over tokens: A = Q(D)^T [N, M], B = Q(x)^T [K, M]
-    (both from the transposed quantizer) plus the two rank-1 terms of the expansion
-      dW = Qd^T Qx + (Qd^T 1) mu_x^T + mu_D (Qx^T 1 + M mu_x)^T."""
-    out_dtype = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
+def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, side=None):
+    """dX = D^ @ W^ on the FP4 GEMM (bitlinear.py:508): contraction over N, so A = Q(D) [M, N] and
+    B = W quantized along N ([K, N], transposed quantizer), plus the row vector mu_D @ W^.
+    `side` = (T, U, row_vec) adds a bf16 rank-r product T @ U^T (in this product's accumulator
+    units) and another row vector in the same launch."""
     w_t = wq.transposed()                                   # [K, N]
-    rank1 = []
-    if da.mean is not None:
-        rank1.append((None, ops.nvfp4_gemv(w_t, da.mean)))
-    grad_input = _packed_matmul(da.q, w_t, rank1=rank1, c=addend, out_dtype=out_dtype)   # (+ addend) in the epilogue
+    row = ops.nvfp4_gemv(w_t, da.mean) if da.mean is not None else None
+    lowrank = None
+    if side is not None:
+        t_acc, u, extra = side
+        lowrank = (t_acc, u)
+        if extra is not None:
+            row = extra if row is None else row + extra
+    rank1 = [(None, row)] if row is not None else []
+    return _packed_matmul(da.q, w_t, rank1=rank1, lowrank=lowrank, c=addend, out_dtype=out_dtype)
 
+
+def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int):
+    """dW = D^T @ x^ on the FP4 GEMM (bitlinear.py:502-505), fp32: contraction over tokens, so
+    A = Q(D)^T [N, M] and B = Q(x)^T [K, M], both from the transposed quantizer, plus the two
+    rank-1 terms of  dW = Qd^T Qx + (Qd^T 1) mu_x^T + mu_D (Qx^T 1 + M mu_x)^T."""
     d_t = da.transposed()                                   # [N, M], col_vec = mu_D
     x_t = xa.transposed()                                   # [K, M], col_vec = mu_x
     rank1 = []
@@ -480,8 +497,14 @@ def _packed_backward(da: PackedOperand, xa: PackedOperand, wq: PackedOperand, M:
         if mu_x is not None:
             tail = tail + float(M) * mu_x
         rank1.append((mu_d, tail))
-    grad_weight = _packed_matmul(d_t, x_t, rank1=rank1, out_dtype=torch.float32)
-    return grad_input, grad_weight
+    return _packed_matmul(d_t, x_t, rank1=rank1, out_dtype=torch.float32)
+
+
+def _packed_backward(da: PackedOperand, xa: PackedOperand, wq: PackedOperand, M: int, N: int, K: int, addend=None):
+    """Both backward products of one quantized linear, with D^ = 1 mu_D^T + Q(D - mu_D) and
+    x^ = 1 mu_x^T + Q(x - mu_x)."""
+    out_dtype = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
+    return _packed_dx(da, wq, out_dtype, addend=addend), _packed_dw(da, xa, M)
 
 
 class LinearLowbit(torch.nn.Module):
@@ -560,6 +583,8 @@ class MetisFusedFunction(torch.autograd.Function):
     ulinear is a plain (unquantized) linear, vlinear and warmup_linear use the quantized
     backward of LinearLowbitFunction."""
 
+    fuse_dx_side_product = True      # bf16 only; False keeps the two dX products as separate launches
+
     @staticmethod
     def forward(ctx, x, xa: PackedOperand, v_weight, vq: PackedOperand, s, u_weight, r_weight,
                 rq: PackedOperand, bias):
@@ -603,12 +628,24 @@ class MetisFusedFunction(torch.autograd.Function):
         d_yv = d_ts * s.to(act)
         centred = F._backward_centred()
         quantizer = F.q_backward_outputgrad
-        # vlinear: quantized backward with grad_output = d_yv
+        # vlinear and warmup_linear (the residual): quantized backward with grad_output = d_yv and g
         dv = F._pack_centred(d_yv, quantizer, centred)
-        gx_v, grad_v = _packed_backward(dv, xa, vq, M, r, K)
-        # warmup_linear (the residual): quantized backward with grad_output = g
         dg = F._pack_centred(g, quantizer, centred)
-        gx, grad_r = _packed_backward(dg, xa, rq, M, N, K, addend=gx_v)      # dX of both branches summed in the epilogue
+        grad_v = _packed_dw(dv, xa, M)
+        grad_r = _packed_dw(dg, xa, M)
+        if MetisFusedFunction.fuse_dx_side_product and act == torch.bfloat16 and r <= 256:
+            # dX of both branches in ONE launch: D^v @ V^ enters the residual product as a bf16
+            # rank-r side product.  e2m1 x e4m3 is exact in bf16; the ratio of the two products'
+            # units goes into T, rounded once to bf16 (the unfused dX_v would be rounded there too).
+            v_t, r_t = vq.transposed(), rq.transposed()
+            ratio = (dv.q.unit * v_t.unit) / (dg.q.unit * r_t.unit)
+            t_acc = ops.nvfp4_dequantize(dv.q, torch.bfloat16, add_mean=False, unit=ratio)
+            u_side = ops.nvfp4_dequantize(v_t, torch.bfloat16, add_mean=False, unit=_one(v_t.unit))
+            extra = ops.nvfp4_gemv(v_t, dv.mean) if dv.mean is not None else None
+            gx = _packed_dx(dg, rq, act, side=(t_acc, u_side, extra))
+        else:
+            gx_v = _packed_dx(dv, vq, act)
+            gx = _packed_dx(dg, rq, act, addend=gx_v)          # summed in the epilogue
         grad_x = gx.reshape(xa.shape)
         return grad_x, None, grad_v, None, grad_s, grad_u, grad_r, None, grad_bias
 

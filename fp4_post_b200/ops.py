@@ -165,13 +165,16 @@ def rmsnorm_nvfp4_quantize(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e
     return (q, norm.reshape(x.shape)) if return_norm else q
 
 
-def nvfp4_dequantize(q: NVFP4Tensor, dtype: torch.dtype = torch.float32, add_mean: bool = True) -> torch.Tensor:
+def nvfp4_dequantize(q: NVFP4Tensor, dtype: torch.dtype = torch.float32, add_mean: bool = True,
+                     unit: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense [R, C] tensor of q.  `unit` (fp32 [1], device) replaces q's own unit, e.g. to express the
+    values in another product's accumulator units."""
     R, Cc = q.shape
     L = cabi.lib()
     with torch.cuda.device(q.device):
         out = torch.empty((R, Cc), dtype=dtype, device=q.device)
         rv = q.row_vec if add_mean else None
-        rc = L.metis_nvfp4_dequantize(q.codes.data_ptr(), q.scales.data_ptr(), q.unit.data_ptr(), q.sf_layout, R, Cc,
+        rc = L.metis_nvfp4_dequantize(q.codes.data_ptr(), q.scales.data_ptr(), (q.unit if unit is None else unit).data_ptr(), q.sf_layout, R, Cc,
                                       _ptr(rv), out.data_ptr(), _DTYPES[dtype], out.stride(0), _stream())
     cabi.check(rc, "metis_nvfp4_dequantize")
     LAUNCHES["dequantize"] += 1

@@ -194,6 +194,29 @@ def test_packed_gradients_agree_with_dense_gradients_up_to_quantization_noise(la
         assert rel_l2(res["packed"][name], res["dense"][name]) <= 0.25, name
 
 
+def test_bf16_input_gradient_fused_into_one_launch_matches_two_launches():
+    from Metis.Metis.bitlinear import MetisFusedFunction
+    torch.manual_seed(5)
+    args = metis_args(64, cache=True)                     # round to nearest everywhere: deterministic
+    layer = BitLinear(512, 384, args=args, bias=True, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+    layer.layer_name = "f"
+    layer.split()
+    layer = layer.to(DEV)
+    x = torch.randn(2, 256, 512, device=DEV, dtype=torch.bfloat16)
+    gout = torch.randn(2, 256, 384, device=DEV, dtype=torch.bfloat16)
+    grads = {}
+    for fused in (True, False):
+        MetisFusedFunction.fuse_dx_side_product = fused
+        try:
+            xin = x.clone().requires_grad_(True)
+            layer(xin).backward(gout)
+            grads[fused] = xin.grad.float().cpu().numpy()
+        finally:
+            MetisFusedFunction.fuse_dx_side_product = True
+    # both round the low-rank branch's contribution to bf16 once, at different points
+    assert rel_l2(grads[True], grads[False]) <= 1e-2
+
+
 def test_grpo_defaults_bf16_stochastic_backward_and_shared_activation():
     torch.manual_seed(1)
     block = torch.nn.Module()
