@@ -249,6 +249,14 @@ template <> struct Load8<float> {
   }
 };
 
+// Largest magnitude of a 16-element block (three-input maxima: 8 instructions).
+__device__ __forceinline__ float abs_max16(const float (&v)[16]) {
+  float a = fmaxf(fabsf(v[0]), fabsf(v[1]));
+#pragma unroll
+  for (int i = 2; i < 16; i += 2) a = max3(a, fabsf(v[i]), fabsf(v[i + 1]));
+  return a;
+}
+
 // 16 consecutive elements (one quantization block) starting at p, 16-byte aligned.
 template <typename T> struct Load16;
 template <> struct Load16<__nv_bfloat16> {
@@ -267,6 +275,33 @@ template <> struct Load16<float> {
       const float4 a = __ldg(reinterpret_cast<const float4*>(p) + i);
       v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
     }
+  }
+};
+
+// The same block kept as loaded (8 or 16 registers) so that the next block's loads can be in
+// flight while the current one is worked on.
+template <typename T> struct RawBlock;
+template <> struct RawBlock<__nv_bfloat16> {
+  uint4 a, b;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    a = __ldg(reinterpret_cast<const uint4*>(p));
+    b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  }
+  __device__ __forceinline__ void unpack(float (&v)[16]) const {
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[2 * i] = bf16_lo(w[i]); v[2 * i + 1] = bf16_hi(w[i]); }
+  }
+};
+template <> struct RawBlock<float> {
+  float4 q[4];
+  __device__ __forceinline__ void load(const float* p) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = __ldg(reinterpret_cast<const float4*>(p) + i);
+  }
+  __device__ __forceinline__ void unpack(float (&v)[16]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[4 * i] = q[i].x; v[4 * i + 1] = q[i].y; v[4 * i + 2] = q[i].z; v[4 * i + 3] = q[i].w; }
   }
 };
 

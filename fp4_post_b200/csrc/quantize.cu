@@ -43,16 +43,12 @@ quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int6
     float m[16];
     if (kMean) Load16<float>::load(col_mean + (int64_t)bc * 16, m);
     const Philox rng(seed);
-    for (int r = blockIdx.y * blockDim.y + threadIdx.y; r < rows; r += row_step) {
-      float v[16];
-      Load16<T>::load(x + (int64_t)r * ld + (int64_t)bc * 16, v);
+    auto quantize_block = [&](float (&v)[16], int r) {
       if (kMean) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = __fsub_rn(v[i], m[i]);
       }
-      float a = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(v[i]));
+      const float a = abs_max16(v);
       const float s = block_scale_from_amax(a);
       const int64_t b = (int64_t)r * blocks_per_row + bc;
       uint32_t packed[2];
@@ -65,6 +61,18 @@ quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int6
       codes[b] = make_uint2(packed[0], packed[1]);
       amax_out[b] = a;
       running = fmaxf(running, a);
+    };
+    // the next row's loads are issued before the current block is worked on
+    int r = blockIdx.y * blockDim.y + threadIdx.y;
+    RawBlock<T> cur, nxt;
+    if (r < rows) cur.load(x + (int64_t)r * ld + (int64_t)bc * 16);
+    for (; r < rows; r += row_step) {
+      const int rn = r + row_step;
+      if (rn < rows) nxt.load(x + (int64_t)rn * ld + (int64_t)bc * 16);
+      float v[16];
+      cur.unpack(v);
+      quantize_block(v, r);
+      cur = nxt;
     }
   }
   // whole warps reach this point together: a warp never spans the bc bound unevenly in y
@@ -317,7 +325,7 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
   const int by = kQuantThreads / bx;
   const int gx = (bpr + bx - 1) / bx;
   int64_t gy = ceil_div(rows, by);
-  const int64_t cap = ceil_div((int64_t)sm_count() * 16, gx);   // ~16 CTAs per SM in total
+  const int64_t cap = ceil_div((int64_t)sm_count() * 16, gx);   // ~16 CTAs per SM in total (swept 3..32: flat above 6)
   if (gy > cap) gy = cap;
   if (gy > 65535) gy = 65535;
   if (gy < 1) gy = 1;

@@ -36,7 +36,33 @@ def _need_cuda(t: torch.Tensor, what: str) -> None:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+
+
+class _on_device:
+    """Makes `dev` current for the calls inside; free when it already is (the common case)."""
+    __slots__ = ("guard",)
+
+    def __init__(self, dev: torch.device):
+        self.guard = None if dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+
+
+def _packed_buffers(L, R: int, Cc: int, sf_layout: int, dev):
+    """codes, scales and unit of one quantized tensor as views of a single allocation."""
+    n_codes = R * (Cc // 2)
+    n_scales = L.metis_nvfp4_sf_bytes(R, Cc, sf_layout)
+    o_scales = (n_codes + 255) & ~255
+    o_unit = (o_scales + n_scales + 255) & ~255
+    buf = torch.empty(o_unit + 16, dtype=torch.uint8, device=dev)
+    return buf[:n_codes].view(R, Cc // 2), buf[o_scales:o_scales + n_scales], buf[o_unit:o_unit + 4].view(torch.float32)
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -82,7 +108,7 @@ def col_mean(x: torch.Tensor) -> torch.Tensor:
     x2 = _rows2d(x)
     rows, cols = x2.shape
     L = cabi.lib()
-    with torch.cuda.device(x2.device):
+    with _on_device(x2.device):
         mean = torch.empty(cols, dtype=torch.float32, device=x2.device)
         ws_bytes = L.metis_col_mean_workspace_bytes(rows, cols)
         ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x2.device)
@@ -112,10 +138,8 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
         _need_cuda(mean, "mean")
         mean = mean.reshape(-1).to(torch.float32).contiguous()
         assert mean.numel() == cols
-    with torch.cuda.device(dev):
-        codes = torch.empty((R, Cc // 2), dtype=torch.uint8, device=dev)
-        scales = torch.empty(L.metis_nvfp4_sf_bytes(R, Cc, sf_layout), dtype=torch.uint8, device=dev)
-        unit = torch.empty(1, dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        codes, scales, unit = _packed_buffers(L, R, Cc, sf_layout, dev)
         ws = torch.empty(L.metis_nvfp4_quantize_workspace_bytes(R, Cc), dtype=torch.uint8, device=dev)
         rc = L.metis_nvfp4_quantize(x2.data_ptr(), _dtype_code(x2, "x"), rows, cols, x2.stride(0), _ptr(mean),
                                     flags, seed & (2**64 - 1), offset & (2**64 - 1), sf_layout,
@@ -146,10 +170,8 @@ def rmsnorm_nvfp4_quantize(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e
     assert gamma.numel() == cols
     L = cabi.lib()
     dev = x2.device
-    with torch.cuda.device(dev):
-        codes = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
-        scales = torch.empty(L.metis_nvfp4_sf_bytes(rows, cols, sf_layout), dtype=torch.uint8, device=dev)
-        unit = torch.empty(1, dtype=torch.float32, device=dev)
+    with _on_device(dev):
+        codes, scales, unit = _packed_buffers(L, rows, cols, sf_layout, dev)
         ws = torch.empty(L.metis_nvfp4_quantize_workspace_bytes(rows, cols), dtype=torch.uint8, device=dev)
         norm = None
         if return_norm:
@@ -171,7 +193,7 @@ def nvfp4_dequantize(q: NVFP4Tensor, dtype: torch.dtype = torch.float32, add_mea
     values in another product's accumulator units."""
     R, Cc = q.shape
     L = cabi.lib()
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         out = torch.empty((R, Cc), dtype=dtype, device=q.device)
         rv = q.row_vec if add_mean else None
         rc = L.metis_nvfp4_dequantize(q.codes.data_ptr(), q.scales.data_ptr(), (q.unit if unit is None else unit).data_ptr(), q.sf_layout, R, Cc,
@@ -190,7 +212,7 @@ def nvfp4_gemv(q: NVFP4Tensor, v: Optional[torch.Tensor] = None) -> torch.Tensor
     if v is not None:
         v = v.reshape(-1).to(torch.float32).contiguous()
         assert v.numel() == Cc
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         out = torch.empty(R, dtype=torch.float32, device=q.device)
         rc = L.metis_nvfp4_gemv(q.codes.data_ptr(), q.scales.data_ptr(), q.unit.data_ptr(), q.sf_layout, R, Cc,
                                 _ptr(v), out.data_ptr(), _stream())
@@ -244,7 +266,7 @@ def nvfp4_gemm(a: NVFP4Tensor, b: NVFP4Tensor, *, lowrank=None, rank1=(), c: Opt
             keep.append(cv)
         setattr(args, f"cvec{i}", _ptr(cv))
         setattr(args, f"rvec{i}", rv.data_ptr())
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=dev)
         else:
