@@ -180,6 +180,7 @@ def main():
     import torch.distributed as dist
     import fp4_post_b200
     from fp4_post_b200 import cabi, ops
+    from fp4_post_b200.dp import allreduce_gradients
     from fp4_post_b200.Metis.Metis.bitlinear import BitLinear
     from fp4_post_b200.grpo.grpo import MetisArgs
 
@@ -225,8 +226,7 @@ def main():
         y = layer(x)
         y.backward(grad)
         if world > 1:
-            for p in params:                       # what DDP would do for this layer
-                dist.all_reduce(p.grad)
+            allreduce_gradients(params)            # what DDP would do for this layer: one bucket per dtype
         return y
 
     def barrier():

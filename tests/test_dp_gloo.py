@@ -1,0 +1,87 @@
+"""Data-parallel path on two CPU ranks (gloo): sharded tokens, replicated weights, one gradient
+all-reduce.  With identity quantizers the layer is linear in the batch, so the all-reduced weight
+gradients must equal the single-process gradients of the whole batch."""
+import os
+import socket
+from types import SimpleNamespace
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _make_layer():
+    import fp4_post_b200
+    fp4_post_b200.install_reference_aliases()
+    from Metis.Metis.bitlinear import BitLinear, LinearLowbit, LinearLowbitFunction as F
+    from Metis.Metis.quant import Cast2Fp32
+    F.compute_dtype = torch.float32
+    for k in ("q_forward_input", "q_forward_weight", "q_backward_input", "q_backward_weight", "q_backward_outputgrad"):
+        setattr(F, k, Cast2Fp32)
+    F.enable_activation_svd = F.enable_backward_svd = F.enable_nv_recipe = False
+    torch.manual_seed(0)
+    args = SimpleNamespace(device="cpu", cache_quantized_weight=False, forward_svd_rank=4)
+    layer = BitLinear.__new__(BitLinear)
+    torch.nn.Module.__init__(layer)
+    layer.args, layer.is_svd_quant, layer.mean_cache = args, True, {}
+    layer.activation_group, layer._merged_rollout_weight_cache, layer.layer_name = None, None, "dp"
+    layer.vlinear = LinearLowbit(16, 4, bias=False, args=args)
+    layer.ulinear = torch.nn.Linear(4, 8, bias=False)
+    layer.warmup_linear = LinearLowbit(16, 8, bias=True, args=args)
+    layer.s = torch.nn.Parameter(torch.rand(4) + 0.5)
+    return layer
+
+
+def _batch():
+    g = torch.Generator().manual_seed(1)
+    return torch.randn(6, 5, 16, generator=g), torch.randn(6, 5, 8, generator=g)
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fp4_post_b200.dp import allreduce_gradients, shard_tokens
+        layer = _make_layer()
+        x, g = _batch()
+        xs, gs = shard_tokens(x, rank, world), shard_tokens(g, rank, world)
+        layer(xs).backward(gs)
+        nbytes = allreduce_gradients(layer.parameters())
+        if rank == 0:
+            out.put(({n: p.grad.clone() for n, p in layer.named_parameters()}, nbytes, tuple(xs.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_reproduce_the_full_batch_weight_gradients():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    grads, nbytes, shard_shape = out.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert shard_shape == (3, 5, 16)
+    layer = _make_layer()
+    x, g = _batch()
+    layer(x).backward(g)
+    assert nbytes == sum(p.numel() * 4 for p in layer.parameters())
+    for name, p in layer.named_parameters():
+        torch.testing.assert_close(grads[name], p.grad, rtol=1e-5, atol=1e-5, msg=name)
+
+
+def test_sharding_covers_the_batch_once_and_allreduce_is_a_noop_without_a_group():
+    from fp4_post_b200.dp import allreduce_gradients, shard_tokens
+    x = torch.arange(7 * 3).reshape(7, 3)
+    parts = [shard_tokens(x, r, 3) for r in range(3)]
+    assert torch.equal(torch.cat(parts), x) and [p.shape[0] for p in parts] == [2, 2, 3]
+    assert allreduce_gradients([torch.nn.Parameter(torch.zeros(2))]) == 0
