@@ -43,6 +43,11 @@ M_TOKENS, HIDDEN_K, HIDDEN_N, RANK = 16384, 4096, 4096, 128
 QUANT_ROWS, QUANT_COLS = 65536, 4096
 METRIC = "metis_nvfp4_linear_fwd_bwd_tflops"
 BYTES_PER_ELEM_BF16 = 2.5625          # 2 (bf16 in) + 0.5 (codes) + 1/16 (E4M3 scale)
+# DRAM bytes (read + write) of one forward GEMM launch, from an ncu capture of the same kernel on
+# M = 8192 (31.7 MB read + 15.6 MB written) scaled by the rows processed; the profile summary
+# profiles/nvfp4_gemm_8192x4096x4096_r128.md holds the capture and its command.
+GEMM_DRAM_BYTES_PER_LAUNCH = int(47.3e6 * M_TOKENS / 8192)
+GEMM_DRAM_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum at M = 8192, scaled by M"
 
 
 def layer_flops(M, N, K, r):
@@ -164,6 +169,47 @@ def workload_config(n_gpus):
             "l2": "inputs larger than L2 (x and grad_out are 128 MiB each)"}
 
 
+# ---- one kernel alone -----------------------------------------------------------------------------------------
+
+def run_single_kernel(args):
+    """`--only K`: a few launches of one kernel on [rows, cols] bf16 (GEMM: M = rows, K = cols, N = n),
+    timed with CUDA events.  Small enough to sit under an ncu capture."""
+    import torch
+    from fp4_post_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    rows, cols = args.rows, args.cols
+    x = torch.randn(rows, cols, device=dev, dtype=torch.bfloat16)
+    if args.only == "gemm":
+        w = torch.randn(args.n, cols, device=dev, dtype=torch.bfloat16) / cols ** 0.5
+        qa, qb = ops.nvfp4_quantize(x), ops.nvfp4_quantize(w)
+        lr = None
+        if args.rank:
+            lr = (torch.randn(rows, args.rank, device=dev, dtype=torch.bfloat16),
+                  torch.randn(args.n, args.rank, device=dev, dtype=torch.bfloat16))
+        out = torch.empty(rows, args.n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.nvfp4_gemm(qa, qb, lowrank=lr, out=out)
+        work, unit = 2 * rows * args.n * (cols + args.rank) / 1e12, "TFLOP/s"
+    else:
+        gamma = torch.ones(cols, device=dev, dtype=torch.bfloat16)
+        fn = {"quant_rows": lambda: ops.nvfp4_quantize(x),
+              "quant_transposed": lambda: ops.nvfp4_quantize(x, transpose=True),
+              "rmsnorm_quant": lambda: ops.rmsnorm_nvfp4_quantize(x, gamma, 1e-6)}[args.only]
+        work, unit = rows * cols * BYTES_PER_ELEM_BF16 / 1e9, "GB/s"
+    for _ in range(max(1, args.warmup)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"only": args.only, "rows": rows, "cols": cols, "n": args.n, "rank": args.rank,
+                      "ms_per_call": ms, "value": work / (ms / 1e3), "unit": unit}), flush=True)
+
+
 # ---- GPU arm ------------------------------------------------------------------------------------------------
 
 def main():
@@ -172,9 +218,17 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm"],
+                    help="time one kernel alone on a small case (the command used for ncu captures)")
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--rank", type=int, default=128)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.only:
+        return run_single_kernel(args)
 
     import torch
     import torch.distributed as dist
@@ -323,7 +377,7 @@ def main():
             "clocks": clock_summary,
             "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_kernel<256> forward residual GEMM + fused rank-128 product",
                          "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
-                         "traffic": None, "peak_source": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s)",
+                         "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "traffic_source": GEMM_DRAM_SOURCE, "peak_source": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s)",
                          "frac_of_nominal_9000": achieved / 9000.0, "ms_per_launch": ms_gemm},
             "quant": quant_lines,
             "hbm_peak_gbs": peaks["hbm_gbs"],
