@@ -51,7 +51,8 @@ template <int BN> struct GemmCfg {
   static constexpr int kSfaBytes = 4 * 512;                        // 4 scale tiles (256 elements)
   static constexpr int kSfbBytes = (BN / 128) * 4 * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int kStagingBytes = 4 * 2048;                   // epilogue: 32 rows x 64 bytes per warp
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 struct GemmParams {
@@ -74,9 +75,10 @@ struct GemmParams {
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void tc_commit_addr(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) { tc_commit_addr(smem_u32(bar)); }
 // Operand descriptors are passed as two 32-bit halves: only the low half (the address field)
 // changes from stage to stage, so the issuing thread advances it with one 32-bit add.
 __device__ __forceinline__ void tc_mma_fp4(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
@@ -136,6 +138,107 @@ __device__ __forceinline__ void report(int32_t* status, volatile int* abort_flag
   if (status) atomicCAS(status, 0, code);
 }
 
+// ---- epilogue arithmetic for one 32-column chunk of one accumulator row -----------------------------
+
+template <typename TD> struct EpilogueCtx {
+  const GemmParams* p;
+  uint8_t* staging;      // 2 KiB of shared memory owned by this warp
+  int64_t row0;          // first of the warp's 32 rows; lane l holds row0 + l
+  float g, c0, c1;
+};
+
+// Lane l arrives with 32 consecutive columns of row row0 + l.  Stored straight from there, one
+// 16-byte store instruction would touch 32 different rows; instead the warp turns the chunk
+// through shared memory (64-byte rows, 16-byte pieces XOR-swizzled by the row so that neither side
+// has bank conflicts) and every store instruction writes 64 contiguous bytes of 8 rows.
+template <typename TD>
+__device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uint32_t (&r)[32], int64_t col0) {
+  const GemmParams& p = *ctx.p;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = ctx.row0 + lane;
+  if (ctx.row0 >= p.M || col0 >= p.N) return;          // warp-uniform
+  const bool live = row < p.M;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ctx.g;
+  const bool full_chunk = col0 + 32 <= p.N;
+  if (p.rvec0) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(ctx.c0, __ldg(p.rvec0 + col0 + i), v[i]);
+  }
+  if (p.rvec1) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(ctx.c1, __ldg(p.rvec1 + col0 + i), v[i]);
+  }
+  const TD* src = (p.c && live) ? static_cast<const TD*>(p.c) + row * p.ldc + col0 : nullptr;
+  if (full_chunk) {
+    const int own_swz = (lane >> 1) & 3;
+    if constexpr (sizeof(TD) == 2) {
+      if (src) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 w = __ldg(reinterpret_cast<const uint4*>(src) + i);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { v[8 * i + 2 * k] += bf16_lo(ww[k]); v[8 * i + 2 * k + 1] += bf16_hi(ww[k]); }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        __nv_bfloat162 o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(v[8 * k + 2 * e], v[8 * k + 2 * e + 1]);
+        *reinterpret_cast<uint4*>(ctx.staging + lane * 64 + ((k ^ own_swz) << 4)) = *reinterpret_cast<uint4*>(o);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rl = 8 * i + (lane >> 2), j = lane & 3;
+        const uint4 w = *reinterpret_cast<const uint4*>(ctx.staging + rl * 64 + ((j ^ ((rl >> 1) & 3)) << 4));
+        if (ctx.row0 + rl < p.M)
+          *reinterpret_cast<uint4*>(static_cast<TD*>(p.d) + (ctx.row0 + rl) * p.ldd + col0 + j * 8) = w;
+      }
+      __syncwarp();
+    } else {
+      if (src) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 w = __ldg(reinterpret_cast<const float4*>(src) + i);
+          v[4 * i] += w.x; v[4 * i + 1] += w.y; v[4 * i + 2] += w.z; v[4 * i + 3] += w.w;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                     // 16 columns = 64 bytes per row at a time
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          *reinterpret_cast<float4*>(ctx.staging + lane * 64 + ((k ^ own_swz) << 4)) =
+              make_float4(v[16 * h + 4 * k], v[16 * h + 4 * k + 1], v[16 * h + 4 * k + 2], v[16 * h + 4 * k + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int rl = 8 * i + (lane >> 2), j = lane & 3;
+          const float4 w = *reinterpret_cast<const float4*>(ctx.staging + rl * 64 + ((j ^ ((rl >> 1) & 3)) << 4));
+          if (ctx.row0 + rl < p.M)
+            *reinterpret_cast<float4*>(static_cast<TD*>(p.d) + (ctx.row0 + rl) * p.ldd + col0 + 16 * h + j * 4) = w;
+        }
+        __syncwarp();
+      }
+    }
+  } else if (live) {
+    TD* dst = static_cast<TD*>(p.d) + row * p.ldd + col0;
+    for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
+      float o = v[i];
+      if constexpr (sizeof(TD) == 2) {
+        if (src) o += __bfloat162float(src[i]);
+        dst[i] = __float2bfloat16_rn(o);
+      } else {
+        if (src) o += src[i];
+        dst[i] = o;
+      }
+    }
+  }
+}
+
 // ---- the kernel ---------------------------------------------------------------------------------------
 
 template <int BN, typename TD>
@@ -148,15 +251,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+  uint8_t* staging = smem + kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
   uint64_t* full = bars;                                   // [kStages]  TMA bytes landed
   uint64_t* empty = bars + kStages;                        // [kStages]  MMAs finished reading the stage
   uint64_t* acc_full = bars + 2 * kStages;                 // accumulator of the current tile complete
   uint64_t* acc_release = bars + 2 * kStages + 1;          // columns the next tile needs are drained
   uint64_t* drain = bars + 2 * kStages + 2;                // error path only
   uint64_t* sf_ready = bars + 2 * kStages + 3;             // [2] scale buffer written by the four movers
-  uint64_t* sf_free = bars + 2 * kStages + 5;              // [2] MMAs that read the scale buffer are done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 7);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -175,7 +278,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(acc_full, 1);
     mbar_init(acc_release, 4);
-    for (int b = 0; b < 2; ++b) { mbar_init(&sf_ready[b], 4); mbar_init(&sf_free[b], 1); }
+    for (int b = 0; b < 2; ++b) mbar_init(&sf_ready[b], 4);
     mbar_init(drain, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -191,97 +294,104 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ===== TMA producer =====
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool first = true;
-      bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
-        const int32_t m0 = (int32_t)(tm * kBM), n0 = (int32_t)(tn * BN);
-        // scale tiles: 4 per stage (2 KiB) and per 128 rows, contiguous along K; those of B exist
-        // only for whole 128-row blocks of N
-        const uint8_t* sfa_src = p.a_scales + ((int64_t)m0 >> 7) * sf_tiles_a * 512;
-        const int64_t rb0 = (int64_t)n0 >> 7;
-        const uint8_t* sfb_src = p.b_scales + rb0 * sf_tiles_a * 512;
-        int sfb_blocks = 0;
-        for (int b = 0; b < BN / 128; ++b) sfb_blocks += (rb0 + b < b_row_blocks) ? 1 : 0;
-        const uint32_t k_bytes = Cfg::kABytes + Cfg::kBBytes + Cfg::kSfaBytes + sfb_blocks * 2048;
-        for (int it = 0; it < iters; ++it) {
-          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
-            report(p.status, abort_flag, METIS_DEV_TIMEOUT_MMA);
-            ok = false;
-            break;
-          }
-          uint8_t* sa = smem + stage * Cfg::kStageBytes;
-          uint8_t* sb = sa + Cfg::kABytes;
-          uint8_t* ssfa = sb + Cfg::kBBytes;
-          uint8_t* ssfb = ssfa + Cfg::kSfaBytes;
+    // ===== TMA producer: the whole warp walks the pipeline, one elected lane issues the copies =====
+    int stage = 0;
+    uint32_t phase = 0;
+    bool first = true;
+    bool ok = true;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t full_base = smem_u32(full);
+    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
+      const int32_t m0 = (int32_t)(tm * kBM), n0 = (int32_t)(tn * BN);
+      // scale tiles: 4 per stage (2 KiB) and per 128 rows, contiguous along K; those of B exist
+      // only for whole 128-row blocks of N
+      const uint8_t* sfa_src = p.a_scales + ((int64_t)m0 >> 7) * sf_tiles_a * 512;
+      const int64_t rb0 = (int64_t)n0 >> 7;
+      const uint8_t* sfb_src = p.b_scales + rb0 * sf_tiles_a * 512;
+      const bool sfb_second = (BN == 256) && (rb0 + 1 < b_row_blocks);
+      const uint32_t k_bytes = Cfg::kABytes + Cfg::kBBytes + Cfg::kSfaBytes + 2048 + (sfb_second ? 2048 : 0);
+      for (int it = 0; it < iters; ++it) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&empty[stage], phase ^ 1u, abort_flag));
+        if (!ok) {
+          if (lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_MMA);
+          break;
+        }
+        const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+        const uint32_t sb = sa + Cfg::kABytes;
+        const uint32_t ssfa = sb + Cfg::kBBytes;
+        const uint32_t ssfb = ssfa + Cfg::kSfaBytes;
+        const uint32_t bar = full_base + stage * 8;
+        if (elect_one()) {
           if (p.debug & kDebugNoLoad) {
-            mbar_arrive(&full[stage]);
+            mbar_arrive_addr(bar);
           } else if (it < k_iters) {
-            mbar_expect_tx(&full[stage], k_bytes);
-            tma_load_2d(sa, &map_a, it * kBKBytes, m0, &full[stage]);
-            tma_load_2d(sb, &map_b, it * kBKBytes, n0, &full[stage]);
+            mbar_expect_tx_addr(bar, k_bytes);
+            tma_load_2d_addr(sa, &map_a, it * kBKBytes, m0, bar);
+            tma_load_2d_addr(sb, &map_b, it * kBKBytes, n0, bar);
             const bool drop = first && (p.debug & kDebugDropFirstSfa);
-            if (!drop) bulk_load(ssfa, sfa_src + (int64_t)it * 2048, 2048, &full[stage]);
-            for (int b = 0; b < sfb_blocks; ++b)
-              bulk_load(ssfb + b * 2048, sfb_src + (b * sf_tiles_a + (int64_t)it * 4) * 512, 2048, &full[stage]);
-            first = false;
+            if (!drop) bulk_load_addr(ssfa, sfa_src + (int64_t)it * 2048, 2048, bar);
+            bulk_load_addr(ssfb, sfb_src + (int64_t)it * 2048, 2048, bar);
+            if (sfb_second) bulk_load_addr(ssfb + 2048, sfb_src + (sf_tiles_a + (int64_t)it * 4) * 512, 2048, bar);
           } else {
             const int j = it - k_iters;   // 64-column panel of the rank-r factors
-            mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes);
-            tma_load_2d(sa, &map_t, j * 64, m0, &full[stage]);
-            tma_load_2d(sb, &map_u, j * 64, n0, &full[stage]);
+            mbar_expect_tx_addr(bar, Cfg::kABytes + Cfg::kBBytes);
+            tma_load_2d_addr(sa, &map_t, j * 64, m0, bar);
+            tma_load_2d_addr(sb, &map_u, j * 64, n0, bar);
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
+        first = false;
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
-    // ===== tensor-core issuer =====
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t local_tile = 0;
-      bool ok = true;
-      bool issued = false;
-      const uint32_t stage0_lo = operand_desc_lo(smem_u32(smem));
-      uint32_t stage_lo = stage0_lo;
-      uint32_t sf_buf = 0, sf_phase = 0;
-      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-        // Tile j may start once the epilogue of tile j-1 has drained the columns the two
-        // accumulators share (release number j-1, i.e. phase parity (j-1)&1).  That also covers
-        // tile j-2, whose accumulator this one reuses: the epilogue finished it before it began j-1.
-        if (local_tile > 0 && !mbar_wait(acc_release, (local_tile - 1u) & 1u, abort_flag)) {
-          report(p.status, abort_flag, METIS_DEV_TIMEOUT_EPI);
-          ok = false;
+    // ===== tensor-core issuer: the whole warp walks the pipeline, one elected lane issues =====
+    // Keeping the loop warp-uniform lets the descriptors and addresses live in uniform registers;
+    // a single diverged lane pays a register move per operand of every MMA and copy.
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t local_tile = 0;
+    bool ok = true;
+    bool issued = false;
+    const uint32_t stage0_lo = operand_desc_lo(smem_u32(smem));
+    const uint32_t empty_base = smem_u32(empty);
+    uint32_t stage_lo = stage0_lo;
+    uint32_t sf_buf = 0, sf_phase = 0;
+    const bool no_mma = (p.debug & kDebugNoMma) != 0;
+    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      // Tile j may start once the epilogue of tile j-1 has drained the columns the two
+      // accumulators share (release number j-1, i.e. phase parity (j-1)&1).  That also covers
+      // tile j-2, whose accumulator this one reuses: the epilogue finished it before it began j-1.
+      if (local_tile > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_release, (local_tile - 1u) & 1u, abort_flag));
+        if (!ok) {
+          if (lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_EPI);
+          break;
+        }
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (local_tile & 1u) * Cfg::kAccStride;
+      for (int it = 0; it < iters; ++it) {
+        const bool scaled = it < k_iters;
+        // A scaled iteration waits for the movers only: they pass the stage's TMA barrier before
+        // they copy, so their arrival also says that the code tiles have landed.
+        uint64_t* wait_bar = (scaled && !no_mma) ? &sf_ready[sf_buf] : &full[stage];
+        const uint32_t wait_parity = (scaled && !no_mma) ? sf_phase : phase;
+        ok = __all_sync(0xffffffffu, mbar_wait(wait_bar, wait_parity, abort_flag));
+        if (!ok) {
+          if (lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_TMA);
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (local_tile & 1u) * Cfg::kAccStride;
-        for (int it = 0; it < iters; ++it) {
-          if (!mbar_wait(&full[stage], phase, abort_flag)) {
-            report(p.status, abort_flag, METIS_DEV_TIMEOUT_TMA);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          // descriptor address fields (16-byte units) of this stage's A, B and scale tiles
-          const uint32_t a_lo = stage_lo;
-          const uint32_t b_lo = stage_lo + (Cfg::kABytes >> 4);
-          if (p.debug & kDebugNoMma) {
-          } else if (it < k_iters) {
+        // descriptor address fields (16-byte units) of this stage's A and B tiles
+        const uint32_t a_lo = stage_lo;
+        const uint32_t b_lo = stage_lo + (Cfg::kABytes >> 4);
+        const uint32_t t_sfa = tmem_base + kSfCol + sf_buf * kSfBufCols, t_sfb = t_sfa + 16;
+        if (elect_one()) {
+          if (no_mma) {
+          } else if (scaled) {
             // the movers have put this iteration's scales into buffer sf_buf: 4 columns per MMA
             // and 128 rows for A, then for B
-            const uint32_t t_sfa = tmem_base + kSfCol + sf_buf * kSfBufCols, t_sfb = t_sfa + 16;
-            if (!mbar_wait(&sf_ready[sf_buf], sf_phase, abort_flag)) {
-              report(p.status, abort_flag, METIS_DEV_TIMEOUT_TMA);
-              ok = false;
-              break;
-            }
-            tc_fence_after();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               // 64 elements of K = 32 bytes (2 units) inside the 128-byte swizzled row
@@ -295,25 +405,24 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               tc_mma_bf16(d_tmem, a_lo + 2 * j, b_lo + 2 * j, kOperandDescHi, idesc_bf16(BN), (it > 0 || j > 0) ? 1u : 0u);
             }
           }
-          issued = true;
-          tc_commit(&empty[stage]);          // frees the stage once these MMAs have read it
-          if (it < k_iters) {
-            tc_commit(&sf_free[sf_buf]);     // and the scale buffer
-            if ((sf_buf ^= 1u) == 0) sf_phase ^= 1u;
-          }
-          stage_lo += Cfg::kStageBytes >> 4;
-          if (++stage == kStages) { stage = 0; phase ^= 1u; stage_lo = stage0_lo; }
+          // frees the stage (for the producer) and, two iterations on, its scale buffer (for the
+          // movers) once these MMAs have read them
+          tc_commit_addr(empty_base + stage * 8);
+          if (it == iters - 1) tc_commit(acc_full);   // accumulator complete
         }
-        if (!ok) break;
-        tc_commit(acc_full);                 // accumulator complete
-      }
-      if (!ok && issued) {
-        // error path: let the tensor core finish what was issued before tensor memory is freed
-        tc_commit(drain);
-        const uint64_t t0 = global_ns();
-        while (!mbar_try(drain, 0) && global_ns() - t0 < kWaitLimitNs) {}
+        issued = true;
+        if (scaled && (sf_buf ^= 1u) == 0) sf_phase ^= 1u;
+        stage_lo += Cfg::kStageBytes >> 4;
+        if (++stage == kStages) { stage = 0; phase ^= 1u; stage_lo = stage0_lo; }
       }
     }
+    if (!ok && issued && elect_one()) {
+      // error path: let the tensor core finish what was issued before tensor memory is freed
+      tc_commit(drain);
+      const uint64_t t0 = global_ns();
+      while (!mbar_try(drain, 0) && global_ns() - t0 < kWaitLimitNs) {}
+    }
+    __syncwarp();
   } else if (warp >= 6) {
     // ===== scale movers: warps 6..9 own tensor-memory lanes 32*(warp%4) .. +31 =====
     // Lane l of every mover reads bytes [16 l, 16 l + 16) of a 512-byte scale tile: the scales of
@@ -321,10 +430,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // lane l holds for that tile.
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     int stage = 0;
-    uint32_t phase = 0, sf_buf = 0, sf_phase = 0;
+    uint32_t phase = 0, sf_buf = 0;
+    uint32_t slot = 0;                       // pipeline iterations so far, of either kind
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int it = 0; it < iters; ++it) {
+      for (int it = 0; it < iters; ++it, ++slot) {
         if (it < k_iters && !(p.debug & kDebugNoMma)) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
           const uint4* sf = reinterpret_cast<const uint4*>(smem + stage * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes) + lane;
@@ -340,7 +450,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               dst[0] = u.x; dst[1] = u.y; dst[2] = u.z; dst[3] = u.w;
             }
           }
-          if (!mbar_wait(&sf_free[sf_buf], sf_phase ^ 1u, abort_flag)) { ok = false; break; }
+          // The scale buffer was last read by the MMAs of an iteration at least two pipeline slots
+          // back; the commit of slot - 2 (which frees that slot's stage) covers every MMA before it.
+          if (slot >= 2) {
+            const int s2 = stage >= 2 ? stage - 2 : stage - 2 + kStages;
+            const uint32_t par2 = stage >= 2 ? phase : phase ^ 1u;
+            if (!mbar_wait(&empty[s2], par2, abort_flag)) { ok = false; break; }
+          }
           tc_fence_after();
           const uint32_t t_sfa = tmem_base + lane_base + kSfCol + sf_buf * kSfBufCols;
           tc_store16(t_sfa, ra);
@@ -353,7 +469,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sf_ready[sf_buf]);
-          if ((sf_buf ^= 1u) == 0) sf_phase ^= 1u;
+          sf_buf ^= 1u;
         }
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
@@ -362,12 +478,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   } else {
     // ===== epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 =====
     const int q = warp & 3;
-    const float g = p.alpha * __ldg(p.a_unit) * __ldg(p.b_unit);
+    EpilogueCtx<TD> ctx;
+    ctx.g = p.alpha * __ldg(p.a_unit) * __ldg(p.b_unit);
+    ctx.p = &p;
+    ctx.staging = staging + q * 2048;
     uint32_t local_tile = 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
       const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
       const int64_t row = tm * kBM + q * 32 + lane;
       const int64_t n0 = tn * BN;
+      ctx.row0 = tm * kBM + q * 32;
+      ctx.c0 = p.rvec0 ? (p.cvec0 ? (row < p.M ? __ldg(p.cvec0 + row) : 0.f) : 1.0f) : 0.0f;
+      ctx.c1 = p.rvec1 ? (p.cvec1 ? (row < p.M ? __ldg(p.cvec1 + row) : 0.f) : 1.0f) : 0.0f;
       if (!mbar_wait(acc_full, local_tile & 1u, abort_flag)) {
         if (lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_MMA);
         break;
@@ -378,81 +500,35 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       // chunk order: the columns shared with the other accumulator first.  For the even
       // accumulator [0,256) they are its last chunks, for the odd one [160,416) its first ones.
       constexpr int kChunks = BN / 32;
-      const int first_chunk = (Cfg::kSharedChunks > 0 && !odd) ? kChunks - Cfg::kSharedChunks : 0;
-      const float c0 = p.rvec0 ? (p.cvec0 ? (row < p.M ? __ldg(p.cvec0 + row) : 0.f) : 1.0f) : 0.0f;
-      const float c1 = p.rvec1 ? (p.cvec1 ? (row < p.M ? __ldg(p.cvec1 + row) : 0.f) : 1.0f) : 0.0f;
+      constexpr int kShared = Cfg::kSharedChunks;
+      const int first_chunk = (kShared > 0 && !odd) ? kChunks - kShared : 0;
+      if constexpr (kShared > 0) {
+        // pull every shared column into registers, hand the columns to the next tile's MMAs,
+        // and only then do the arithmetic and the stores
+        uint32_t rs[kShared][32];
+#pragma unroll
+        for (int s = 0; s < kShared; ++s) tc_load32(t_row + (first_chunk + s) * 32, rs[s]);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_release);
+#pragma unroll
+        for (int s = 0; s < kShared; ++s) emit_chunk<TD>(ctx, rs[s], n0 + (first_chunk + s) * 32);
+      } else {
+        // separate accumulators: the next tile never touches this one
+        if (lane == 0) mbar_arrive(acc_release);
+      }
 #pragma unroll 1
-      for (int step = 0; step < kChunks; ++step) {
+      for (int step = kShared; step < kChunks; ++step) {
         int ch = first_chunk + step;
         if (ch >= kChunks) ch -= kChunks;
-        if (step == Cfg::kSharedChunks) {
-          // everything the next tile's accumulator overlaps has been read out of tensor memory
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_release);
-        }
         uint32_t r[32];
         tc_load32(t_row + ch * 32, r);
         tc_wait_ld();
-        const int64_t col0 = n0 + ch * 32;
-        if (row < p.M && col0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * g;
-          const bool full_chunk = col0 + 32 <= p.N;
-          if (p.rvec0) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(c0, __ldg(p.rvec0 + col0 + i), v[i]);
-          }
-          if (p.rvec1) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(c1, __ldg(p.rvec1 + col0 + i), v[i]);
-          }
-          TD* dst = static_cast<TD*>(p.d) + row * p.ldd + col0;
-          const TD* src = p.c ? static_cast<const TD*>(p.c) + row * p.ldc + col0 : nullptr;
-          if (full_chunk) {
-            if constexpr (sizeof(TD) == 2) {
-              if (src) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const uint4 w = __ldg(reinterpret_cast<const uint4*>(src) + i);
-                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                  for (int k = 0; k < 4; ++k) { v[8 * i + 2 * k] += bf16_lo(ww[k]); v[8 * i + 2 * k + 1] += bf16_hi(ww[k]); }
-                }
-              }
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                __nv_bfloat162 o[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(v[8 * i + 2 * k], v[8 * i + 2 * k + 1]);
-                reinterpret_cast<uint4*>(dst)[i] = *reinterpret_cast<uint4*>(o);
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                if (src) {
-                  const float4 w = __ldg(reinterpret_cast<const float4*>(src) + i);
-                  o.x += w.x; o.y += w.y; o.z += w.z; o.w += w.w;
-                }
-                reinterpret_cast<float4*>(dst)[i] = o;
-              }
-            }
-          } else {
-            for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-              float o = v[i];
-              if constexpr (sizeof(TD) == 2) {
-                if (src) o += __bfloat162float(src[i]);
-                dst[i] = __float2bfloat16_rn(o);
-              } else {
-                if (src) o += src[i];
-                dst[i] = o;
-              }
-            }
-          }
-        }
+        emit_chunk<TD>(ctx, r, n0 + ch * 32);
       }
+      // the accumulator is free again only when every lane has read it
+      tc_fence_before();
     }
   }
 
