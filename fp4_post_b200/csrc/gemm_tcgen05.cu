@@ -17,227 +17,9 @@
 //              block-scale layout wants).  A tcgen05.cp issued by warp 1 would do the same, but it
 //              runs in the MMA pipe and cost about as much time there as the MMAs themselves.
 // Hand-offs are mbarriers; every wait is bounded and reports through the status word.
-#include "common.cuh"
-#include "tma.cuh"
+#include "gemm_common.cuh"
 
 namespace metis {
-
-constexpr int kBM = 128;             // rows of A per tile (the MMA M)
-constexpr int kBKBytes = 128;        // bytes of packed codes per row per stage = 256 elements
-constexpr int kGemmThreads = 320;     // producer, issuer, 4 epilogue warps, 4 scale-mover warps
-constexpr int kTmemCols = 512;
-// Scale columns in tensor memory: two buffers of 48 columns (16 for A, 32 for B), used by
-// alternate pipeline iterations so that the copy for one iteration never has to wait for the
-// MMAs of the previous one to finish reading.
-constexpr int kSfCol = 416;
-constexpr int kSfBufCols = 48;
-
-// debug knob carried in metis_gemm_args.reserved: the producer arms the first stage's barrier
-// for the scale bytes of A but never issues that copy, so the consumer's bounded wait expires.
-constexpr int kDebugDropFirstSfa = 1;
-// timing experiments (results are meaningless): issue no MMAs / request no data
-constexpr int kDebugNoMma = 2;
-constexpr int kDebugNoLoad = 4;
-
-template <int BN> struct GemmCfg {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  // Two accumulators.  256 + 256 columns do not fit beside the scale columns, so for BN = 256 the
-  // second one starts at column 160: columns [160,256) belong to both.  The epilogue drains those
-  // columns first and then lets the next tile's MMAs start while it drains the rest.
-  static constexpr int kAccStride = (BN == 256) ? 160 : BN;
-  static constexpr int kSharedChunks = (BN == 256) ? 3 : 0;     // 32-column chunks in the overlap
-  static constexpr int kABytes = kBM * kBKBytes;                   // 16 KiB
-  static constexpr int kBBytes = BN * kBKBytes;                    // 16 or 32 KiB
-  static constexpr int kSfaBytes = 4 * 512;                        // 4 scale tiles (256 elements)
-  static constexpr int kSfbBytes = (BN / 128) * 4 * 512;
-  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStagingBytes = 4 * 2048;                   // epilogue: 32 rows x 64 bytes per warp
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment*/ + 256 /*barriers*/;
-};
-
-struct GemmParams {
-  int64_t M, N, K;
-  int32_t rank;
-  int32_t debug;
-  const uint8_t* a_scales;
-  const uint8_t* b_scales;
-  const float* a_unit;
-  const float* b_unit;
-  float alpha;
-  const float* cvec0;  const float* rvec0;
-  const float* cvec1;  const float* rvec1;
-  const void* c;  int64_t ldc;
-  void* d;        int64_t ldd;
-  int32_t* status;
-};
-
-// ---- PTX wrappers ---------------------------------------------------------------------------------
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit_addr(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint64_t* bar) { tc_commit_addr(smem_u32(bar)); }
-// Operand descriptors are passed as two 32-bit halves: only the low half (the address field)
-// changes from stage to stage, so the issuing thread advances it with one 32-bit add.
-__device__ __forceinline__ void tc_mma_fp4(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
-                                           uint32_t sfa, uint32_t sfb, uint32_t acc) {
-  asm volatile(
-      "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %7, 0; mov.b64 da, {%1, %3}; mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p; }"
-      ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(sfa), "r"(sfb), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
-                                            uint32_t acc) {
-  asm volatile(
-      "{ .reg .pred p; .reg .b64 da, db; setp.ne.b32 p, %5, 0; mov.b64 da, {%1, %3}; mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p; }"
-      ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void tc_load32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_store16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptors (64-bit): start address >> 4 in [0,14), leading byte offset
-// >> 4 in [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in [46,48), swizzle
-// mode in [61,64) (0 none, 2 = 128-byte).
-// K-major operand tile stored as rows of 128 bytes, 128-byte swizzled: groups of 8 rows are
-// 1024 bytes apart (stride field 64), leading field 1, version 1, swizzle mode 2.
-constexpr uint32_t kOperandDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t operand_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
-// Instruction descriptors (32-bit): formats of A [7,10) and B [10,13), N>>3 in [17,23),
-// M>>4 in [24,29); both operands K-major.
-__host__ __device__ constexpr uint32_t idesc_fp4(int bn) {
-  // A, B = e2m1 (1); scale format UE4M3 (bit 23 = 0); scale ids 0; K = 64 (bit 31 = 0)
-  return (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-}
-__host__ __device__ constexpr uint32_t idesc_bf16(int bn) {
-  // D = f32 (1 in [4,6)); A, B = bf16 (1)
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-}
-
-__device__ __forceinline__ void report(int32_t* status, volatile int* abort_flag, int32_t code) {
-  *abort_flag = 1;
-  if (status) atomicCAS(status, 0, code);
-}
-
-// ---- epilogue arithmetic for one 32-column chunk of one accumulator row -----------------------------
-
-template <typename TD> struct EpilogueCtx {
-  const GemmParams* p;
-  uint8_t* staging;      // 2 KiB of shared memory owned by this warp
-  int64_t row0;          // first of the warp's 32 rows; lane l holds row0 + l
-  float g, c0, c1;
-};
-
-// Lane l arrives with 32 consecutive columns of row row0 + l.  Stored straight from there, one
-// 16-byte store instruction would touch 32 different rows; instead the warp turns the chunk
-// through shared memory (64-byte rows, 16-byte pieces XOR-swizzled by the row so that neither side
-// has bank conflicts) and every store instruction writes 64 contiguous bytes of 8 rows.
-template <typename TD>
-__device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uint32_t (&r)[32], int64_t col0) {
-  const GemmParams& p = *ctx.p;
-  const int lane = threadIdx.x & 31;
-  const int64_t row = ctx.row0 + lane;
-  if (ctx.row0 >= p.M || col0 >= p.N) return;          // warp-uniform
-  const bool live = row < p.M;
-  float v[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ctx.g;
-  const bool full_chunk = col0 + 32 <= p.N;
-  if (p.rvec0) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(ctx.c0, __ldg(p.rvec0 + col0 + i), v[i]);
-  }
-  if (p.rvec1) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(ctx.c1, __ldg(p.rvec1 + col0 + i), v[i]);
-  }
-  const TD* src = (p.c && live) ? static_cast<const TD*>(p.c) + row * p.ldc + col0 : nullptr;
-  if (full_chunk) {
-    const int own_swz = (lane >> 1) & 3;
-    if constexpr (sizeof(TD) == 2) {
-      if (src) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 w = __ldg(reinterpret_cast<const uint4*>(src) + i);
-          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) { v[8 * i + 2 * k] += bf16_lo(ww[k]); v[8 * i + 2 * k + 1] += bf16_hi(ww[k]); }
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        __nv_bfloat162 o[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(v[8 * k + 2 * e], v[8 * k + 2 * e + 1]);
-        *reinterpret_cast<uint4*>(ctx.staging + lane * 64 + ((k ^ own_swz) << 4)) = *reinterpret_cast<uint4*>(o);
-      }
-      __syncwarp();
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int rl = 8 * i + (lane >> 2), j = lane & 3;
-        const uint4 w = *reinterpret_cast<const uint4*>(ctx.staging + rl * 64 + ((j ^ ((rl >> 1) & 3)) << 4));
-        if (ctx.row0 + rl < p.M)
-          *reinterpret_cast<uint4*>(static_cast<TD*>(p.d) + (ctx.row0 + rl) * p.ldd + col0 + j * 8) = w;
-      }
-      __syncwarp();
-    } else {
-      if (src) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 w = __ldg(reinterpret_cast<const float4*>(src) + i);
-          v[4 * i] += w.x; v[4 * i + 1] += w.y; v[4 * i + 2] += w.z; v[4 * i + 3] += w.w;
-        }
-      }
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {                     // 16 columns = 64 bytes per row at a time
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          *reinterpret_cast<float4*>(ctx.staging + lane * 64 + ((k ^ own_swz) << 4)) =
-              make_float4(v[16 * h + 4 * k], v[16 * h + 4 * k + 1], v[16 * h + 4 * k + 2], v[16 * h + 4 * k + 3]);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int rl = 8 * i + (lane >> 2), j = lane & 3;
-          const float4 w = *reinterpret_cast<const float4*>(ctx.staging + rl * 64 + ((j ^ ((rl >> 1) & 3)) << 4));
-          if (ctx.row0 + rl < p.M)
-            *reinterpret_cast<float4*>(static_cast<TD*>(p.d) + (ctx.row0 + rl) * p.ldd + col0 + 16 * h + j * 4) = w;
-        }
-        __syncwarp();
-      }
-    }
-  } else if (live) {
-    TD* dst = static_cast<TD*>(p.d) + row * p.ldd + col0;
-    for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-      float o = v[i];
-      if constexpr (sizeof(TD) == 2) {
-        if (src) o += __bfloat162float(src[i]);
-        dst[i] = __float2bfloat16_rn(o);
-      } else {
-        if (src) o += src[i];
-        dst[i] = o;
-      }
-    }
-  }
-}
 
 // ---- the kernel ---------------------------------------------------------------------------------------
 
@@ -557,6 +339,9 @@ static int32_t launch_gemm(const metis_gemm_args* a, const CUtensorMap& ma, cons
   return METIS_OK;
 }
 
+int32_t launch_gemm_pair(const metis_gemm_args* a, const CUtensorMap& ma, const CUtensorMap& mb,
+                         const CUtensorMap& mt, const CUtensorMap& mu, const GemmParams& p);   // gemm_tcgen05_pair.cu
+
 }  // namespace metis
 
 using namespace metis;
@@ -581,15 +366,18 @@ extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
       return fail(METIS_ERR_BAD_ALIGNMENT, "lr_t and lr_u must be 16-byte aligned with leading dimensions that are multiples of 8");
   }
   if ((a->cvec0 && !a->rvec0) || (a->cvec1 && !a->rvec1)) return fail(METIS_ERR_BAD_ARGUMENT, "a cvec needs its rvec");
-  if (a->reserved & ~(kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad)) return fail(METIS_ERR_BAD_ARGUMENT, "reserved must be 0");
+  if (a->reserved & ~kDebugMask) return fail(METIS_ERR_BAD_ARGUMENT, "reserved must be 0");
 
   const int bn = (a->N > 128) ? 256 : 128;
+  // CTA pairs (256 x 256 tiles) whenever there is more than one 128-row block of each operand
+  const bool pair = bn == 256 && a->M > 128 && !(a->reserved & kDebugSingleCta);
+  const int b_box = pair ? 128 : bn;       // rows of B (and U) one CTA loads per stage
   CUtensorMap ma, mb, mt, mu;
   if (int32_t rc = make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->a_codes, a->K / 2, a->M, a->K / 2, kBKBytes, kBM, "A")) return rc;
-  if (int32_t rc = make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b_codes, a->K / 2, a->N, a->K / 2, kBKBytes, bn, "B")) return rc;
+  if (int32_t rc = make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b_codes, a->K / 2, a->N, a->K / 2, kBKBytes, b_box, "B")) return rc;
   if (a->rank > 0) {
     if (int32_t rc = make_map(&mt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->lr_t, a->rank, a->M, a->ldt * 2, 64, kBM, "T")) return rc;
-    if (int32_t rc = make_map(&mu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->lr_u, a->rank, a->N, a->ldu * 2, 64, bn, "U")) return rc;
+    if (int32_t rc = make_map(&mu, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->lr_u, a->rank, a->N, a->ldu * 2, 64, b_box, "U")) return rc;
   } else {
     mt = ma;
     mu = mb;
@@ -600,6 +388,7 @@ extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
   p.alpha = a->alpha;
   p.cvec0 = a->cvec0; p.rvec0 = a->rvec0; p.cvec1 = a->cvec1; p.rvec1 = a->rvec1;
   p.c = a->c; p.ldc = a->ldc; p.d = a->d; p.ldd = a->ldd; p.status = a->status;
+  if (pair) return launch_gemm_pair(a, ma, mb, mt, mu, p);
   if (bn == 256) {
     if (a->d_dtype == METIS_DTYPE_BF16) return launch_gemm<256, __nv_bfloat16>(a, ma, mb, mt, mu, p);
     return launch_gemm<256, float>(a, ma, mb, mt, mu, p);

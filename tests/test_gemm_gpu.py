@@ -63,6 +63,33 @@ def test_fused_low_rank_product(M, N, K, rank):
     assert rel_l2(got, want) <= 1e-5, rel_l2(got, want)
 
 
+@pytest.mark.parametrize("single_cta", [False, True])
+def test_more_tiles_than_sms_ragged_edges_and_rank(single_cta):
+    # every persistent CTA (or CTA pair) walks several tiles, so accumulator hand-over, stage ring
+    # and scale buffers wrap many times, with rank iterations between the tiles; _debug=8 forces
+    # the single-CTA kernel where the dispatcher would take CTA pairs
+    M, N, K, rank = 2344, 4872, 512, 64
+    qa, qb, da, db = operands(M, N, K, seed=11)
+    g = torch.Generator().manual_seed(3)
+    t = (torch.randn(M, rank, generator=g) * 3).to(torch.bfloat16)
+    u = (torch.randn(N, rank, generator=g) / rank ** 0.5).to(torch.bfloat16)
+    scale = float(qa.unit.item()) * float(qb.unit.item())
+    t_acc = (t.float() / scale).to(torch.bfloat16)
+    want = O.gemm_reference(da, db) + ((t_acc.float().numpy() * scale) @ u.float().numpy().T)
+    dbg = 8 if single_cta else 0
+    got = run(qa, qb, lowrank=(t_acc.to(DEV), u.to(DEV)), out_dtype=torch.float32, _debug=dbg).cpu().numpy()
+    assert rel_l2(got, want) <= 1e-5, rel_l2(got, want)
+    got16 = run(qa, qb, lowrank=(t_acc.to(DEV), u.to(DEV)), out_dtype=torch.bfloat16, _debug=dbg).float().cpu().numpy()
+    assert rel_l2(got16, torch.from_numpy(want).to(torch.bfloat16).float().numpy()) <= TOL
+
+
+@pytest.mark.parametrize("M,N,K", [(384, 512, 1024), (130, 264, 96), (1024, 1536, 4096)])
+def test_single_cta_kernel_where_pairs_would_run(M, N, K):
+    qa, qb, da, db = operands(M, N, K, seed=M + N + K)
+    got = run(qa, qb, out_dtype=torch.float32, _debug=8).cpu().numpy()
+    assert rel_l2(got, O.gemm_reference(da, db)) <= 1e-5
+
+
 def test_rank1_terms_bias_and_addend():
     M, N, K = 260, 392, 768
     qa, qb, da, db = operands(M, N, K, seed=77)
@@ -115,10 +142,11 @@ def test_backward_products_through_the_transposed_quantizer():
     assert rel_l2(dw, want) <= 1e-5
 
 
-def test_a_wait_that_cannot_complete_reports_a_status_and_leaves_the_context_usable():
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (512, 512, 512)])      # single CTA; CTA pairs
+def test_a_wait_that_cannot_complete_reports_a_status_and_leaves_the_context_usable(M, N, K):
     # debug knob: the producer arms the first stage for bytes it never requests, so the consumer's
     # bounded wait runs out; the kernel must return with a status instead of spinning.
-    qa, qb, da, db = operands(128, 128, 256, seed=9)
+    qa, qb, da, db = operands(M, N, K, seed=9)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     ops.nvfp4_gemm(qa, qb, status=status, out_dtype=torch.float32, _debug=1)
     torch.cuda.synchronize()
