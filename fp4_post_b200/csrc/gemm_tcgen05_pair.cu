@@ -7,15 +7,15 @@
 // instead of the 54 KiB of the single-CTA kernel, for the same 512 tensor-pipe cycles: the operand
 // feed (L2 -> shared memory, and shared memory -> tensor core) is what bounds the single-CTA kernel.
 //
-// Roles per CTA (192 threads): warp 0 TMA producer, warp 1 tensor-core issuer (leader only),
-// warps 2-5 epilogue.  The scale tiles travel shared memory -> tensor memory by tcgen05.cp issued
+// Roles per CTA (320 threads): warp 0 TMA producer, warp 1 tensor-core issuer (leader only),
+// warps 2-9 epilogue (two warps per 32-lane quarter of tensor memory, alternate column chunks).  The scale tiles travel shared memory -> tensor memory by tcgen05.cp issued
 // by the leader in front of each stage's MMAs: one instruction copies in both CTAs, in pipe order
 // with the MMAs, so no cross-SM handshake sits inside the pipeline loop (a handshake through the
 // peer costs a cluster round trip of more than a thousand cycles per two stages).
 //   full[s]      leader's: all bytes of stage s of BOTH CTAs (the peer's TMA loads signal it remotely)
 //   empty[s]     local: stage s consumed (commit multicast by the leader to both CTAs)
 //   acc_full     local: accumulator complete (commit multicast)
-//   acc_release  leader's: 8 epilogue warps (4 remote arrivals) have drained the shared accumulator columns
+//   acc_release  leader's: 16 epilogue warps (8 remote arrivals) have drained the shared accumulator columns
 // No copy is multicast.  Every wait is bounded; both CTAs meet at a cluster barrier before they
 // free tensor memory, so neither exits while the other can still signal or read it.
 #include "gemm_common.cuh"
@@ -32,9 +32,9 @@ struct PairCfg {
   static constexpr int kSfaBytes = 4 * 512;               // scales of this CTA's rows of A
   static constexpr int kSfbBytes = 2 * 4 * 512;           // scales of all 256 rows of B
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 38 KiB
-  static constexpr int kStagingBytes = 4 * 2048;
+  static constexpr int kStagingBytes = 8 * 2048;           // epilogue: 32 rows x 64 bytes for each of 8 warps
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
-  static constexpr int kThreads = 192;
+  static constexpr int kThreads = 320;
 };
 
 // ---- cluster plumbing ------------------------------------------------------------------------------------
@@ -154,7 +154,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(acc_full, 1);
-    mbar_init(acc_release, 8);
+    mbar_init(acc_release, 16);
     mbar_init(drain, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -303,13 +303,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       __syncwarp();
     }
   } else {
-    // ===== epilogue (both CTAs): warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 =====
+    // ===== epilogue (both CTAs): warps 2..9; warp w owns tensor-memory lanes 32*(w%4) .. +31 and,
+    // of the 8 column chunks taken in drain order, those with index (w-2)/4, +2, +4, +6 =====
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const uint32_t release_leader = map_to_cta(smem_u32(acc_release), 0);
     EpilogueCtx<TD> ctx;
     ctx.g = p.alpha * __ldg(p.a_unit) * __ldg(p.b_unit);
     ctx.p = &p;
-    ctx.staging = staging + q * 2048;
+    ctx.staging = staging + (warp - 2) * 2048;
     uint32_t local_tile = 0;
     for (int64_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
       const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
@@ -326,29 +328,32 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       tc_fence_after();
       const uint32_t odd = local_tile & 1u;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + odd * Cfg::kAccStride;
+      // drain order: the 3 chunks shared with the other accumulator first.  For the even
+      // accumulator [0,256) they are its last chunks, for the odd one [160,416) its first ones.
       constexpr int kChunks = BN / 32;
-      constexpr int kShared = Cfg::kSharedChunks;
-      const int first_chunk = !odd ? kChunks - kShared : 0;
-      {
-        uint32_t rs[kShared][32];
+      const int first_chunk = !odd ? kChunks - Cfg::kSharedChunks : 0;
+      int ch[4];
 #pragma unroll
-        for (int s = 0; s < kShared; ++s) tc_load32(t_row + (first_chunk + s) * 32, rs[s]);
-        tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(release_leader);
-#pragma unroll
-        for (int s = 0; s < kShared; ++s) emit_chunk<TD>(ctx, rs[s], n0 + (first_chunk + s) * 32);
-      }
-#pragma unroll 1
-      for (int step = kShared; step < kChunks; ++step) {
-        int ch = first_chunk + step;
-        if (ch >= kChunks) ch -= kChunks;
-        uint32_t r[32];
-        tc_load32(t_row + ch * 32, r);
-        tc_wait_ld();
-        emit_chunk<TD>(ctx, r, n0 + ch * 32);
-      }
+      for (int k = 0; k < 4; ++k) ch[k] = (first_chunk + half + 2 * k) & (kChunks - 1);
+      // this warp's first two chunks cover its part of the shared columns (drain index 0 and 2,
+      // or 1): pull them into registers and hand the columns to the next tile's MMAs at once
+      uint32_t ra[32], rb[32];
+      tc_load32(t_row + ch[0] * 32, ra);
+      tc_load32(t_row + ch[1] * 32, rb);
+      tc_wait_ld(ra);
+      tc_wait_ld(rb);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(release_leader);
+      // the other two loads fly while the first two chunks are scaled and stored
+      emit_chunk<TD>(ctx, ra, n0 + ch[0] * 32);
+      tc_load32(t_row + ch[2] * 32, ra);
+      emit_chunk<TD>(ctx, rb, n0 + ch[1] * 32);
+      tc_load32(t_row + ch[3] * 32, rb);
+      tc_wait_ld(ra);
+      tc_wait_ld(rb);
+      emit_chunk<TD>(ctx, ra, n0 + ch[2] * 32);
+      emit_chunk<TD>(ctx, rb, n0 + ch[3] * 32);
       tc_fence_before();
     }
   }
