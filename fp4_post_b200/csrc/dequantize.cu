@@ -61,6 +61,23 @@ __device__ __forceinline__ int twice_e2m1(uint32_t nib) {
   return (nib & 8u) ? -mag : mag;
 }
 
+// Sum of the 16 signed codes of one block, in half units.  prmt looks four codes up at once in the
+// 8-entry magnitude table {0,1,2,3,4,6,8,12}; a selector nibble with bit 3 set yields the sign
+// replica of the table byte, i.e. zero, so the first look-up keeps the positive codes and the second
+// (sign bits flipped) the negative ones.  Byte sums stay below 256, one dp4a adds the four bytes.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ int block_code_sum(uint2 w) {
+  constexpr uint32_t kLo = 0x03020100u, kHi = 0x0C080604u;
+  const uint32_t nx = w.x ^ 0x88888888u, ny = w.y ^ 0x88888888u;
+  const uint32_t pos = prmt(kLo, kHi, w.x) + prmt(kLo, kHi, w.x >> 16) + prmt(kLo, kHi, w.y) + prmt(kLo, kHi, w.y >> 16);
+  const uint32_t neg = prmt(kLo, kHi, nx) + prmt(kLo, kHi, nx >> 16) + prmt(kLo, kHi, ny) + prmt(kLo, kHi, ny >> 16);
+  return __dp4a(pos, 0x01010101u, 0u) - __dp4a(neg, 0x01010101u, 0u);
+}
+
 template <bool kHasV>
 __global__ void __launch_bounds__(256)
 gemv_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
@@ -73,6 +90,20 @@ gemv_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
   const int64_t tiles = sf_tiles_per_row(C);
   const uint2* row_codes = codes + row * sf_cols;
   float acc = 0.0f;
+  if (!kHasV && sf_layout == METIS_SF_MMA && (sf_cols & 3) == 0) {
+    // row sums: four blocks per lane and trip (two 16-byte loads of codes, the four scale bytes
+    // are one aligned word of the tile layout)
+#pragma unroll 2
+    for (int64_t g = lane; g < (sf_cols >> 2); g += 32) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(row_codes + 4 * g));
+      const uint4 b = __ldg(reinterpret_cast<const uint4*>(row_codes + 4 * g) + 1);
+      const uint32_t s4 = __ldg(reinterpret_cast<const uint32_t*>(scales + sf_mma_offset(row, 4 * g, tiles)));
+      acc = fmaf((float)block_code_sum(make_uint2(a.x, a.y)), e4m3_to_float(s4 & 0xFFu), acc);
+      acc = fmaf((float)block_code_sum(make_uint2(a.z, a.w)), e4m3_to_float((s4 >> 8) & 0xFFu), acc);
+      acc = fmaf((float)block_code_sum(make_uint2(b.x, b.y)), e4m3_to_float((s4 >> 16) & 0xFFu), acc);
+      acc = fmaf((float)block_code_sum(make_uint2(b.z, b.w)), e4m3_to_float(s4 >> 24), acc);
+    }
+  } else
 #pragma unroll 4
   for (int64_t k = lane; k < sf_cols; k += 32) {
     const uint2 w2 = __ldg(row_codes + k);
@@ -93,10 +124,7 @@ gemv_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
         part = fmaf((float)twice_e2m1(n4 >> 12), f.w, part);
       }
     } else {
-      int isum = 0;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) isum += twice_e2m1(w[i >> 3] >> (4 * (i & 7)));
-      part = (float)isum;
+      part = (float)block_code_sum(w2);
     }
     acc = fmaf(part, sc, acc);
   }

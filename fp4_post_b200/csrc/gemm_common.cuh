@@ -146,6 +146,27 @@ template <typename TD> struct EpilogueCtx {
   float g, c0, c1;
 };
 
+// v[i] += c * rvec[col0 + i] for the 32 columns of a chunk (128-bit loads when the chunk is whole
+// and the vector 16-byte aligned; every lane reads the same addresses)
+__device__ __forceinline__ void add_rank1(float (&v)[32], const float* __restrict__ rvec, float c, int64_t col0,
+                                          int64_t N, bool full_chunk) {
+  if (!rvec) return;
+  if (full_chunk && (reinterpret_cast<uintptr_t>(rvec) & 15u) == 0) {
+    const float4* r4 = reinterpret_cast<const float4*>(rvec + col0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 f = __ldg(r4 + i);
+      v[4 * i] = fmaf(c, f.x, v[4 * i]);
+      v[4 * i + 1] = fmaf(c, f.y, v[4 * i + 1]);
+      v[4 * i + 2] = fmaf(c, f.z, v[4 * i + 2]);
+      v[4 * i + 3] = fmaf(c, f.w, v[4 * i + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < N) v[i] = fmaf(c, __ldg(rvec + col0 + i), v[i]);
+  }
+}
+
 // Lane l arrives with 32 consecutive columns of row row0 + l.  Stored straight from there, one
 // 16-byte store instruction would touch 32 different rows; instead the warp turns the chunk
 // through shared memory (64-byte rows, 16-byte pieces XOR-swizzled by the row so that neither side
@@ -161,14 +182,8 @@ __device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uin
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ctx.g;
   const bool full_chunk = col0 + 32 <= p.N;
-  if (p.rvec0) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(ctx.c0, __ldg(p.rvec0 + col0 + i), v[i]);
-  }
-  if (p.rvec1) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) if (full_chunk || col0 + i < p.N) v[i] = fmaf(ctx.c1, __ldg(p.rvec1 + col0 + i), v[i]);
-  }
+  add_rank1(v, p.rvec0, ctx.c0, col0, p.N, full_chunk);
+  add_rank1(v, p.rvec1, ctx.c1, col0, p.N, full_chunk);
   const TD* src = (p.c && live) ? static_cast<const TD*>(p.c) + row * p.ldc + col0 : nullptr;
   if (full_chunk) {
     const int own_swz = (lane >> 1) & 3;

@@ -368,7 +368,10 @@ extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
   if ((a->cvec0 && !a->rvec0) || (a->cvec1 && !a->rvec1)) return fail(METIS_ERR_BAD_ARGUMENT, "a cvec needs its rvec");
   if (a->reserved & ~kDebugMask) return fail(METIS_ERR_BAD_ARGUMENT, "reserved must be 0");
 
-  const int bn = (a->N > 128) ? 256 : 128;
+  int bn = (a->N > 128) ? 256 : 128;
+  // one row block of A and few column tiles (the weight gradient of a rank-r factor): narrower
+  // tiles put twice as many SMs to work, which matters more than the MMA shape there
+  if (bn == 256 && a->M <= 128 && ceil_div(a->N, 256) * 2 <= device_sm_count()) bn = 128;
   // CTA pairs (256 x 256 tiles) whenever there is more than one 128-row block of each operand
   const bool pair = bn == 256 && a->M > 128 && !(a->reserved & kDebugSingleCta);
   const int b_box = pair ? 128 : bn;       // rows of B (and U) one CTA loads per stage
