@@ -325,7 +325,15 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
   const int by = kQuantThreads / bx;
   const int gx = (bpr + bx - 1) / bx;
   int64_t gy = ceil_div(rows, by);
-  const int64_t cap = ceil_div((int64_t)sm_count() * 16, gx);   // ~16 CTAs per SM in total (swept 3..32: flat above 6)
+  // four waves of resident CTAs (grid-stride over the rows): whole waves leave no tail
+  int per_sm = 0;
+#define METIS_OCC_ROWS(MEAN, SR) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_rows_kernel<T, MEAN, SR>, kQuantThreads, 0)
+  if (mean) { if (sr) METIS_OCC_ROWS(true, true); else METIS_OCC_ROWS(true, false); }
+  else      { if (sr) METIS_OCC_ROWS(false, true); else METIS_OCC_ROWS(false, false); }
+#undef METIS_OCC_ROWS
+  if (per_sm < 1) per_sm = 1;
+  int64_t cap = (int64_t)sm_count() * per_sm * 4 / gx;
+  if (cap < 1) cap = 1;
   if (gy > cap) gy = cap;
   if (gy > 65535) gy = 65535;
   if (gy < 1) gy = 1;

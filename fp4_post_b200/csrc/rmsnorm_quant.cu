@@ -31,6 +31,7 @@ rmsnorm_quantize_kernel(const TX* __restrict__ x, int rows, int blocks_per_row, 
   // The product normalised(x) * gamma has the promoted dtype: bf16 only if both are bf16.
   constexpr bool kProductBf16 = (sizeof(TX) == 2) && (sizeof(TG) == 2);
   __shared__ float s_red[kNormThreads / 32];
+  __shared__ float s_rs[kNormThreads / 32];        // reciprocal RMS of each row in flight (rows span >= 1 warp here)
   const int bx = blockDim.x, by = blockDim.y;
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int tid = ty * bx + tx;
@@ -39,6 +40,19 @@ rmsnorm_quantize_kernel(const TX* __restrict__ x, int rows, int blocks_per_row, 
   const int warps_per_row = bx >> 5;                 // 0 when a warp holds several rows
   const float n_cols = (float)(blocks_per_row * 16);
   float running = 0.0f;
+
+  // The row after the current one is already on its way from HBM while the current one is reduced,
+  // normalised and quantized: its blocks wait in registers as loaded.
+  RawBlock<TX> raw[kBlocks];
+  auto fetch = [&](int r_first) {
+    const int r = r_first + ty;
+#pragma unroll
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (r < rows && bc < blocks_per_row) raw[j].load(x + (int64_t)r * ld + (int64_t)bc * 16);
+    }
+  };
+  fetch(blockIdx.x * by);
 
   for (int r0 = blockIdx.x * by; r0 < rows; r0 += gridDim.x * by) {
     const int r = r0 + ty;
@@ -49,43 +63,68 @@ rmsnorm_quantize_kernel(const TX* __restrict__ x, int rows, int blocks_per_row, 
     for (int j = 0; j < kBlocks; ++j) {
       const int bc = tx + j * bx;
       if (row_live && bc < blocks_per_row) {
-        Load16<TX>::load(x + (int64_t)r * ld + (int64_t)bc * 16, v[j]);
+        raw[j].unpack(v[j]);
 #pragma unroll
         for (int i = 0; i < 16; ++i) ss = __fmaf_rn(v[j][i], v[j][i], ss);
       }
     }
+    fetch(r0 + gridDim.x * by);
     for (int o = seg >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    float tot = ss;
+    // x * rsqrt(mean(x^2) + eps) with the IEEE operations the CPU reference uses: correctly
+    // rounded division, square root and reciprocal (llama.py:23-24).  The sequence is some 50
+    // instructions, so one thread per row runs it and the others pick the result up.
+    float rs;
     if (warps_per_row > 1) {                           // uniform over the CTA
       if (lane == 0) s_red[warp] = ss;
       __syncthreads();
-      tot = 0.0f;
-      for (int w = 0; w < warps_per_row; ++w) tot += s_red[ty * warps_per_row + w];
-      __syncthreads();                                 // s_red is rewritten by the next row
+      if (tx == 0) {
+        float tot = 0.0f;
+        for (int w = 0; w < warps_per_row; ++w) tot += s_red[ty * warps_per_row + w];
+        s_rs[ty] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, n_cols), eps)));
+      }
+      __syncthreads();                                 // also: s_red may be rewritten by the next row
+      rs = s_rs[ty];
+    } else {
+      rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, n_cols), eps)));   // every lane of the row holds the sum
     }
-    // x * rsqrt(mean(x^2) + eps) with the IEEE operations the CPU reference uses:
-    // correctly rounded division, square root and reciprocal (llama.py:23-24).
-    const float rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, n_cols), eps)));
 
 #pragma unroll
     for (int j = 0; j < kBlocks; ++j) {
       const int bc = tx + j * bx;
       if (!(row_live && bc < blocks_per_row)) continue;
-      float g[16];
-      Load16<TG>::load(gamma + (int64_t)bc * 16, g);
       float y[16];
+      float a;
+      if constexpr (kProductBf16) {
+        // both roundings of the reference in packed bf16: n = bf16(x * rs) (llama.py:28), then
+        // n * gamma as one bf16x2 multiply: the product of two bf16 is exact in fp32, so rounding
+        // it once to bf16 is what the fp32 multiply followed by the conversion gives (llama.py:31)
+        RawBlock<__nv_bfloat16> graw;
+        graw.load(reinterpret_cast<const __nv_bfloat16*>(gamma) + (int64_t)bc * 16);
+        const uint32_t gw[8] = {graw.a.x, graw.a.y, graw.a.z, graw.a.w, graw.b.x, graw.b.y, graw.b.z, graw.b.w};
+        __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.0f, 0.0f);
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        float n0 = __fmul_rn(v[j][i], rs), n1 = __fmul_rn(v[j][i + 1], rs);
-        if (sizeof(TX) == 2) round_bf16x2(n0, n1);                      // .type_as(x), llama.py:28
-        float p0 = __fmul_rn(n0, g[i]), p1 = __fmul_rn(n1, g[i + 1]);   // * weight, llama.py:31
-        if (kProductBf16) round_bf16x2(p0, p1);
-        y[i] = p0;
-        y[i + 1] = p1;
+        for (int i = 0; i < 8; ++i) {
+          const __nv_bfloat162 n2 = __floats2bfloat162_rn(__fmul_rn(v[j][2 * i], rs), __fmul_rn(v[j][2 * i + 1], rs));
+          const __nv_bfloat162 p2 = __hmul2(n2, *reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+          amax2 = __hmax2(amax2, __habs2(p2));
+          const uint32_t w = *reinterpret_cast<const uint32_t*>(&p2);
+          y[2 * i] = bf16_lo(w);
+          y[2 * i + 1] = bf16_hi(w);
+        }
+        const uint32_t aw = *reinterpret_cast<const uint32_t*>(&amax2);
+        a = fmaxf(bf16_lo(aw), bf16_hi(aw));
+      } else {
+        float g[16];
+        Load16<TG>::load(gamma + (int64_t)bc * 16, g);
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          float n0 = __fmul_rn(v[j][i], rs), n1 = __fmul_rn(v[j][i + 1], rs);
+          if (sizeof(TX) == 2) round_bf16x2(n0, n1);                      // .type_as(x), llama.py:28
+          y[i] = __fmul_rn(n0, g[i]);                                     // * weight, llama.py:31
+          y[i + 1] = __fmul_rn(n1, g[i + 1]);
+        }
+        a = abs_max16(y);
       }
-      float a = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) a = fmaxf(a, fabsf(y[i]));
       uint32_t packed[2];
       quantize_rn<2>(y, block_scale_from_amax(a), packed);
       const int64_t b = (int64_t)r * blocks_per_row + bc;
@@ -117,7 +156,12 @@ template <typename TX, typename TG, int kBlocks>
 static void launch_norm(const TX* x, int64_t rows, int bpr, int bx, int64_t ld, const TG* gamma, float eps,
                         uint32_t* codes, const WorkspaceView& ws, void* norm_out, int sms, cudaStream_t st) {
   const int by = kNormThreads / bx;
-  int64_t blocks = (int64_t)sms * (kBlocks <= 1 ? 6 : (kBlocks <= 2 ? 4 : 2));
+  // persistent CTAs: exactly as many as are resident at once, so that all of them finish together
+  int per_sm = 0;
+  if (norm_out) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_quantize_kernel<TX, TG, kBlocks, true>, kNormThreads, 0);
+  else          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_quantize_kernel<TX, TG, kBlocks, false>, kNormThreads, 0);
+  if (per_sm < 1) per_sm = 1;
+  int64_t blocks = (int64_t)sms * per_sm;
   const int64_t need = ceil_div(rows, by);
   if (blocks > need) blocks = need;
   const dim3 b((unsigned)bx, (unsigned)by);
