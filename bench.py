@@ -172,6 +172,44 @@ def workload_config(n_gpus):
 
 # ---- one kernel alone -----------------------------------------------------------------------------------------
 
+GEMM_SWEEP = [(M, N, K) for (N, K) in ((4096, 4096), (14336, 4096), (4096, 14336)) for M in (16, 128, 4096, 16384)]
+
+
+def run_gemm_sweep(args):
+    """`--only gemm_sweep`: the GEMM shape grid (decode to training token counts, square and MLP shapes),
+    each with and without the fused rank-128 product; one JSON line per shape."""
+    import torch
+    from fp4_post_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    for M, N, K in GEMM_SWEEP:
+        qa = ops.nvfp4_quantize(torch.randn(M, K, device=dev, dtype=torch.bfloat16))
+        qb = ops.nvfp4_quantize(torch.randn(N, K, device=dev, dtype=torch.bfloat16) / K ** 0.5)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        line = {"only": "gemm_sweep", "M": M, "N": N, "K": K}
+        for rank in (0, args.rank):
+            lr = None
+            if rank:
+                lr = (torch.randn(M, rank, device=dev, dtype=torch.bfloat16), torch.randn(N, rank, device=dev, dtype=torch.bfloat16))
+            fn = lambda: ops.nvfp4_gemm(qa, qb, lowrank=lr, out=out)
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            key = f"r{rank}"
+            line[key + "_us"] = round(ms * 1e3, 2)
+            line[key + "_tflops"] = round(2 * M * N * (K + rank) / ms / 1e9, 1)
+            # operand + output bytes: what a decode-sized product is bound by
+            line[key + "_gbs"] = round((M * K * 0.5625 + N * K * 0.5625 + M * N * 2 + rank * (M + N) * 2) / ms / 1e6, 1)
+        print(json.dumps(line), flush=True)
+
+
 def run_single_kernel(args):
     """`--only K`: a few launches of one kernel on [rows, cols] bf16 (GEMM: M = rows, K = cols, N = n),
     timed with CUDA events.  Small enough to sit under an ncu capture."""
@@ -219,7 +257,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
@@ -228,6 +266,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.only == "gemm_sweep":
+        return run_gemm_sweep(args)
     if args.only:
         return run_single_kernel(args)
 

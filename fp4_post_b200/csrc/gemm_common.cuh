@@ -60,6 +60,19 @@ struct GemmParams {
   int32_t* status;
 };
 
+// Tile order: bands of `group` row tiles; inside a band the row tile runs fastest, then the column
+// tile.  The CTAs that run at the same time then share a few A row panels and walk the B column
+// panels together, so both stay in L2 whatever M, N and K are (row tile fastest over the whole of M
+// re-reads all of A from HBM once per column tile as soon as A outgrows L2).
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int group, int64_t& tm, int64_t& tn) {
+  const int64_t per_band = (int64_t)group * tiles_n;
+  const int64_t band = tile / per_band, in_band = tile - band * per_band;
+  const int64_t first = band * group;
+  const int64_t rows = tiles_m - first < group ? tiles_m - first : group;
+  tn = in_band / rows;
+  tm = first + (in_band - tn * rows);
+}
+
 // ---- PTX wrappers ---------------------------------------------------------------------------------
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

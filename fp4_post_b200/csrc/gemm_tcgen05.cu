@@ -84,7 +84,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full_base = smem_u32(full);
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
+      int64_t tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, 16, tm, tn);
       const int32_t m0 = (int32_t)(tm * kBM), n0 = (int32_t)(tn * BN);
       // scale tiles: 4 per stage (2 KiB) and per 128 rows, contiguous along K; those of B exist
       // only for whole 128-row blocks of N
@@ -266,7 +267,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     ctx.staging = staging + q * 2048;
     uint32_t local_tile = 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
-      const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
+      int64_t tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, 16, tm, tn);
       const int64_t row = tm * kBM + q * 32 + lane;
       const int64_t n0 = tn * BN;
       ctx.row0 = tm * kBM + q * 32;

@@ -180,7 +180,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t full_local = smem_u32(full);
     const uint32_t full_leader = map_to_cta(full_local, 0);
     for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-      const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
+      int64_t tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, 8, tm, tn);
       const int32_t m0 = (int32_t)(tm * 2 * kBM + cta * kBM);         // this CTA's rows of A
       const int32_t n0 = (int32_t)(tn * BN);
       const int32_t nb0 = n0 + (int32_t)cta * 128;                    // this CTA's rows of B
@@ -314,7 +315,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     ctx.staging = staging + (warp - 2) * 2048;
     uint32_t local_tile = 0;
     for (int64_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
-      const int64_t tm = tile % tiles_m, tn = tile / tiles_m;
+      int64_t tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, 8, tm, tn);
       const int64_t row0 = tm * 2 * kBM + cta * kBM + q * 32;
       const int64_t row = row0 + lane;
       const int64_t n0 = tn * BN;
