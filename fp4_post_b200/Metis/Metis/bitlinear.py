@@ -445,6 +445,9 @@ class LinearLowbitFunction(torch.autograd.Function):
 
 
 _ONES = {}
+# fp4_post_b200.dp.GradientReducer installs itself here: the fused backward hands it every weight
+# gradient the moment it is final (data-parallel training); None = single process.
+GRADIENT_REDUCER = None
 
 
 def _one(like: torch.Tensor) -> torch.Tensor:
@@ -631,8 +634,11 @@ class MetisFusedFunction(torch.autograd.Function):
         # vlinear and warmup_linear (the residual): quantized backward with grad_output = d_yv and g
         dv = F._pack_centred(d_yv, quantizer, centred)
         dg = F._pack_centred(g, quantizer, centred)
-        grad_v = _packed_dw(dv, xa, M)
+        reducer = GRADIENT_REDUCER
         grad_r = _packed_dw(dg, xa, M)
+        if reducer is not None:
+            reducer.ready(grad_r)           # the big all-reduce starts here and runs beside the dX product
+        grad_v = _packed_dw(dv, xa, M)
         if MetisFusedFunction.fuse_dx_side_product and act == torch.bfloat16 and r <= 256:
             # dX of both branches in ONE launch: D^v @ V^ enters the residual product as a bf16
             # rank-r side product.  e2m1 x e4m3 is exact in bf16; the ratio of the two products'
@@ -647,6 +653,10 @@ class MetisFusedFunction(torch.autograd.Function):
             gx_v = _packed_dx(dv, vq, act)
             gx = _packed_dx(dg, rq, act, addend=gx_v)          # summed in the epilogue
         grad_x = gx.reshape(xa.shape)
+        if reducer is not None:
+            for t in (grad_v, grad_s, grad_u, grad_bias):
+                reducer.ready(t)
+            reducer.flush()
         return grad_x, None, grad_v, None, grad_s, grad_u, grad_r, None, grad_bias
 
 

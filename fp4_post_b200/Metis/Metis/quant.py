@@ -269,10 +269,17 @@ class _NativeNVFP4(BlockQuantFunc):
     def _native_input(cls, x: torch.Tensor) -> torch.Tensor:
         return x if x.dtype in (torch.bfloat16, torch.float32) else x.float()
 
+    _counters = {}          # device -> int64 [1]: the Philox offset of the next stochastic call
+
     @classmethod
-    def _next_offset(cls) -> int:
-        _NativeNVFP4._calls += 1
-        return _NativeNVFP4._calls
+    def _offset_counter(cls, device: torch.device) -> torch.Tensor:
+        """Per-device call counter kept ON the device (like torch's graph-safe Philox offset): every
+        stochastic quantization reads and bumps it, so eager calls and replays of a captured CUDA
+        graph both draw fresh random bits.  Created on first use: run one step before capturing."""
+        ctr = _NativeNVFP4._counters.get(device)
+        if ctr is None:
+            ctr = _NativeNVFP4._counters[device] = torch.ones(1, dtype=torch.int64, device=device)
+        return ctr
 
     @classmethod
     @torch.no_grad()
@@ -282,8 +289,8 @@ class _NativeNVFP4(BlockQuantFunc):
         transpose).  `mean` (fp32 [cols]) is subtracted first and recorded on the result."""
         cls._check(x)
         return ops.nvfp4_quantize(cls._native_input(x), transpose=transpose, stochastic=cls.stochastic,
-                                  seed=cls._seed, offset=cls._next_offset() if cls.stochastic else 0,
-                                  sf_layout=sf_layout, mean=mean)
+                                  seed=cls._seed, sf_layout=sf_layout, mean=mean,
+                                  offset_counter=cls._offset_counter(x.device) if cls.stochastic else None)
 
     @classmethod
     @torch.no_grad()

@@ -40,7 +40,7 @@ static inline WorkspaceView view_workspace(void* ws) {
 }
 // Shared by the stand-alone and the RMSNorm-fused quantizers (defined in quantize.cu).
 int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t sf_layout,
-                        uint8_t* scales, float* unit, cudaStream_t st);
+                        uint8_t* scales, float* unit, cudaStream_t st, uint64_t* offset_ctr = nullptr);
 int32_t check_quant_outputs(int64_t R, int64_t C, int32_t sf_layout, const void* codes,
                             const void* scales, const void* unit, const void* workspace,
                             int64_t workspace_bytes);

@@ -34,8 +34,9 @@ template <typename T, bool kMean, bool kSR>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int64_t ld,
                      const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
-                     uint2* __restrict__ codes, float* __restrict__ amax_out,
+                     const uint64_t* __restrict__ offset_ctr, uint2* __restrict__ codes, float* __restrict__ amax_out,
                      unsigned int* __restrict__ gmax) {
+  if (kSR && offset_ctr) offset += *offset_ctr;             // per-device call counter (graph-safe stream of offsets)
   const int bc = blockIdx.x * blockDim.x + threadIdx.x;     // column block of this thread
   const int row_step = gridDim.y * blockDim.y;
   float running = 0.0f;
@@ -102,7 +103,7 @@ template <typename T, bool kMean, bool kSR>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_cols_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, int64_t cols,
                      const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
-                     uint8_t* __restrict__ codes, float* __restrict__ amax_out,
+                     const uint64_t* __restrict__ offset_ctr, uint8_t* __restrict__ codes, float* __restrict__ amax_out,
                      unsigned int* __restrict__ gmax) {
   using TT = TransposeTile<T>;
   extern __shared__ uint8_t smem_raw[];
@@ -112,6 +113,7 @@ quantize_cols_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, in
   uint64_t* full = reinterpret_cast<uint64_t*>(s_amax + TT::kCols * TT::kRowBlocks);   // [2]
   __shared__ int s_failed;
 
+  if (kSR && offset_ctr) offset += *offset_ctr;
   const int tid = threadIdx.x;
   const int64_t row_tiles = (rows + TT::kRows - 1) / TT::kRows;
   const int64_t col_tiles = (cols + TT::kCols - 1) / TT::kCols;
@@ -211,11 +213,14 @@ quantize_cols_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, in
 __global__ void __launch_bounds__(kQuantThreads)
 finalize_scales_kernel(const float* __restrict__ amax, const unsigned int* __restrict__ gmax,
                        int64_t R, int64_t sf_cols, int32_t sf_layout, uint8_t* __restrict__ scales,
-                       float* __restrict__ unit_out) {
+                       float* __restrict__ unit_out, uint64_t* __restrict__ offset_ctr) {
   const float smax = block_scale_from_amax(__uint_as_float(*gmax));
   // quant.py:21-22; a pass-1 kernel that gave up on a load raises gmax[1]: publish NaN so that it shows
   const float unit = gmax[1] ? __uint_as_float(0x7FC00000u) : __fdiv_rn(smax, 448.0f);
-  if (blockIdx.x == 0 && threadIdx.x == 0) *unit_out = unit;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *unit_out = unit;
+    if (offset_ctr) *offset_ctr += 1;       // pass 1 of this call has finished: the next call draws fresh bits
+  }
   const int64_t elem_cols = sf_cols * 16;
   const int64_t tiles = sf_tiles_per_row(elem_cols);
   const int64_t groups_per_row = (sf_layout == METIS_SF_MMA) ? tiles : (sf_cols + 3) / 4;
@@ -317,7 +322,7 @@ static int sm_count() { return device_sm_count(); }
 
 template <typename T>
 static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
-                        uint64_t seed, uint64_t offset, uint32_t* codes, const WorkspaceView& ws,
+                        uint64_t seed, uint64_t offset, const uint64_t* ctr, uint32_t* codes, const WorkspaceView& ws,
                         cudaStream_t st) {
   const int bpr = (int)(cols >> 4);
   int bx = 1;                                      // threads along the row: a power of two <= 256
@@ -339,7 +344,7 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
   if (gy < 1) gy = 1;
   const dim3 g((unsigned)gx, (unsigned)gy), b((unsigned)bx, (unsigned)by);
 #define METIS_LAUNCH_ROWS(MEAN, SR)                                                              \
-  quantize_rows_kernel<T, MEAN, SR><<<g, b, 0, st>>>(x, (int)rows, bpr, ld, mean, seed, offset,  \
+  quantize_rows_kernel<T, MEAN, SR><<<g, b, 0, st>>>(x, (int)rows, bpr, ld, mean, seed, offset, ctr, \
                                                      reinterpret_cast<uint2*>(codes), ws.amax, ws.gmax)
   if (mean) { if (sr) METIS_LAUNCH_ROWS(true, true); else METIS_LAUNCH_ROWS(true, false); }
   else      { if (sr) METIS_LAUNCH_ROWS(false, true); else METIS_LAUNCH_ROWS(false, false); }
@@ -348,7 +353,7 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
 
 template <typename T>
 static int32_t launch_cols(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
-                           uint64_t seed, uint64_t offset, uint8_t* codes, const WorkspaceView& ws,
+                           uint64_t seed, uint64_t offset, const uint64_t* ctr, uint8_t* codes, const WorkspaceView& ws,
                            cudaStream_t st) {
   using TT = TransposeTile<T>;
   CUtensorMap map;
@@ -362,7 +367,7 @@ static int32_t launch_cols(const T* x, int64_t rows, int64_t cols, int64_t ld, c
   do {                                                                                                      \
     auto kern = quantize_cols_kernel<T, MEAN, SR>;                                                          \
     METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TT::kSmemBytes)); \
-    kern<<<(unsigned)grid, kQuantThreads, TT::kSmemBytes, st>>>(map, rows, cols, mean, seed, offset, codes,  \
+    kern<<<(unsigned)grid, kQuantThreads, TT::kSmemBytes, st>>>(map, rows, cols, mean, seed, offset, ctr, codes, \
                                                                 ws.amax, ws.gmax);                          \
   } while (0)
   if (mean) { if (sr) METIS_LAUNCH_COLS(true, true); else METIS_LAUNCH_COLS(true, false); }
@@ -372,7 +377,7 @@ static int32_t launch_cols(const T* x, int64_t rows, int64_t cols, int64_t ld, c
 }
 
 int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t sf_layout,
-                        uint8_t* scales, float* unit, cudaStream_t st) {
+                        uint8_t* scales, float* unit, cudaStream_t st, uint64_t* offset_ctr) {
   const int64_t sf_cols = C / 16;
   const int64_t groups = (sf_layout == METIS_SF_MMA)
                              ? ceil_div(R, 128) * 128 * sf_tiles_per_row(C)
@@ -382,7 +387,7 @@ int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t s
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   finalize_scales_kernel<<<(unsigned)blocks, kQuantThreads, 0, st>>>(ws.amax, ws.gmax, R, sf_cols,
-                                                                    sf_layout, scales, unit);
+                                                                    sf_layout, scales, unit, offset_ctr);
   METIS_CUDA_OK(cudaGetLastError());
   return METIS_OK;
 }
@@ -427,7 +432,12 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
                                         int64_t workspace_bytes, void* stream) {
   const bool transpose = flags & METIS_Q_TRANSPOSE;
   const bool sr = flags & METIS_Q_STOCHASTIC;
-  if (flags & ~(METIS_Q_TRANSPOSE | METIS_Q_STOCHASTIC)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x", flags);
+  // graph-safe random stream: `offset` carries the address of a device counter instead of a value
+  uint64_t* ctr = (sr && (flags & METIS_Q_OFFSET_ON_DEVICE)) ? reinterpret_cast<uint64_t*>(static_cast<uintptr_t>(offset)) : nullptr;
+  if (ctr) offset = 0;
+  if ((flags & METIS_Q_OFFSET_ON_DEVICE) && (!sr || !ctr || (reinterpret_cast<uintptr_t>(ctr) & 7u)))
+    return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_OFFSET_ON_DEVICE needs METIS_Q_STOCHASTIC and an 8-byte aligned device address in offset");
+  if (flags & ~(METIS_Q_TRANSPOSE | METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x", flags);
   if (!x) return fail(METIS_ERR_BAD_ARGUMENT, "x is null");
   if (x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown x_dtype %d", x_dtype);
   if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)rows, (long long)cols);
@@ -447,19 +457,19 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, 2 * sizeof(unsigned int), st));   // running maximum and error word
   if (!transpose) {
     if (x_dtype == METIS_DTYPE_BF16)
-      launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset,
+      launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr,
                   reinterpret_cast<uint32_t*>(codes), ws, st);
     else
-      launch_rows(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset,
+      launch_rows(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr,
                   reinterpret_cast<uint32_t*>(codes), ws, st);
   } else {
     const int32_t rc = x_dtype == METIS_DTYPE_BF16
-        ? launch_cols(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, codes, ws, st)
-        : launch_cols(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, codes, ws, st);
+        ? launch_cols(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, codes, ws, st)
+        : launch_cols(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, codes, ws, st);
     if (rc) return rc;
   }
   METIS_CUDA_OK(cudaGetLastError());
-  return launch_finalize(ws, R, C, sf_layout, scales, unit, st);
+  return launch_finalize(ws, R, C, sf_layout, scales, unit, st, ctr);
 }
 
 extern "C" int64_t metis_col_mean_workspace_bytes(int64_t rows, int64_t cols) {
@@ -557,9 +567,9 @@ extern "C" int32_t metis_nvfp4_quantize_static(const void* x, int32_t x_dtype, i
   // have to start at zero; every block maximum this call reads back is written by this call first.
   METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, 2 * sizeof(unsigned int), st));   // running maximum and error word
   if (x_dtype == METIS_DTYPE_BF16)
-    launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, nullptr, false, 0, 0, reinterpret_cast<uint32_t*>(codes), ws, st);
+    launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, nullptr, false, 0, 0, nullptr, reinterpret_cast<uint32_t*>(codes), ws, st);
   else
-    launch_rows(static_cast<const float*>(x), rows, cols, ld, nullptr, false, 0, 0, reinterpret_cast<uint32_t*>(codes), ws, st);
+    launch_rows(static_cast<const float*>(x), rows, cols, ld, nullptr, false, 0, 0, nullptr, reinterpret_cast<uint32_t*>(codes), ws, st);
   METIS_CUDA_OK(cudaGetLastError());
   return launch_finalize(ws, rows, cols, sf_layout, scales, unit, st);
 }

@@ -19,6 +19,67 @@ def shard_tokens(batch: torch.Tensor, rank: int, world: int, dim: int = 0) -> to
     return batch.narrow(dim, lo, hi - lo)
 
 
+class GradientReducer:
+    """All-reduce of weight gradients started from INSIDE the backward pass, as soon as each gradient
+    is final, so that the collective of the large residual gradient runs beside the input-gradient
+    GEMM instead of after it (what DDP's bucket hooks do across layers, here inside one layer).
+
+        reducer = GradientReducer(); reducer.attach()      # once, after init_process_group
+        loss.backward()                                    # gradients arrive summed over the group
+
+    `ready(t)` starts an asynchronous in-place all-reduce of a large tensor and just remembers a small
+    one; `flush()` reduces the small ones in one flat bucket and makes the current stream wait for
+    everything.  The fused Metis backward calls both; `flush()` runs before backward returns, so
+    autograd never sees a gradient that is still being reduced."""
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, average: bool = False, small_bytes: int = 1 << 20):
+        self.group, self.average, self.small_bytes = group, average, small_bytes
+        self._work, self._small, self.bytes_reduced = [], [], 0
+
+    def active(self) -> bool:
+        return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
+
+    def ready(self, t: torch.Tensor) -> None:
+        if t is None or not self.active():
+            return
+        if t.numel() * t.element_size() < self.small_bytes or not t.is_contiguous():
+            self._small.append(t)
+            return
+        self._work.append((dist.all_reduce(t, group=self.group, async_op=True), t))
+
+    def flush(self) -> None:
+        if not self.active():
+            return
+        world = dist.get_world_size(self.group)
+        by_dtype = {}
+        for t in self._small:
+            by_dtype.setdefault(t.dtype, []).append(t)
+        for tensors in by_dtype.values():
+            flat = _flatten_dense_tensors(tensors)
+            dist.all_reduce(flat, group=self.group)
+            if self.average:
+                flat.div_(world)
+            for t, synced in zip(tensors, _unflatten_dense_tensors(flat, tensors)):
+                t.copy_(synced)
+            self.bytes_reduced += flat.numel() * flat.element_size()
+        for work, t in self._work:
+            work.wait()                       # the current stream waits for the collective
+            if self.average:
+                t.div_(world)
+            self.bytes_reduced += t.numel() * t.element_size()
+        self._work, self._small = [], []
+
+    def attach(self) -> "GradientReducer":
+        from fp4_post_b200.Metis.Metis import bitlinear
+        bitlinear.GRADIENT_REDUCER = self
+        return self
+
+    @staticmethod
+    def detach() -> None:
+        from fp4_post_b200.Metis.Metis import bitlinear
+        bitlinear.GRADIENT_REDUCER = None
+
+
 def allreduce_gradients(params: Iterable[torch.nn.Parameter], group: Optional[dist.ProcessGroup] = None,
                         average: bool = False) -> int:
     """Sum (or average) the .grad of every parameter over the group, one collective per dtype.

@@ -121,10 +121,13 @@ def col_mean(x: torch.Tensor) -> torch.Tensor:
 
 def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool = False, seed: int = 0,
                    offset: int = 0, sf_layout: int = cabi.SF_MMA,
-                   mean: Optional[torch.Tensor] = None) -> NVFP4Tensor:
+                   mean: Optional[torch.Tensor] = None,
+                   offset_counter: Optional[torch.Tensor] = None) -> NVFP4Tensor:
     """Quantize x (viewed as [rows, cols]) or, with transpose=True, its transpose.
 
-    `mean` (fp32 [cols]) is subtracted from every row of x first."""
+    `mean` (fp32 [cols]) is subtracted from every row of x first.  Stochastic rounding draws
+    Philox(seed; element, offset); with `offset_counter` (int64 [1] on x's device) the offset is that
+    counter's value and the call increments it, so the call can sit in a CUDA graph that is replayed."""
     _need_cuda(x, "x")
     x2 = _rows2d(x)
     rows, cols = x2.shape
@@ -134,6 +137,11 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
     L = cabi.lib()
     flags = (cabi.Q_TRANSPOSE if transpose else 0) | (cabi.Q_STOCHASTIC if stochastic else 0)
     dev = x2.device
+    if stochastic and offset_counter is not None:
+        if offset_counter.dtype != torch.int64 or offset_counter.device != dev or offset_counter.numel() != 1:
+            raise ValueError("offset_counter must be an int64 tensor with one element on the device of x")
+        flags |= cabi.Q_OFFSET_ON_DEVICE
+        offset = offset_counter.data_ptr()
     if mean is not None:
         _need_cuda(mean, "mean")
         mean = mean.reshape(-1).to(torch.float32).contiguous()

@@ -55,6 +55,7 @@ extern "C" {
 /* quantizer flags */
 #define METIS_Q_TRANSPOSE   (1u << 0) /* quantize x^T: blocks run along the rows of x     */
 #define METIS_Q_STOCHASTIC  (1u << 1) /* stochastic rounding (Philox4x32-10, seed/offset) */
+#define METIS_Q_OFFSET_ON_DEVICE (1u << 2) /* offset = address of a device uint64 counter   */
 
 /* status codes (host return values are <= 0, device status words are >= 0) */
 #define METIS_OK                 0
@@ -107,7 +108,13 @@ int64_t metis_nvfp4_quantize_workspace_bytes(int64_t R, int64_t C);
  * Arithmetic (fp32, round-to-nearest mode bit-exact with the reference run on
  * x.float()): s = amax/6 + 1e-9 per block; unit = max(s)/448; scale = e4m3(s/unit);
  * code = round-half-even of |x|/(s/2) folded onto the e2m1 grid; sign bit = (x < 0).
- * Stochastic mode adds U[-0.5, 0.5) to the folded index before rounding.
+ * Stochastic mode adds U[-0.5, 0.5) to the folded index before rounding.  The random bits are
+ * Philox4x32-10(seed; element index, offset).  With METIS_Q_OFFSET_ON_DEVICE the offset is not
+ * the argument's value but the content of the device uint64 it points to (8-byte aligned),
+ * and the call adds 1 to that counter when its kernels have read it: successive calls on one
+ * stream draw fresh bits although their arguments are identical, which is what a captured
+ * CUDA graph needs when it is replayed (the reference's torch.rand advances a device-side
+ * Philox offset in the same situation).
  */
 int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
                              const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,

@@ -79,6 +79,50 @@ def test_two_ranks_reproduce_the_full_batch_weight_gradients():
         torch.testing.assert_close(grads[name], p.grad, rtol=1e-5, atol=1e-5, msg=name)
 
 
+def _reducer_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fp4_post_b200.dp import GradientReducer
+        red = GradientReducer(small_bytes=1024)
+        big = torch.full((64, 64), float(rank + 1))             # 16 KiB: its own asynchronous all-reduce
+        small = [torch.full((5,), float(rank + 1)), torch.full((3, 2), 10.0 * (rank + 1))]
+        red.ready(big)
+        for t in small:
+            red.ready(t)
+        red.ready(None)                                           # an absent gradient (no bias) is skipped
+        red.flush()
+        if rank == 0:
+            out.put((big.clone(), [t.clone() for t in small], red.bytes_reduced))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gradient_reducer_sums_large_tensors_in_place_and_small_ones_in_one_bucket():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_reducer_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    big, small, nbytes = out.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert torch.equal(big, torch.full((64, 64), 3.0))
+    assert torch.equal(small[0], torch.full((5,), 3.0)) and torch.equal(small[1], torch.full((3, 2), 30.0))
+    assert nbytes == (64 * 64 + 5 + 6) * 4
+
+
+def test_gradient_reducer_is_inert_without_a_process_group():
+    from fp4_post_b200.dp import GradientReducer
+    red = GradientReducer()
+    t = torch.ones(4)
+    red.ready(t)
+    red.flush()
+    assert torch.equal(t, torch.ones(4)) and red.bytes_reduced == 0
+
+
 def test_sharding_covers_the_batch_once_and_allreduce_is_a_noop_without_a_group():
     from fp4_post_b200.dp import allreduce_gradients, shard_tokens
     x = torch.arange(7 * 3).reshape(7, 3)
