@@ -275,7 +275,7 @@ def main():
     import torch.distributed as dist
     import fp4_post_b200
     from fp4_post_b200 import cabi, ops
-    from fp4_post_b200.dp import GradientReducer
+    from fp4_post_b200.dp import allreduce_gradients
     from fp4_post_b200.graphs import GraphedStep
     from fp4_post_b200.Metis.Metis.bitlinear import BitLinear
     from fp4_post_b200.grpo.grpo import MetisArgs
@@ -305,10 +305,6 @@ def main():
     layer.layer_name = "bench.layer"
     layer.split()                                  # exact SVD once, outside the timed region
     params = [p for p in layer.parameters()]
-    if world > 1:
-        # data-parallel training: the all-reduce of the residual weight's gradient starts as soon as
-        # that gradient exists and overlaps the input-gradient GEMM (fp4_post_b200/dp.py)
-        GradientReducer().attach()
 
     g = torch.Generator(device="cpu").manual_seed(1 + rank)
     x_host = torch.randn(1, M_TOKENS, HIDDEN_K, generator=g).to(torch.bfloat16)
@@ -324,8 +320,14 @@ def main():
             p.grad = None
         x.grad = None
         y = layer(x)
-        y.backward(grad)                           # world > 1: the reducer sums the weight gradients inside backward
+        y.backward(grad)
         return y
+
+    def reduce_grads():
+        # what DDP does for this layer; issued after the captured step, outside the graph (NCCL's
+        # watchdog and a stream capture do not mix without extra process-wide settings)
+        if world > 1:
+            allreduce_gradients(params)
 
     def barrier():
         if world > 1:
@@ -354,13 +356,19 @@ def main():
             step(x_dev, g_dev)
         # The timed step is one CUDA-graph launch: the ~35 kernels and the torch ops between them are
         # captured once (fp4_post_b200/graphs.py) instead of being issued from Python every step.
-        ms_eager = timed(lambda: step(x_dev, g_dev), max(3, args.steps // 5))      # the same step issued from Python
+        def eager_step():
+            step(x_dev, g_dev)
+            reduce_grads()
+        ms_eager = timed(eager_step, max(3, args.steps // 5))                        # the same step issued from Python
         launches0 = ops.launch_count()
         graphed = GraphedStep(lambda: step(x_dev, g_dev), warmup=1)
         launches_per_step = (ops.launch_count() - launches0) // 2          # one warm-up run + the capture
-        for _ in range(3):
+        def graph_step():
             graphed()
-        ms_step = timed(graphed, args.steps)
+            reduce_grads()
+        for _ in range(3):
+            graph_step()
+        ms_step = timed(graph_step, args.steps)
         launches = launches_per_step * args.steps
 
         # ---- end to end: host inputs, checksum back -------------------------------------------------------------
@@ -397,6 +405,7 @@ def main():
                 main.wait_event(ready[i])
                 check = e2e_graphs[i]()
                 consumed[i].record(main)
+                reduce_grads()
                 total += float(check.item())
             return total
 
@@ -452,7 +461,7 @@ def main():
             "e2e": {"value": world * flops / ms_e2e / 1e9, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": x_host.numel() * 2 + g_host.numel() * 2, "d2h_bytes_per_step": 8,
                     "ms_per_step": ms_e2e},
-            "gpu_launches": launches, "launch_mode": "one CUDA graph per step", "ms_per_step_eager": ms_eager,
+            "gpu_launches": launches, "launch_mode": "one CUDA graph per step" + (" + NCCL all-reduce of the weight gradients" if world > 1 else ""), "ms_per_step_eager": ms_eager,
             "clocks": clock_summary,
             "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_pair_kernel (CTA pairs, 256x256 tiles) forward residual GEMM + fused rank-128 product",
                          "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,

@@ -81,23 +81,17 @@ class GradientReducer:
 
 
 def allreduce_gradients(params: Iterable[torch.nn.Parameter], group: Optional[dist.ProcessGroup] = None,
-                        average: bool = False) -> int:
-    """Sum (or average) the .grad of every parameter over the group, one collective per dtype.
-    Returns the number of bytes reduced.  A no-op without an initialised process group."""
+                        average: bool = False, small_bytes: int = 1 << 20) -> int:
+    """Sum (or average) the .grad of every parameter over the group: gradients of at least
+    `small_bytes` are reduced in place, one collective each, the small ones share one flat bucket per
+    dtype.  Returns the number of bytes reduced.  A no-op without an initialised process group."""
     if not (dist.is_available() and dist.is_initialized()):
         return 0
-    world = dist.get_world_size(group)
-    by_dtype = {}
+    red = GradientReducer(group, average, small_bytes)
+    if not red.active():
+        # a group of one still counts the bytes, as the collective would
+        return sum(p.grad.numel() * p.grad.element_size() for p in params if p.grad is not None)
     for p in params:
-        if p.grad is not None:
-            by_dtype.setdefault(p.grad.dtype, []).append(p.grad)
-    total = 0
-    for grads in by_dtype.values():
-        flat = _flatten_dense_tensors(grads)
-        dist.all_reduce(flat, group=group)
-        if average:
-            flat.div_(world)
-        for g, synced in zip(grads, _unflatten_dense_tensors(flat, grads)):
-            g.copy_(synced)
-        total += flat.numel() * flat.element_size()
-    return total
+        red.ready(p.grad)
+    red.flush()
+    return red.bytes_reduced
