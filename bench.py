@@ -180,6 +180,7 @@ def run_gemm_sweep(args):
     each with and without the fused rank-128 product; one JSON line per shape."""
     import torch
     from fp4_post_b200 import ops
+    from fp4_post_b200.graphs import GraphedStep
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
     for M, N, K in GEMM_SWEEP:
@@ -192,16 +193,21 @@ def run_gemm_sweep(args):
             if rank:
                 lr = (torch.randn(M, rank, device=dev, dtype=torch.bfloat16), torch.randn(N, rank, device=dev, dtype=torch.bfloat16))
             fn = lambda: ops.nvfp4_gemm(qa, qb, lowrank=lr, out=out)
-            for _ in range(3):
-                fn()
+            # `steps` launches replayed as one CUDA graph: the small shapes take less GPU time than
+            # Python needs to issue them, so eager back-to-back calls would time the host
+            def burst():
+                for _ in range(args.steps):
+                    fn()
+            graphed = GraphedStep(burst, warmup=1)
+            graphed()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for _ in range(args.steps):
-                fn()
+            graphed()
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / args.steps
+            del graphed
             key = f"r{rank}"
             line[key + "_us"] = round(ms * 1e3, 2)
             line[key + "_tflops"] = round(2 * M * N * (K + rank) / ms / 1e9, 1)

@@ -26,7 +26,7 @@ EXPORTS = (
     "metis_query", "metis_last_error_string", "metis_nvfp4_sf_bytes",
     "metis_nvfp4_quantize_workspace_bytes", "metis_nvfp4_quantize", "metis_rmsnorm_nvfp4_quantize",
     "metis_nvfp4_dequantize", "metis_col_mean_workspace_bytes", "metis_col_mean", "metis_nvfp4_gemv",
-    "metis_nvfp4_gemm", "metis_nvfp4_quantize_static",
+    "metis_nvfp4_gemm", "metis_nvfp4_quantize_static", "metis_nvfp4_gemm_workspace_bytes",
 )
 
 
@@ -45,6 +45,7 @@ class GemmArgs(C.Structure):
         ("d", C.c_void_p), ("ldd", C.c_int64),
         ("d_dtype", C.c_int32), ("reserved", C.c_int32),
         ("status", C.c_void_p), ("stream", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -90,6 +91,8 @@ def lib() -> C.CDLL:
     L.metis_nvfp4_gemv.restype = i32
     L.metis_nvfp4_gemm.argtypes = [C.POINTER(GemmArgs)]
     L.metis_nvfp4_gemm.restype = i32
+    L.metis_nvfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
+    L.metis_nvfp4_gemm_workspace_bytes.restype = i64
     _lib = L
     return L
 

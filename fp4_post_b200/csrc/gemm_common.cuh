@@ -58,6 +58,12 @@ struct GemmParams {
   const void* c;  int64_t ldc;
   void* d;        int64_t ldd;
   int32_t* status;
+  // split-K (single-CTA kernel only): number of K splits, K iterations per split, partial sums
+  // [splits, M, ldp] fp32; splits = 1 means none
+  int32_t splits = 1;
+  int32_t k_per_split = 1 << 30;
+  float* partial = nullptr;
+  int64_t ldp = 0;
 };
 
 // Tile order: bands of `group` row tiles; inside a band the row tile runs fastest, then the column
@@ -157,6 +163,8 @@ template <typename TD> struct EpilogueCtx {
   uint8_t* staging;      // 2 KiB of shared memory owned by this warp
   int64_t row0;          // first of the warp's 32 rows; lane l holds row0 + l
   float g, c0, c1;
+  float* partial = nullptr;   // split-K: raw fp32 partial sums [M, ldp] of this split go here instead of D
+  int64_t ldp = 0;
 };
 
 // v[i] += c * rvec[col0 + i] for the 32 columns of a chunk (128-bit loads when the chunk is whole
@@ -191,6 +199,15 @@ __device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uin
   const int64_t row = ctx.row0 + lane;
   if (ctx.row0 >= p.M || col0 >= p.N) return;          // warp-uniform
   const bool live = row < p.M;
+  if (ctx.partial) {                                   // warp-uniform; ldp is a multiple of 32: the chunk fits
+    if (live) {
+      float4* dst = reinterpret_cast<float4*>(ctx.partial + row * ctx.ldp + col0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+    }
+    return;
+  }
   float v[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ctx.g;

@@ -50,9 +50,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int64_t tiles_m = (p.M + kBM - 1) / kBM;
   const int64_t tiles_n = (p.N + BN - 1) / BN;
   const int64_t num_tiles = tiles_m * tiles_n;
-  const int k_iters = (int)((p.K + 255) / 256);
+  const int k_iters_all = (int)((p.K + 255) / 256);
   const int r_iters = (p.rank + 63) / 64;
-  const int iters = k_iters + r_iters;
+  // Split-K: a work item is (tile, split); split s owns the K iterations [s k_per, (s+1) k_per) and,
+  // if it is split 0, the rank-r iterations after them.  With more than one split the epilogue
+  // stores raw fp32 partial sums and a second kernel adds them up and applies the epilogue terms.
+  const int splits = p.splits;
+  const int64_t num_work = num_tiles * splits;
+#define METIS_WORK_ITEM(w)                                                                        \
+  const int64_t tile = (w) / splits;                                                              \
+  const int split = (int)((w) - tile * splits);                                                   \
+  const int it0 = split * p.k_per_split;                                                          \
+  const int k_iters = (k_iters_all - it0 < p.k_per_split) ? k_iters_all - it0 : p.k_per_split;    \
+  const int iters = k_iters + (split == 0 ? r_iters : 0);                                         \
+  (void)it0
   const int64_t sf_tiles_a = sf_tiles_per_row(p.K);        // per 128-row block (A and B share K)
   const int64_t b_row_blocks = (p.N + 127) / 128;
 
@@ -83,7 +94,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     bool ok = true;
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t full_base = smem_u32(full);
-    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int64_t w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      METIS_WORK_ITEM(w);
       int64_t tm, tn;
       tile_coords(tile, tiles_m, tiles_n, 16, tm, tn);
       const int32_t m0 = (int32_t)(tm * kBM), n0 = (int32_t)(tn * BN);
@@ -110,12 +122,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             mbar_arrive_addr(bar);
           } else if (it < k_iters) {
             mbar_expect_tx_addr(bar, k_bytes);
-            tma_load_2d_addr(sa, &map_a, it * kBKBytes, m0, bar);
-            tma_load_2d_addr(sb, &map_b, it * kBKBytes, n0, bar);
+            const int kit = it0 + it;
+            tma_load_2d_addr(sa, &map_a, kit * kBKBytes, m0, bar);
+            tma_load_2d_addr(sb, &map_b, kit * kBKBytes, n0, bar);
             const bool drop = first && (p.debug & kDebugDropFirstSfa);
-            if (!drop) bulk_load_addr(ssfa, sfa_src + (int64_t)it * 2048, 2048, bar);
-            bulk_load_addr(ssfb, sfb_src + (int64_t)it * 2048, 2048, bar);
-            if (sfb_second) bulk_load_addr(ssfb + 2048, sfb_src + (sf_tiles_a + (int64_t)it * 4) * 512, 2048, bar);
+            if (!drop) bulk_load_addr(ssfa, sfa_src + (int64_t)kit * 2048, 2048, bar);
+            bulk_load_addr(ssfb, sfb_src + (int64_t)kit * 2048, 2048, bar);
+            if (sfb_second) bulk_load_addr(ssfb + 2048, sfb_src + (sf_tiles_a + (int64_t)kit * 4) * 512, 2048, bar);
           } else {
             const int j = it - k_iters;   // 64-column panel of the rank-r factors
             mbar_expect_tx_addr(bar, Cfg::kABytes + Cfg::kBBytes);
@@ -141,7 +154,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint32_t stage_lo = stage0_lo;
     uint32_t sf_buf = 0, sf_phase = 0;
     const bool no_mma = (p.debug & kDebugNoMma) != 0;
-    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+    for (int64_t w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++local_tile) {
+      METIS_WORK_ITEM(w);
       // Tile j may start once the epilogue of tile j-1 has drained the columns the two
       // accumulators share (release number j-1, i.e. phase parity (j-1)&1).  That also covers
       // tile j-2, whose accumulator this one reuses: the epilogue finished it before it began j-1.
@@ -216,7 +230,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint32_t phase = 0, sf_buf = 0;
     uint32_t slot = 0;                       // pipeline iterations so far, of either kind
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int64_t w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      METIS_WORK_ITEM(w);
       for (int it = 0; it < iters; ++it, ++slot) {
         if (it < k_iters && !(p.debug & kDebugNoMma)) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
@@ -266,12 +281,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     ctx.p = &p;
     ctx.staging = staging + q * 2048;
     uint32_t local_tile = 0;
-    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+    for (int64_t w = blockIdx.x; w < num_work; w += gridDim.x, ++local_tile) {
+      METIS_WORK_ITEM(w);
       int64_t tm, tn;
       tile_coords(tile, tiles_m, tiles_n, 16, tm, tn);
       const int64_t row = tm * kBM + q * 32 + lane;
       const int64_t n0 = tn * BN;
       ctx.row0 = tm * kBM + q * 32;
+      ctx.partial = splits > 1 ? p.partial + (int64_t)split * p.M * p.ldp : nullptr;
+      ctx.ldp = p.ldp;
       ctx.c0 = p.rvec0 ? (p.cvec0 ? (row < p.M ? __ldg(p.cvec0 + row) : 0.f) : 1.0f) : 0.0f;
       ctx.c1 = p.rvec1 ? (p.cvec1 ? (row < p.M ? __ldg(p.cvec1 + row) : 0.f) : 1.0f) : 0.0f;
       if (!mbar_wait(acc_full, local_tile & 1u, abort_flag)) {
@@ -324,6 +342,57 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
+// ---- split-K: sum of the partial products + the epilogue terms -----------------------------------------
+
+template <typename TD>
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const GemmParams p) {
+  const int64_t groups_per_row = (p.N + 3) / 4;
+  const float g = p.alpha * __ldg(p.a_unit) * __ldg(p.b_unit);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.M * groups_per_row; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / groups_per_row, col = (i - row * groups_per_row) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < p.splits; ++s) {            // fixed order: the result does not depend on timing
+      const float4 v = *reinterpret_cast<const float4*>(p.partial + ((int64_t)s * p.M + row) * p.ldp + col);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float o[4] = {acc.x * g, acc.y * g, acc.z * g, acc.w * g};
+    const float c0 = p.rvec0 ? (p.cvec0 ? __ldg(p.cvec0 + row) : 1.0f) : 0.0f;
+    const float c1 = p.rvec1 ? (p.cvec1 ? __ldg(p.cvec1 + row) : 1.0f) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col + j >= p.N) break;
+      if (p.rvec0) o[j] = fmaf(c0, __ldg(p.rvec0 + col + j), o[j]);
+      if (p.rvec1) o[j] = fmaf(c1, __ldg(p.rvec1 + col + j), o[j]);
+      if (p.c) {
+        if constexpr (sizeof(TD) == 2) o[j] += __bfloat162float(static_cast<const __nv_bfloat16*>(p.c)[row * p.ldc + col + j]);
+        else o[j] += static_cast<const float*>(p.c)[row * p.ldc + col + j];
+      }
+      if constexpr (sizeof(TD) == 2) static_cast<__nv_bfloat16*>(p.d)[row * p.ldd + col + j] = __float2bfloat16_rn(o[j]);
+      else static_cast<float*>(p.d)[row * p.ldd + col + j] = o[j];
+    }
+  }
+}
+
+// Splits the library would use for this shape: only products with a single row block of A (decode-
+// sized M) whose tiles leave most SMs idle, and never fewer than 2 K iterations per split.
+static int choose_splits(int64_t M, int64_t N, int64_t K, int bn, int sms) {
+  if (M > 128) return 1;
+  const int64_t tiles = ceil_div(N, bn);
+  const int64_t k_iters = ceil_div(K, 256);
+  int64_t s = sms / tiles;
+  if (s > k_iters / 2) s = k_iters / 2;
+  if (s > 8) s = 8;
+  return s < 2 ? 1 : (int)s;
+}
+static int tile_width(int64_t M, int64_t N, int sms) {
+  int bn = (N > 128) ? 256 : 128;
+  // one row block of A and few column tiles (the weight gradient of a rank-r factor, decode):
+  // narrower tiles put twice as many SMs to work, which matters more than the MMA shape there
+  if (bn == 256 && M <= 128 && ceil_div(N, 256) * 2 <= sms) bn = 128;
+  return bn;
+}
+
 // ---- host side ----------------------------------------------------------------------------------------------
 
 template <int BN, typename TD>
@@ -333,11 +402,19 @@ static int32_t launch_gemm(const metis_gemm_args* a, const CUtensorMap& ma, cons
   auto kern = nvfp4_gemm_kernel<BN, TD>;
   // per device and cheap, so it is simply repeated on every launch
   METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-  const int64_t tiles = ceil_div(a->M, kBM) * ceil_div(a->N, BN);
+  const int64_t work = ceil_div(a->M, kBM) * ceil_div(a->N, BN) * p.splits;
   int64_t grid = device_sm_count();
-  if (grid > tiles) grid = tiles;
-  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, reinterpret_cast<cudaStream_t>(a->stream)>>>(ma, mb, mt, mu, p);
+  if (grid > work) grid = work;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ma, mb, mt, mu, p);
   METIS_CUDA_OK(cudaGetLastError());
+  if (p.splits > 1) {
+    const int64_t threads = a->M * ceil_div(a->N, 4);
+    int64_t blocks = ceil_div(threads, 256);
+    if (blocks > (int64_t)device_sm_count() * 8) blocks = (int64_t)device_sm_count() * 8;
+    splitk_finish_kernel<TD><<<(unsigned)blocks, 256, 0, st>>>(p);
+    METIS_CUDA_OK(cudaGetLastError());
+  }
   return METIS_OK;
 }
 
@@ -347,6 +424,13 @@ int32_t launch_gemm_pair(const metis_gemm_args* a, const CUtensorMap& ma, const 
 }  // namespace metis
 
 using namespace metis;
+
+extern "C" int64_t metis_nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || M > 128) return 0;
+  const int sms = device_sm_count();
+  const int splits = choose_splits(M, N, K, tile_width(M, N, sms), sms);
+  return splits > 1 ? (int64_t)splits * M * (ceil_div(N, 32) * 32) * (int64_t)sizeof(float) : 0;
+}
 
 extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
   if (!a) return fail(METIS_ERR_BAD_ARGUMENT, "args is null");
@@ -370,10 +454,8 @@ extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
   if ((a->cvec0 && !a->rvec0) || (a->cvec1 && !a->rvec1)) return fail(METIS_ERR_BAD_ARGUMENT, "a cvec needs its rvec");
   if (a->reserved & ~kDebugMask) return fail(METIS_ERR_BAD_ARGUMENT, "reserved must be 0");
 
-  int bn = (a->N > 128) ? 256 : 128;
-  // one row block of A and few column tiles (the weight gradient of a rank-r factor): narrower
-  // tiles put twice as many SMs to work, which matters more than the MMA shape there
-  if (bn == 256 && a->M <= 128 && ceil_div(a->N, 256) * 2 <= device_sm_count()) bn = 128;
+  const int sms = device_sm_count();
+  const int bn = tile_width(a->M, a->N, sms);
   // CTA pairs (256 x 256 tiles) whenever there is more than one 128-row block of each operand
   const bool pair = bn == 256 && a->M > 128 && !(a->reserved & kDebugSingleCta);
   const int b_box = pair ? 128 : bn;       // rows of B (and U) one CTA loads per stage
@@ -393,6 +475,16 @@ extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
   p.alpha = a->alpha;
   p.cvec0 = a->cvec0; p.rvec0 = a->rvec0; p.cvec1 = a->cvec1; p.rvec1 = a->rvec1;
   p.c = a->c; p.ldc = a->ldc; p.d = a->d; p.ldd = a->ldd; p.status = a->status;
+  // split-K needs the caller's scratch; without it (or with too little) the product runs unsplit
+  const int splits = pair ? 1 : choose_splits(a->M, a->N, a->K, bn, sms);
+  if (splits > 1 && a->workspace && a->workspace_bytes >= metis_nvfp4_gemm_workspace_bytes(a->M, a->N, a->K) &&
+      aligned16(a->workspace) && !(a->reserved & (kDebugNoMma | kDebugNoLoad | kDebugDropFirstSfa))) {
+    const int64_t k_iters = ceil_div(a->K, 256);
+    p.k_per_split = (int32_t)ceil_div(k_iters, splits);
+    p.splits = (int32_t)ceil_div(k_iters, p.k_per_split);       // no split is left without iterations
+    p.partial = static_cast<float*>(a->workspace);
+    p.ldp = ceil_div(a->N, 32) * 32;
+  }
   if (pair) return launch_gemm_pair(a, ma, mb, mt, mu, p);
   if (bn == 256) {
     if (a->d_dtype == METIS_DTYPE_BF16) return launch_gemm<256, __nv_bfloat16>(a, ma, mb, mt, mu, p);

@@ -222,9 +222,19 @@ typedef struct metis_gemm_args {
   int32_t reserved;
   int32_t* status;          /* optional device int32: 0, or a METIS_DEV_* code */
   void* stream;
+  void* workspace;          /* optional scratch, 16-byte aligned: metis_nvfp4_gemm_workspace_bytes */
+  int64_t workspace_bytes;
 } metis_gemm_args;
 
 int32_t metis_nvfp4_gemm(const metis_gemm_args* args);
+
+/*
+ * Scratch that lets a decode-sized product (M <= 128: the rollout path, bitlinear.py:704-751,
+ * and the weight gradients of the rank-r factors) split its K loop over otherwise idle SMs:
+ * bytes of fp32 partial sums, 0 when the shape is not split.  Without the scratch the same
+ * product runs unsplit on fewer SMs; the result is the same up to fp32 summation order.
+ */
+int64_t metis_nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 #ifdef __cplusplus
 }

@@ -90,6 +90,34 @@ def test_single_cta_kernel_where_pairs_would_run(M, N, K):
     assert rel_l2(got, O.gemm_reference(da, db)) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 1024, 4096), (100, 1160, 2304), (128, 4096, 1024)])
+def test_decode_sized_products_split_their_k_loop(M, N, K):
+    # one row block of A and few column tiles: the K loop is split over idle SMs (fp32 partial sums in
+    # a scratch buffer, summed in a fixed order by a second kernel that also applies every epilogue term)
+    assert cabi.lib().metis_nvfp4_gemm_workspace_bytes(M, N, K) > 0
+    assert cabi.lib().metis_nvfp4_gemm_workspace_bytes(4096, N, K) == 0
+    qa, qb, da, db = operands(M, N, K, seed=M + K)
+    g = torch.Generator().manual_seed(M)
+    rank = 64
+    t = (torch.randn(M, rank, generator=g) * 3).to(torch.bfloat16)
+    u = (torch.randn(N, rank, generator=g) / rank ** 0.5).to(torch.bfloat16)
+    scale = float(qa.unit.item()) * float(qb.unit.item())
+    t_acc = (t.float() / scale).to(torch.bfloat16)
+    bias, cv, rv = torch.randn(N, generator=g), torch.randn(M, generator=g), torch.randn(N, generator=g)
+    c = torch.randn(M, N, generator=g)
+    want = (O.gemm_reference(da, db) + (t_acc.float().numpy() * scale) @ u.float().numpy().T) * 0.5 \
+        + bias.numpy()[None, :] + np.outer(cv.numpy(), rv.numpy()) + c.numpy()
+    kw = dict(lowrank=(t_acc.to(DEV), u.to(DEV)), rank1=[(None, bias.to(DEV)), (cv.to(DEV), rv.to(DEV))], alpha=0.5)
+    got = run(qa, qb, c=c.to(DEV), out_dtype=torch.float32, **kw).cpu().numpy()
+    assert rel_l2(got, want) <= 1e-5, rel_l2(got, want)
+    again = run(qa, qb, c=c.to(DEV), out_dtype=torch.float32, **kw).cpu().numpy()
+    assert np.array_equal(got, again)                       # fixed summation order: bit-reproducible
+    c16 = c.to(torch.bfloat16)
+    got16 = run(qa, qb, c=c16.to(DEV), out_dtype=torch.bfloat16, **kw).float().cpu().numpy()
+    want16 = want - c.numpy() + c16.float().numpy()
+    assert rel_l2(got16, torch.from_numpy(want16.astype(np.float32)).to(torch.bfloat16).float().numpy()) <= TOL
+
+
 def test_rank1_terms_bias_and_addend():
     M, N, K = 260, 392, 768
     qa, qb, da, db = operands(M, N, K, seed=77)
