@@ -428,9 +428,17 @@ def main():
         u16 = layer.ulinear.weight.detach().to(torch.bfloat16)
         out = torch.empty(M_TOKENS, HIDDEN_N, device=dev, dtype=torch.bfloat16)
         gemm = lambda: ops.nvfp4_gemm(shared.q, rq.q, lowrank=(t_acc, u16), out=out)
-        for _ in range(3):
-            gemm()
-        ms_gemm = timed(gemm, 20)
+        def burst_ms(fn, n):
+            """average device time of one call: n calls captured into one CUDA graph (a kernel that runs
+            for 0.1 ms would otherwise be timed together with the gap Python leaves between launches)"""
+            def burst():
+                for _ in range(n):
+                    fn()
+            g = GraphedStep(burst, warmup=1, pool=graphed.pool())
+            g()
+            return timed(g, 3) / n
+
+        ms_gemm = burst_ms(gemm, 20)
         gemm_flops = 2 * M_TOKENS * HIDDEN_N * HIDDEN_K + 2 * M_TOKENS * HIDDEN_N * RANK
 
         xq = torch.randn(QUANT_ROWS, QUANT_COLS, device=dev, dtype=torch.bfloat16)
@@ -439,9 +447,7 @@ def main():
         for name, fn in (("rmsnorm_quant", lambda: ops.rmsnorm_nvfp4_quantize(xq, gamma, 1e-6)),
                          ("quant_rows", lambda: ops.nvfp4_quantize(xq)),
                          ("quant_transposed", lambda: ops.nvfp4_quantize(xq, transpose=True))):
-            for _ in range(3):
-                fn()
-            ms = timed(fn, 10)
+            ms = burst_ms(fn, 10)
             gbs = QUANT_ROWS * QUANT_COLS * BYTES_PER_ELEM_BF16 / ms / 1e6
             quant_lines[name] = {"gbs": round(gbs, 1), "ms": round(ms, 4), "frac_of_hbm_copy": round(gbs / peaks["hbm_gbs"], 4)}
         del xq
