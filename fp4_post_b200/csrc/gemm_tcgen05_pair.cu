@@ -267,16 +267,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           if (elect_one()) {
             if (no_mma) {
             } else if (scaled) {
-              // scales of this stage into buffer sf_buf (the MMAs that last read it were issued two
-              // stages ago; copies and MMAs run in issue order): 4 tiles of A, 2 x 4 of B
+              // Scales of this stage into buffer sf_buf (the MMAs that last read it were issued two
+              // stages ago; copies and MMAs run in issue order): per MMA one tile of A and two of B.
+              // The copies of MMA j+1 are issued behind MMA j, so that they run while it computes;
+              // only the first three of a stage wait for nothing.
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 tc_copy_scales_pair(t_sfa + 4 * j, sf_lo + 32 * j);
                 tc_copy_scales_pair(t_sfb + 8 * j, sf_lo + 128 + 32 * j);
                 tc_copy_scales_pair(t_sfb + 8 * j + 4, sf_lo + 256 + 32 * j);
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
                 tc_mma_fp4_pair(d_tmem, a_lo + 2 * j, b_lo + 2 * j, kOperandDescHi, idesc_fp4(BN, 2 * kBM), t_sfa + 4 * j,
                                 t_sfb + 8 * j, (it > 0 || j > 0) ? 1u : 0u);
               }
