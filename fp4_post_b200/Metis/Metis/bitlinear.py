@@ -31,7 +31,7 @@ import torch.nn.init as init
 
 from fp4_post_b200 import ops
 from .quant import *  # noqa: F401,F403  (the reference re-exports its quantizers the same way)
-from .quant import is_native, quant_func
+from .quant import is_native, quant_func, random_lane
 
 
 class PackedOperand:
@@ -445,6 +445,17 @@ class LinearLowbitFunction(torch.autograd.Function):
 
 
 _ONES = {}
+_AUX_STREAMS = {}
+
+
+def _aux_stream(device: torch.device) -> "torch.cuda.Stream":
+    """The second stream of `device` for work that may overlap the current stream's (one per device)."""
+    st = _AUX_STREAMS.get(device)
+    if st is None:
+        st = _AUX_STREAMS[device] = torch.cuda.Stream(device=device)
+    return st
+
+
 # fp4_post_b200.dp.GradientReducer installs itself here: the fused backward hands it every weight
 # gradient the moment it is final (data-parallel training); None = single process.
 GRADIENT_REDUCER = None
@@ -587,6 +598,7 @@ class MetisFusedFunction(torch.autograd.Function):
     backward of LinearLowbitFunction."""
 
     fuse_dx_side_product = True      # bf16 only; False keeps the two dX products as separate launches
+    concurrent_branches = True       # backward of the low-rank branch on a second CUDA stream
 
     @staticmethod
     def forward(ctx, x, xa: PackedOperand, v_weight, vq: PackedOperand, s, u_weight, r_weight,
@@ -622,23 +634,47 @@ class MetisFusedFunction(torch.autograd.Function):
         act = yv.dtype
         g = grad_output.reshape(M, N).to(act)
         grad_bias = g.sum(dim=0).to(torch.float32) if ctx.has_bias else None
-        # ulinear: plain linear on ts = s . yv
-        ts = yv * s.to(act)
-        u = u_weight.to(act)
-        grad_u = (g.T @ ts).to(u_weight.dtype)
-        d_ts = g @ u                                                                # [M, r]
-        grad_s = (d_ts * yv).sum(dim=0).to(s.dtype)
-        d_yv = d_ts * s.to(act)
         centred = F._backward_centred()
         quantizer = F.q_backward_outputgrad
-        # vlinear and warmup_linear (the residual): quantized backward with grad_output = d_yv and g
-        dv = F._pack_centred(d_yv, quantizer, centred)
-        dg = F._pack_centred(g, quantizer, centred)
         reducer = GRADIENT_REDUCER
-        grad_r = _packed_dw(dg, xa, M)
-        if reducer is not None:
-            reducer.ready(grad_r)           # the big all-reduce starts here and runs beside the dX product
-        grad_v = _packed_dw(dv, xa, M)
+
+        def low_rank_branch():
+            # ulinear: plain linear on ts = s . yv; vlinear: quantized backward with grad_output = d_yv
+            ts = yv * s.to(act)
+            u = u_weight.to(act)
+            grad_u = (g.T @ ts).to(u_weight.dtype)
+            d_ts = g @ u                                                            # [M, r]
+            grad_s = (d_ts * yv).sum(dim=0).to(s.dtype)
+            d_yv = d_ts * s.to(act)
+            dv = F._pack_centred(d_yv, quantizer, centred)
+            return grad_u, grad_s, dv, _packed_dw(dv, xa, M)
+
+        def residual_branch():
+            # warmup_linear (the residual): quantized backward with grad_output = g
+            dg = F._pack_centred(g, quantizer, centred)
+            grad_r = _packed_dw(dg, xa, M)
+            if reducer is not None:
+                reducer.ready(grad_r)       # the big all-reduce starts here and runs beside the dX product
+            return dg, grad_r
+
+        if MetisFusedFunction.concurrent_branches and g.is_cuda:
+            # The low-rank branch is a dozen small kernels that leave most of the GPU idle; on a second
+            # stream they run in the shadow of the residual branch's quantizers and weight-gradient
+            # GEMM.  Both branches contract over the transposed activation: made once, before the fork.
+            x_t = xa.transposed()
+            if centred:
+                _row_sums(x_t)              # cached on x_t and read by both branches
+            main, aux = torch.cuda.current_stream(), _aux_stream(g.device)
+            aux.wait_stream(main)
+            with torch.cuda.stream(aux), random_lane(1):
+                grad_u, grad_s, dv, grad_v = low_rank_branch()
+            dg, grad_r = residual_branch()
+            main.wait_stream(aux)
+            for t in (grad_u, grad_s, grad_v):
+                t.record_stream(main)       # allocated on the second stream, consumed by autograd on this one
+        else:
+            grad_u, grad_s, dv, grad_v = low_rank_branch()
+            dg, grad_r = residual_branch()
         if MetisFusedFunction.fuse_dx_side_product and act == torch.bfloat16 and r <= 256:
             # dX of both branches in ONE launch: D^v @ V^ enters the residual product as a bf16
             # rank-r side product.  e2m1 x e4m3 is exact in bf16; the ratio of the two products'

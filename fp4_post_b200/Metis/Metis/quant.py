@@ -248,6 +248,24 @@ def _eager_nosr_graph(x: torch.Tensor) -> torch.Tensor:
     return (_unfold_e2m1(r) * blocks.sign() / two * d).reshape(x.shape)
 
 
+class random_lane:
+    """Context manager: stochastic quantizations issued inside use their own Philox key and their own
+    device-side offset counter.  Work that runs on a second CUDA stream takes a lane of its own, so that
+    two streams never read and bump one counter at the same time (and never share random bits)."""
+
+    def __init__(self, lane: int):
+        self.lane = int(lane)
+
+    def __enter__(self):
+        self.saved = _NativeNVFP4._lane
+        _NativeNVFP4._lane = self.lane
+        return self
+
+    def __exit__(self, *exc):
+        _NativeNVFP4._lane = self.saved
+        return False
+
+
 class _NativeNVFP4(BlockQuantFunc):
     """Common part of the two NVFP4 quantizers: CUDA only, kernels behind the C ABI."""
     stochastic = False
@@ -269,16 +287,18 @@ class _NativeNVFP4(BlockQuantFunc):
     def _native_input(cls, x: torch.Tensor) -> torch.Tensor:
         return x if x.dtype in (torch.bfloat16, torch.float32) else x.float()
 
-    _counters = {}          # device -> int64 [1]: the Philox offset of the next stochastic call
+    _counters = {}          # (device, lane) -> int64 [1]: the Philox offset of the next stochastic call
+    _lane = 0               # random lane of the calls being issued now (see random_lane)
 
     @classmethod
     def _offset_counter(cls, device: torch.device) -> torch.Tensor:
         """Per-device call counter kept ON the device (like torch's graph-safe Philox offset): every
         stochastic quantization reads and bumps it, so eager calls and replays of a captured CUDA
         graph both draw fresh random bits.  Created on first use: run one step before capturing."""
-        ctr = _NativeNVFP4._counters.get(device)
+        key = (device, _NativeNVFP4._lane)
+        ctr = _NativeNVFP4._counters.get(key)
         if ctr is None:
-            ctr = _NativeNVFP4._counters[device] = torch.ones(1, dtype=torch.int64, device=device)
+            ctr = _NativeNVFP4._counters[key] = torch.ones(1, dtype=torch.int64, device=device)
         return ctr
 
     @classmethod
@@ -289,7 +309,7 @@ class _NativeNVFP4(BlockQuantFunc):
         transpose).  `mean` (fp32 [cols]) is subtracted first and recorded on the result."""
         cls._check(x)
         return ops.nvfp4_quantize(cls._native_input(x), transpose=transpose, stochastic=cls.stochastic,
-                                  seed=cls._seed, sf_layout=sf_layout, mean=mean,
+                                  seed=cls._seed + _NativeNVFP4._lane, sf_layout=sf_layout, mean=mean,
                                   offset_counter=cls._offset_counter(x.device) if cls.stochastic else None)
 
     @classmethod
