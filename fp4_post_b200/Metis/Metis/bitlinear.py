@@ -50,6 +50,8 @@ class PackedOperand:
         self.shape = tuple(shape)      # shape of the tensor this stands for, e.g. [B, T, K]
         self._qt = None
         self._dense = {}
+        self.mean_event = None         # recorded when the column mean exists (before the quantization that uses it)
+        self.fresh = True              # produced by kernels of the current call (cleared by a weight-cache hit)
 
     @property
     def dtype(self):
@@ -319,8 +321,14 @@ class LinearLowbitFunction(torch.autograd.Function):
                 mean = fresh
                 if mean_cache is not None:
                     mean_cache[cache_key] = (fresh.detach().reshape(1, -1), rows)
+        mean_event = None
+        if mean is not None and flat.is_cuda:
+            mean_event = torch.cuda.Event()
+            mean_event.record()             # work that needs only the mean may overlap the quantization
         q = quantizer.quantize_packed(flat, mean=mean)
-        return PackedOperand(q, flat, quantizer, tensor.shape)
+        packed = PackedOperand(q, flat, quantizer, tensor.shape)
+        packed.mean_event = mean_event
+        return packed
 
     @staticmethod
     def _backward_centred() -> bool:
@@ -456,6 +464,35 @@ def _aux_stream(device: torch.device) -> "torch.cuda.Stream":
     return st
 
 
+class _beside:
+    """`with _beside(event, device) as join: ...` issues the body on the device's second stream once
+    `event` has happened; `join(*tensors)` afterwards makes the current stream wait for it and hands
+    the tensors over.  With event None the body simply runs on the current stream."""
+
+    def __init__(self, event, device):
+        self.event, self.device, self.ctx = event, device, None
+
+    def __enter__(self):
+        if self.event is None:
+            return lambda *tensors: None
+        self.main, self.aux = torch.cuda.current_stream(self.device), _aux_stream(self.device)
+        self.aux.wait_event(self.event)
+        self.ctx = torch.cuda.stream(self.aux)
+        self.ctx.__enter__()
+
+        def join(*tensors):
+            self.main.wait_stream(self.aux)
+            for t in tensors:
+                if t is not None:
+                    t.record_stream(self.main)
+        return join
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+        return False
+
+
 # fp4_post_b200.dp.GradientReducer installs itself here: the fused backward hands it every weight
 # gradient the moment it is final (data-parallel training); None = single process.
 GRADIENT_REDUCER = None
@@ -479,13 +516,15 @@ def _row_sums(q):
     return cached
 
 
-def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, side=None):
+def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, side=None, mean_row=None):
     """dX = D^ @ W^ on the FP4 GEMM (bitlinear.py:508): contraction over N, so A = Q(D) [M, N] and
     B = W quantized along N ([K, N], transposed quantizer), plus the row vector mu_D @ W^.
     `side` = (T, U, row_vec) adds a bf16 rank-r product T @ U^T (in this product's accumulator
     units) and another row vector in the same launch."""
     w_t = wq.transposed()                                   # [K, N]
-    row = ops.nvfp4_gemv(w_t, da.mean) if da.mean is not None else None
+    row = mean_row
+    if row is None and da.mean is not None:
+        row = ops.nvfp4_gemv(w_t, da.mean)
     lowrank = None
     if side is not None:
         t_acc, u, extra = side
@@ -563,6 +602,8 @@ class LinearLowbit(torch.nn.Module):
         if self.cache_quantized_weight and self._quantized_weight_cache is not None:
             cached_key, cached_weight = self._quantized_weight_cache
             if cached_key == cache_key:
+                if isinstance(cached_weight, PackedOperand):
+                    cached_weight.fresh = False      # quantized in an earlier call: long since complete
                 return cached_weight
         if packed:
             source = weight_compute.detach()
@@ -608,8 +649,15 @@ class MetisFusedFunction(torch.autograd.Function):
         act = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
         rank1_v, rank1_r = [], []
         if xa.mean is not None:
-            rank1_v.append((None, ops.nvfp4_gemv(vq.q, xa.mean)))
-            rank1_r.append((None, ops.nvfp4_gemv(rq.q, xa.mean)))
+            # mu_x V^T and mu_x R^T need the mean only: on the second stream they run beside the
+            # quantization of x instead of after it
+            # (only with weights from the cache: fresh ones are still being quantized on this stream)
+            overlap = MetisFusedFunction.concurrent_branches and not vq.fresh and not rq.fresh
+            with _beside(xa.mean_event if overlap else None, xa.mean.device) as join:
+                row_v, row_r = ops.nvfp4_gemv(vq.q, xa.mean), ops.nvfp4_gemv(rq.q, xa.mean)
+            join(row_v, row_r)
+            rank1_v.append((None, row_v))
+            rank1_r.append((None, row_r))
         if bias is not None:
             rank1_r.append((None, bias.float()))
         yv = _packed_matmul(xa.q, vq.q, rank1=rank1_v, out_dtype=act)                 # [M, r]
@@ -638,6 +686,8 @@ class MetisFusedFunction(torch.autograd.Function):
         quantizer = F.q_backward_outputgrad
         reducer = GRADIENT_REDUCER
 
+        fuse_dx = MetisFusedFunction.fuse_dx_side_product and act == torch.bfloat16 and r <= 256
+
         def low_rank_branch():
             # ulinear: plain linear on ts = s . yv; vlinear: quantized backward with grad_output = d_yv
             ts = yv * s.to(act)
@@ -647,16 +697,22 @@ class MetisFusedFunction(torch.autograd.Function):
             grad_s = (d_ts * yv).sum(dim=0).to(s.dtype)
             d_yv = d_ts * s.to(act)
             dv = F._pack_centred(d_yv, quantizer, centred)
-            return grad_u, grad_s, dv, _packed_dw(dv, xa, M)
+            side = None
+            if fuse_dx:
+                # operands of the bf16 side product of the fused dX launch that depend on this branch only
+                v_t = vq.transposed()
+                u_side = ops.nvfp4_dequantize(v_t, torch.bfloat16, add_mean=False, unit=_one(v_t.unit))
+                side = (u_side, ops.nvfp4_gemv(v_t, dv.mean) if dv.mean is not None else None)
+            return grad_u, grad_s, dv, _packed_dw(dv, xa, M), side
 
-        def residual_branch():
+        def residual_weight_gradient(dg):
             # warmup_linear (the residual): quantized backward with grad_output = g
-            dg = F._pack_centred(g, quantizer, centred)
             grad_r = _packed_dw(dg, xa, M)
             if reducer is not None:
                 reducer.ready(grad_r)       # the big all-reduce starts here and runs beside the dX product
-            return dg, grad_r
+            return grad_r
 
+        mean_row = None
         if MetisFusedFunction.concurrent_branches and g.is_cuda:
             # The low-rank branch is a dozen small kernels that leave most of the GPU idle; on a second
             # stream they run in the shadow of the residual branch's quantizers and weight-gradient
@@ -666,28 +722,33 @@ class MetisFusedFunction(torch.autograd.Function):
                 _row_sums(x_t)              # cached on x_t and read by both branches
             main, aux = torch.cuda.current_stream(), _aux_stream(g.device)
             aux.wait_stream(main)
+            dg = F._pack_centred(g, quantizer, centred)
             with torch.cuda.stream(aux), random_lane(1):
-                grad_u, grad_s, dv, grad_v = low_rank_branch()
-            dg, grad_r = residual_branch()
+                grad_u, grad_s, dv, grad_v, side = low_rank_branch()
+                if dg.mean is not None:
+                    # mu_D R^ for the input gradient needs the mean of g only
+                    aux.wait_event(dg.mean_event)
+                    mean_row = ops.nvfp4_gemv(rq.transposed(), dg.mean)
+            grad_r = residual_weight_gradient(dg)
             main.wait_stream(aux)
             for t in (grad_u, grad_s, grad_v):
                 t.record_stream(main)       # allocated on the second stream, consumed by autograd on this one
         else:
-            grad_u, grad_s, dv, grad_v = low_rank_branch()
-            dg, grad_r = residual_branch()
-        if MetisFusedFunction.fuse_dx_side_product and act == torch.bfloat16 and r <= 256:
+            grad_u, grad_s, dv, grad_v, side = low_rank_branch()
+            dg = F._pack_centred(g, quantizer, centred)
+            grad_r = residual_weight_gradient(dg)
+        if fuse_dx:
             # dX of both branches in ONE launch: D^v @ V^ enters the residual product as a bf16
             # rank-r side product.  e2m1 x e4m3 is exact in bf16; the ratio of the two products'
             # units goes into T, rounded once to bf16 (the unfused dX_v would be rounded there too).
             v_t, r_t = vq.transposed(), rq.transposed()
+            u_side, extra = side
             ratio = (dv.q.unit * v_t.unit) / (dg.q.unit * r_t.unit)
             t_acc = ops.nvfp4_dequantize(dv.q, torch.bfloat16, add_mean=False, unit=ratio)
-            u_side = ops.nvfp4_dequantize(v_t, torch.bfloat16, add_mean=False, unit=_one(v_t.unit))
-            extra = ops.nvfp4_gemv(v_t, dv.mean) if dv.mean is not None else None
-            gx = _packed_dx(dg, rq, act, side=(t_acc, u_side, extra))
+            gx = _packed_dx(dg, rq, act, side=(t_acc, u_side, extra), mean_row=mean_row)
         else:
             gx_v = _packed_dx(dv, vq, act)
-            gx = _packed_dx(dg, rq, act, addend=gx_v)          # summed in the epilogue
+            gx = _packed_dx(dg, rq, act, addend=gx_v, mean_row=mean_row)          # summed in the epilogue
         grad_x = gx.reshape(xa.shape)
         if reducer is not None:
             for t in (grad_v, grad_s, grad_u, grad_bias):

@@ -145,7 +145,10 @@ def test_packed_backward_equals_the_chain_rule_on_the_operands_it_consumed(backw
     finally:
         F._pack_centred = staticmethod(real)
     assert len(recorded) == 3
-    xa, dv, dg = recorded                         # activation, grad of vlinear's output, grad of the residual's output
+    # activation, then (in either order) grad of vlinear's output [M, r] and grad of the residual's output [M, N]
+    xa = recorded[0]
+    dv, dg = sorted(recorded[1:], key=lambda op: op.q.shape[1])
+    assert dv.q.shape[1] == r and dg.q.shape[1] == N
 
     M = B * T
     U, s = _f64(layer.ulinear.weight), _f64(layer.s)
