@@ -202,29 +202,32 @@ struct Philox {
   }
 };
 
-// Stochastic-rounding codes of 8 values sharing scale s: the folded index plus u in (-0.5, 0.5)
-// built from 16 random bits, rounded to nearest and clamped to [0, 7] (quant.py:139-147).
+// Stochastic-rounding codes of 8 values sharing scale s: floor(folded index + U) with U uniform on
+// [0, 1) in steps of 2^-16, which rounds up with probability frac(index) (quant.py:139-147: the
+// reference adds rand - 0.5 and rounds to nearest).  Fixed point: index * 2^16 lands in the low
+// mantissa bits of a 2^23 magic add, the 16 random bits are added as an integer, bits [16, 19) are
+// the code (the index is at most 7, so the sum stays below 8 * 2^16 and the magic's own bits 0x4B00
+// do not reach the nibble).  No exact division here: the quotient only enters in distribution.
 __device__ __forceinline__ uint32_t quantize8_sr(const float* x, float s, uint4 rnd) {
-  const float two_over_s = 2.0f * rcp_approx(s);     // no exactness needed here: checked in distribution
+  const float two_over_s = 2.0f * rcp_approx(s);
   const uint32_t rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
-  const uint32_t magic_sum = 0x4B400000u * 0x11111111u;
   uint32_t acc = 0;
   float sign_lo = 0.0f, sign_hi = 0.0f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const float m = folded_index(fabsf(x[i]) * two_over_s);
-    // 16 bits -> [1, 2) by filling the top of the mantissa, then to (-0.5, 0.5)
     const uint32_t bits = (i & 1) ? (rw[i >> 1] >> 16) : (rw[i >> 1] & 0xFFFFu);
-    const float u = __uint_as_float(0x3F800000u | (bits << 7)) - (1.5f - 0.5f / 65536.0f);
-    const float q = fminf(fmaxf(m + u, 0.0f), 7.0f);
-    acc += __float_as_uint(q + METIS_ROUND_MAGIC) << (4 * i);
+    const uint32_t v = __float_as_uint(__fmaf_rn(m, 65536.0f, 8388608.0f)) + bits;
+    // code = (v >> 16) & 7, moved to nibble i
+    const uint32_t placed = (4 * i <= 16) ? (v >> (16 - 4 * i)) : (v << (4 * i - 16));
+    acc |= placed & (0x7u << (4 * i));
     const float neg = is_negative(x[i]);
     if (i < 4) sign_lo = __fmaf_rn(neg, (float)(8u << (4 * i)), sign_lo);
     else       sign_hi = __fmaf_rn(neg, (float)(8u << (4 * (i - 4))), sign_hi);
   }
   const uint32_t slo = __float_as_uint(sign_lo + 8388608.0f) & 0xFFFFu;
   const uint32_t shi = __float_as_uint(sign_hi + 8388608.0f) << 16;
-  return (acc - magic_sum) | slo | shi;
+  return acc | slo | shi;
 }
 
 // ---- loads ------------------------------------------------------------------------------------------------
