@@ -84,7 +84,7 @@ def quant_inputs():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of decisivemoments/fp4-post (the directory that holds src/)")
     ref = Path(ap.parse_args().reference)
     sys.path.insert(0, str(ref / "src"))
     from Metis.Metis.bitlinear import BitLinear, LinearLowbit, LinearLowbitFunction
