@@ -661,11 +661,13 @@ class MetisFusedFunction(torch.autograd.Function):
         if bias is not None:
             rank1_r.append((None, bias.float()))
         yv = _packed_matmul(xa.q, vq.q, rank1=rank1_v, out_dtype=act)                 # [M, r]
-        ts = yv * s.to(act)                                                           # torch.mul(self.s, y)
-        # the side product accumulates in units of 1/(unit_x * unit_R)
-        t_acc = ts.float() / (xa.q.unit * rq.q.unit)
-        y = _packed_matmul(xa.q, rq.q, rank1=rank1_r, lowrank=_bf16_factors(t_acc, u_weight.detach(), act),
-                           out_dtype=act)
+        # torch.mul(self.s, y), in the units the side product accumulates in: 1/(unit_x * unit_R)
+        if act == torch.bfloat16:
+            lowrank = (ops.lowrank_scale(yv, s, xa.q.unit, rq.q.unit), u_weight.detach().to(torch.bfloat16))
+        else:
+            ts = yv * s.to(act)
+            lowrank = _bf16_factors(ts.float() / (xa.q.unit * rq.q.unit), u_weight.detach(), act)
+        y = _packed_matmul(xa.q, rq.q, rank1=rank1_r, lowrank=lowrank, out_dtype=act)
         ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
         ctx.has_bias = bias is not None
         ctx.dims = (M, N, K)

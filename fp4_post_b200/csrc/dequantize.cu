@@ -133,9 +133,59 @@ gemv_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
   if (lane == 0) out[row] = acc * (0.5f * __ldg(unit_ptr));
 }
 
+// t = bf16( float(bf16(yv * s)) / (unit_a * unit_b) ), 8 elements per thread
+template <typename TS>
+__global__ void __launch_bounds__(256)
+lowrank_scale_kernel(const __nv_bfloat16* __restrict__ yv, int64_t M, int64_t r, int64_t ld,
+                     const TS* __restrict__ s, const float* __restrict__ unit_a,
+                     const float* __restrict__ unit_b, __nv_bfloat16* __restrict__ t) {
+  const int64_t groups_per_row = r >> 3;
+  const float div = __fmul_rn(__ldg(unit_a), __ldg(unit_b));
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * groups_per_row;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / groups_per_row, j0 = (i - m * groups_per_row) * 8;
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(yv + m * ld + j0));
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __nv_bfloat162 s2;
+      if constexpr (sizeof(TS) == 2) s2 = *reinterpret_cast<const __nv_bfloat162*>(s + j0 + 2 * k);
+      else s2 = __floats2bfloat162_rn(__ldg(s + j0 + 2 * k), __ldg(s + j0 + 2 * k + 1));
+      const __nv_bfloat162 ts = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&ww[k]), s2);   // one rounding: the product is exact in fp32
+      const uint32_t tw = *reinterpret_cast<const uint32_t*>(&ts);
+      const __nv_bfloat162 o = __floats2bfloat162_rn(__fdiv_rn(bf16_lo(tw), div), __fdiv_rn(bf16_hi(tw), div));
+      out[k] = *reinterpret_cast<const uint32_t*>(&o);
+    }
+    *reinterpret_cast<uint4*>(t + m * r + j0) = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
 }  // namespace metis
 
 using namespace metis;
+
+extern "C" int32_t metis_lowrank_scale(const void* yv, int64_t M, int64_t r, int64_t ld, const void* s,
+                                       int32_t s_dtype, const float* unit_a, const float* unit_b, void* t,
+                                       void* stream) {
+  if (!yv || !s || !unit_a || !unit_b || !t) return fail(METIS_ERR_BAD_ARGUMENT, "null pointer");
+  if (M <= 0 || r <= 0 || r % 8 != 0) return fail(METIS_ERR_BAD_SHAPE, "bad shape [%lld, %lld]: r must be a positive multiple of 8", (long long)M, (long long)r);
+  if (s_dtype != METIS_DTYPE_BF16 && s_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown s_dtype %d", s_dtype);
+  if (ld < r || ld % 8 != 0 || !aligned16(yv) || !aligned16(t) || (reinterpret_cast<uintptr_t>(s) & 3u))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "yv and t must be 16-byte aligned, ld a multiple of 8 and >= r");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int64_t blocks = ceil_div(M * (r >> 3), 256);
+  const int64_t cap = (int64_t)device_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(yv);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(t);
+  if (s_dtype == METIS_DTYPE_BF16)
+    lowrank_scale_kernel<<<(unsigned)blocks, 256, 0, st>>>(y, M, r, ld, static_cast<const __nv_bfloat16*>(s), unit_a, unit_b, o);
+  else
+    lowrank_scale_kernel<<<(unsigned)blocks, 256, 0, st>>>(y, M, r, ld, static_cast<const float*>(s), unit_a, unit_b, o);
+  METIS_CUDA_OK(cudaGetLastError());
+  return METIS_OK;
+}
 
 extern "C" int32_t metis_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales, const float* unit,
                                           int32_t sf_layout, int64_t R, int64_t C,

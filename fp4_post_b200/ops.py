@@ -229,6 +229,26 @@ def nvfp4_gemv(q: NVFP4Tensor, v: Optional[torch.Tensor] = None) -> torch.Tensor
     return out
 
 
+def lowrank_scale(yv: torch.Tensor, s: torch.Tensor, unit_a: torch.Tensor, unit_b: torch.Tensor) -> torch.Tensor:
+    """bf16( (yv * s).float() / (unit_a * unit_b) ) for bf16 yv [M, r]: torch.mul(self.s, y) of the
+    low-rank branch, in the accumulator units of the GEMM whose side product it feeds (one kernel)."""
+    _need_cuda(yv, "yv")
+    if yv.dtype != torch.bfloat16 or yv.dim() != 2 or yv.stride(1) != 1:
+        raise TypeError("yv must be a bf16 matrix with contiguous rows")
+    if s.dtype not in (torch.bfloat16, torch.float32):
+        s = s.float()
+    s = s.reshape(-1).contiguous()
+    M, r = yv.shape
+    assert s.numel() == r and s.device == yv.device
+    with _on_device(yv.device):
+        out = torch.empty((M, r), dtype=torch.bfloat16, device=yv.device)
+        rc = cabi.lib().metis_lowrank_scale(yv.data_ptr(), M, r, yv.stride(0), s.data_ptr(), _dtype_code(s, "s"),
+                                            unit_a.data_ptr(), unit_b.data_ptr(), out.data_ptr(), _stream())
+    cabi.check(rc, "metis_lowrank_scale")
+    LAUNCHES["gemv"] += 1
+    return out
+
+
 def nvfp4_gemm(a: NVFP4Tensor, b: NVFP4Tensor, *, lowrank=None, rank1=(), c: Optional[torch.Tensor] = None,
                out_dtype: torch.dtype = torch.bfloat16, alpha: float = 1.0,
                status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,

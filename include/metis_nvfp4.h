@@ -191,6 +191,17 @@ int32_t metis_nvfp4_gemv(const uint8_t* codes, const uint8_t* scales, const floa
 /* ---- GEMM --------------------------------------------------------------------------------- */
 
 /*
+ * The rank-r factor of the fused side product: t[m][j] = bf16( float(bf16(yv[m][j] * s[j])) /
+ * (unit_a * unit_b) ), i.e. torch.mul(self.s, y) of the low-rank branch (bitlinear.py:752-760)
+ * in the activation dtype, expressed in the accumulator units of the residual GEMM that adds
+ * T @ U^T.  yv and t are bf16 [M, r] (row pitch ld elements, r a multiple of 8); s is bf16 or
+ * fp32 [r] (fp32 is rounded to bf16 first, as s.to(bf16) does); unit_a, unit_b device fp32.
+ */
+int32_t metis_lowrank_scale(const void* yv, int64_t M, int64_t r, int64_t ld, const void* s,
+                            int32_t s_dtype, const float* unit_a, const float* unit_b, void* t,
+                            void* stream);
+
+/*
  * D[M,N] = g * ( sum_k A[m,k] B[n,k]  +  sum_j T[m,j] U[n,j] )
  *          + cvec0[m]*rvec0[n] + cvec1[m]*rvec1[n]  ( + C[m,n] )
  * with g = alpha * (*a_unit) * (*b_unit).

@@ -183,6 +183,23 @@ def test_a_wait_that_cannot_complete_reports_a_status_and_leaves_the_context_usa
     assert rel_l2(got, O.gemm_reference(da, db)) <= 1e-5
 
 
+@pytest.mark.parametrize("s_dtype", [torch.bfloat16, torch.float32])
+def test_lowrank_scale_equals_the_torch_expression_bit_for_bit(s_dtype):
+    g = torch.Generator().manual_seed(2)
+    yv = (torch.randn(1000, 72, generator=g) * 5).to(torch.bfloat16).to(DEV)
+    s = (torch.rand(72, generator=g) + 0.25).to(s_dtype).to(DEV)
+    ua = torch.tensor([3.1e-3], device=DEV)
+    ub = torch.tensor([7.7e-5], device=DEV)
+    want = ((yv * s.to(torch.bfloat16)).float() / (ua * ub)).to(torch.bfloat16)
+    got = ops.lowrank_scale(yv, s, ua, ub)
+    assert torch.equal(got, want)
+    padded = torch.zeros(1000, 80, dtype=torch.bfloat16, device=DEV)      # row pitch larger than r
+    padded[:, :72] = yv
+    assert torch.equal(ops.lowrank_scale(padded[:, :72], s, ua, ub), want)
+    with pytest.raises(TypeError):
+        ops.lowrank_scale(yv.float(), s, ua, ub)
+
+
 def test_argument_errors():
     qa, qb, _, _ = operands(128, 128, 256, seed=4)
     qr = ops.nvfp4_quantize(torch.zeros(128, 256, device=DEV), sf_layout=cabi.SF_ROWMAJOR)
