@@ -220,6 +220,36 @@ def test_bf16_input_gradient_fused_into_one_launch_matches_two_launches():
     assert rel_l2(grads[True], grads[False]) <= 1e-2
 
 
+def test_second_stream_gives_the_gradients_of_the_single_stream_order_bit_for_bit():
+    # round to nearest everywhere, cached weights (so that the forward overlaps too): a missing
+    # dependency between the two streams would show as a difference
+    from Metis.Metis.bitlinear import MetisFusedFunction
+    torch.manual_seed(11)
+    args = metis_args(64, cache=True)
+    layer = BitLinear(1024, 768, args=args, bias=True, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+    layer.layer_name = "streams"
+    layer.split()
+    layer = layer.to(DEV)
+    x = torch.randn(4, 512, 1024, device=DEV, dtype=torch.bfloat16)
+    gout = torch.randn(4, 512, 768, device=DEV, dtype=torch.bfloat16)
+    results = {}
+    for concurrent in (True, False, True):
+        MetisFusedFunction.concurrent_branches = concurrent
+        try:
+            for rep in range(3):                                  # repeat: a race need not show the first time
+                xin = x.clone().requires_grad_(True)
+                for p in layer.parameters():
+                    p.grad = None
+                y = layer(xin)
+                y.backward(gout)
+                got = [y.detach().clone(), xin.grad.clone()] + [p.grad.clone() for p in layer.parameters()]
+                key = results.setdefault("ref", got)
+                for a, b in zip(got, key):
+                    assert torch.equal(a, b), f"concurrent={concurrent}, repetition {rep}"
+        finally:
+            MetisFusedFunction.concurrent_branches = True
+
+
 def test_grpo_defaults_bf16_stochastic_backward_and_shared_activation():
     torch.manual_seed(1)
     block = torch.nn.Module()
