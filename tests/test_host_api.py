@@ -320,3 +320,27 @@ def test_constructor_writes_the_process_global_configuration():
     assert F.tp_simulation is False and F.tp_simulate is False      # written under one name, read under the other
     with pytest.raises(ValueError, match="Unsupported compute_dtype"):
         BitLinear(16, 8, args=args, dtype=torch.float64)
+
+
+def test_graph_capture_and_packed_export_need_a_cuda_device():
+    # no CPU fallback anywhere on the NVFP4 path: the helpers say so instead of computing something else
+    from fp4_post_b200 import checkpoint, graphs, ops
+    if torch.cuda.is_available():
+        pytest.skip("checks the message given on a machine without a GPU")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        graphs.GraphedStep(lambda: None)
+    with pytest.raises((RuntimeError, TypeError, ValueError)):
+        ops.lowrank_scale(torch.zeros(8, 8, dtype=torch.bfloat16), torch.ones(8), torch.ones(1), torch.ones(1))
+    with pytest.raises((RuntimeError, AssertionError)):
+        checkpoint.export_packed({"m.warmup_linear.weight": torch.zeros(16, 32)}, device="cuda")
+
+
+def test_random_lane_is_scoped_and_restored():
+    from fp4_post_b200.Metis.Metis.quant import Cast2NVFp4e2m1Block, random_lane
+    base = Cast2NVFp4e2m1Block._lane
+    with random_lane(3):
+        assert Cast2NVFp4e2m1Block._lane == 3
+        with random_lane(1):
+            assert Cast2NVFp4e2m1Block._lane == 1
+        assert Cast2NVFp4e2m1Block._lane == 3
+    assert Cast2NVFp4e2m1Block._lane == base
