@@ -163,14 +163,13 @@ quantize_cols_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, in
     for (int u = 0; u < TT::kUnits; ++u) {
       const int rb = rb0 + u * (kQuantThreads / TT::kCols);
       float v[16];
-      float a = 0.0f;
 #pragma unroll
       for (int r = 0; r < 16; ++r) {
         float e = (float)tile_smem[(rb * 16 + r) * TT::kCols + c];
         if (kMean) e = __fsub_rn(e, m);
         v[r] = e;
-        a = fmaxf(a, fabsf(e));
       }
+      const float a = abs_max16(v);
       const float s = block_scale_from_amax(a);
       uint32_t packed[2];
       if (kSR) {
