@@ -1,4 +1,6 @@
-// NVFP4 block-scaled GEMM with a fused bf16 rank-r side product, for sm_100a.
+// NVFP4 block-scaled GEMM with a fused bf16 rank-r side product, for sm_100a: the single-CTA kernel
+// (one row block of A, or N <= 128; larger products run on CTA pairs, gemm_tcgen05_pair.cu) and the
+// C entry point that chooses between the two.
 //
 //   D[M,N] = g * ( sum_k A[m,k] B[n,k] + sum_j T[m,j] U[n,j] ) + rank-1 terms (+ C)
 //
@@ -14,8 +16,10 @@
 //              scalar, the rank-1 terms and the optional addend, store bf16 or fp32.
 //   warps 6-9  scale movers: carry each stage's E4M3 scale tiles shared memory -> registers ->
 //              tensor memory (tcgen05.st, each warp its own 32 lanes: the four copies the
-//              block-scale layout wants).  A tcgen05.cp issued by warp 1 would do the same, but it
-//              runs in the MMA pipe and cost about as much time there as the MMAs themselves.
+//              block-scale layout wants) beside the MMAs; a tcgen05.cp issued by warp 1 does the
+//              same inside the MMA pipe, where three copies cost more than half an MMA.
+// Decode-sized products split their K loop over idle SMs: a work item is (tile, K split), partial
+// sums go to caller scratch and splitk_finish_kernel adds them up and applies the epilogue terms.
 // Hand-offs are mbarriers; every wait is bounded and reports through the status word.
 #include "gemm_common.cuh"
 
