@@ -41,6 +41,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 M_TOKENS, HIDDEN_K, HIDDEN_N, RANK = 16384, 4096, 4096, 128
+OVERLAP_SMS = 32                      # SMs the input-gradient GEMM leaves to the gradient all-reduce (N > 1)
 QUANT_ROWS, QUANT_COLS = 65536, 4096
 METRIC = "metis_nvfp4_linear_fwd_bwd_tflops"
 BYTES_PER_ELEM_BF16 = 2.5625          # 2 (bf16 in) + 0.5 (codes) + 1/16 (E4M3 scale)
@@ -281,7 +282,7 @@ def main():
     import torch.distributed as dist
     import fp4_post_b200
     from fp4_post_b200 import cabi, ops
-    from fp4_post_b200.dp import allreduce_gradients
+    from fp4_post_b200.dp import GradientReducer
     from fp4_post_b200.graphs import GraphedStep
     from fp4_post_b200.Metis.Metis.bitlinear import BitLinear
     from fp4_post_b200.grpo.grpo import MetisArgs
@@ -296,6 +297,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_MAX_CTAS", str(OVERLAP_SMS))       # the collective fits beside the capped GEMM
         dist.init_process_group("nccl", device_id=dev)
     warmup = max(3, args.warmup)
     peaks = measured_peaks()
@@ -329,11 +331,12 @@ def main():
         y.backward(grad)
         return y
 
-    def reduce_grads():
-        # what DDP does for this layer; issued after the captured step, outside the graph (NCCL's
-        # watchdog and a stream capture do not mix without extra process-wide settings)
-        if world > 1:
-            allreduce_gradients(params)
+    if world > 1:
+        # What DDP does for this layer, started inside the backward pass: the all-reduce of the residual
+        # weight's gradient begins when that gradient exists and runs beside the input-gradient GEMM,
+        # which leaves it OVERLAP_SMS SMs; the collectives are captured with the rest of the step.
+        GradientReducer(overlap_sms=OVERLAP_SMS).attach()
+    graphs = []                                    # released before the process group is destroyed
 
     def barrier():
         if world > 1:
@@ -364,17 +367,14 @@ def main():
         # captured once (fp4_post_b200/graphs.py) instead of being issued from Python every step.
         def eager_step():
             step(x_dev, g_dev)
-            reduce_grads()
         ms_eager = timed(eager_step, max(3, args.steps // 5))                        # the same step issued from Python
         launches0 = ops.launch_count()
         graphed = GraphedStep(lambda: step(x_dev, g_dev), warmup=1)
         launches_per_step = (ops.launch_count() - launches0) // 2          # one warm-up run + the capture
-        def graph_step():
-            graphed()
-            reduce_grads()
+        graphs.append(graphed)
         for _ in range(3):
-            graph_step()
-        ms_step = timed(graph_step, args.steps)
+            graphed()
+        ms_step = timed(graphed, args.steps)
         launches = launches_per_step * args.steps
 
         # ---- end to end: host inputs, checksum back -------------------------------------------------------------
@@ -399,6 +399,7 @@ def main():
             return y.float().abs().mean() + bufs[i][0].grad.float().abs().mean()
 
         e2e_graphs = [GraphedStep(lambda i=i: checked_step(i), warmup=1, pool=graphed.pool()) for i in range(2)]
+        graphs.extend(e2e_graphs)
 
         def e2e_run(n):
             main = torch.cuda.current_stream()
@@ -411,7 +412,6 @@ def main():
                 main.wait_event(ready[i])
                 check = e2e_graphs[i]()
                 consumed[i].record(main)
-                reduce_grads()
                 total += float(check.item())
             return total
 
@@ -436,7 +436,9 @@ def main():
                     fn()
             g = GraphedStep(burst, warmup=1, pool=graphed.pool())
             g()
-            return timed(g, 3) / n
+            ms = timed(g, 3) / n
+            g.release()
+            return ms
 
         ms_gemm = burst_ms(gemm, 20)
         gemm_flops = 2 * M_TOKENS * HIDDEN_N * HIDDEN_K + 2 * M_TOKENS * HIDDEN_N * RANK
@@ -473,7 +475,7 @@ def main():
             "e2e": {"value": world * flops / ms_e2e / 1e9, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": x_host.numel() * 2 + g_host.numel() * 2, "d2h_bytes_per_step": 8,
                     "ms_per_step": ms_e2e},
-            "gpu_launches": launches, "launch_mode": "one CUDA graph per step" + (" + NCCL all-reduce of the weight gradients" if world > 1 else ""), "ms_per_step_eager": ms_eager,
+            "gpu_launches": launches, "launch_mode": "one CUDA graph per step" + (" (NCCL all-reduce of the weight gradients captured inside)" if world > 1 else ""), "ms_per_step_eager": ms_eager,
             "clocks": clock_summary,
             "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_pair_kernel (CTA pairs, 256x256 tiles) forward residual GEMM + fused rank-128 product",
                          "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
@@ -485,6 +487,9 @@ def main():
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        for g in graphs:                           # graphs that hold captured NCCL kernels go first
+            g.release()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
 
 

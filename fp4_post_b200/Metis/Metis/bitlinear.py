@@ -739,6 +739,14 @@ class MetisFusedFunction(torch.autograd.Function):
             grad_u, grad_s, dv, grad_v, side = low_rank_branch()
             dg = F._pack_centred(g, quantizer, centred)
             grad_r = residual_weight_gradient(dg)
+        if reducer is not None:
+            # the small gradients are final too: their bucket goes out before the input-gradient GEMM
+            for t in (grad_v, grad_s, grad_u, grad_bias):
+                reducer.ready(t)
+            reducer.start_small()
+        # with a gradient all-reduce in flight the input-gradient GEMM leaves it some SMs
+        sm_limit = reducer.gemm_sm_limit(g.device) if reducer is not None else 0
+        saved_limit = ops.set_gemm_sm_limit(sm_limit) if sm_limit else 0
         if fuse_dx:
             # dX of both branches in ONE launch: D^v @ V^ enters the residual product as a bf16
             # rank-r side product.  e2m1 x e4m3 is exact in bf16; the ratio of the two products'
@@ -751,10 +759,10 @@ class MetisFusedFunction(torch.autograd.Function):
         else:
             gx_v = _packed_dx(dv, vq, act)
             gx = _packed_dx(dg, rq, act, addend=gx_v, mean_row=mean_row)          # summed in the epilogue
+        if sm_limit:
+            ops.set_gemm_sm_limit(saved_limit)
         grad_x = gx.reshape(xa.shape)
         if reducer is not None:
-            for t in (grad_v, grad_s, grad_u, grad_bias):
-                reducer.ready(t)
             reducer.flush()
         return grad_x, None, grad_v, None, grad_s, grad_u, grad_r, None, grad_bias
 

@@ -27,7 +27,7 @@ EXPORTS = (
     "metis_nvfp4_quantize_workspace_bytes", "metis_nvfp4_quantize", "metis_rmsnorm_nvfp4_quantize",
     "metis_nvfp4_dequantize", "metis_col_mean_workspace_bytes", "metis_col_mean", "metis_nvfp4_gemv",
     "metis_nvfp4_gemm", "metis_nvfp4_quantize_static", "metis_nvfp4_gemm_workspace_bytes",
-    "metis_lowrank_scale",
+    "metis_lowrank_scale", "metis_set_gemm_sm_limit",
 )
 
 
@@ -92,6 +92,8 @@ def lib() -> C.CDLL:
     L.metis_nvfp4_gemv.restype = i32
     L.metis_nvfp4_gemm.argtypes = [C.POINTER(GemmArgs)]
     L.metis_nvfp4_gemm.restype = i32
+    L.metis_set_gemm_sm_limit.argtypes = [i32]
+    L.metis_set_gemm_sm_limit.restype = i32
     L.metis_lowrank_scale.argtypes = [vp, i64, i64, i64, vp, i32, vp, vp, vp, vp]
     L.metis_lowrank_scale.restype = i32
     L.metis_nvfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]

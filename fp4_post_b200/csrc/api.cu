@@ -1,6 +1,8 @@
 // Status plumbing and queries of the C ABI.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace metis {
 
 static thread_local char g_last_error[512] = "";
@@ -16,6 +18,21 @@ int32_t fail(int32_t code, const char* fmt, ...) {
 }  // namespace metis
 
 extern "C" const char* metis_last_error_string(void) { return metis::g_last_error; }
+
+static std::atomic<int32_t> g_gemm_sm_limit{0};
+
+namespace metis {
+// SMs the persistent GEMM kernels may take on the current device
+int gemm_sm_budget() {
+  const int n = device_sm_count();
+  const int32_t limit = g_gemm_sm_limit.load(std::memory_order_relaxed);
+  return (limit > 0 && limit < n) ? (int)limit : n;
+}
+}  // namespace metis
+
+extern "C" int32_t metis_set_gemm_sm_limit(int32_t sms) {
+  return g_gemm_sm_limit.exchange(sms < 0 ? 0 : sms, std::memory_order_relaxed);
+}
 
 extern "C" int32_t metis_query(int32_t* abi_version, int32_t* compiled_sm, int32_t* device_sm_count) {
   if (abi_version) *abi_version = METIS_NVFP4_ABI_VERSION;

@@ -407,7 +407,7 @@ static int32_t launch_gemm(const metis_gemm_args* a, const CUtensorMap& ma, cons
   // per device and cheap, so it is simply repeated on every launch
   METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   const int64_t work = ceil_div(a->M, kBM) * ceil_div(a->N, BN) * p.splits;
-  int64_t grid = device_sm_count();
+  int64_t grid = gemm_sm_budget();
   if (grid > work) grid = work;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
   kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ma, mb, mt, mu, p);

@@ -28,13 +28,24 @@ class GradientReducer:
         loss.backward()                                    # gradients arrive summed over the group
 
     `ready(t)` starts an asynchronous in-place all-reduce of a large tensor and just remembers a small
-    one; `flush()` reduces the small ones in one flat bucket and makes the current stream wait for
+    one (with `overlap_sms` > 0 the fused backward caps its input-gradient GEMM at that many SMs fewer
+    than the device has, so that the collective really runs beside it); `flush()` reduces the small ones in one flat bucket and makes the current stream wait for
     everything.  The fused Metis backward calls both; `flush()` runs before backward returns, so
     autograd never sees a gradient that is still being reduced."""
 
-    def __init__(self, group: Optional[dist.ProcessGroup] = None, average: bool = False, small_bytes: int = 8 << 20):
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, average: bool = False, small_bytes: int = 8 << 20,
+                 overlap_sms: int = 0):
         self.group, self.average, self.small_bytes = group, average, small_bytes
-        self._work, self._small, self.bytes_reduced = [], [], 0
+        self.overlap_sms = overlap_sms        # SMs the input-gradient GEMM leaves to the collective that runs beside it
+        self._work, self._small, self._buckets, self.bytes_reduced = [], [], [], 0
+
+    def gemm_sm_limit(self, device) -> int:
+        """SM budget of the GEMM that overlaps the big all-reduce (0: no cap).  The persistent GEMM
+        kernels otherwise hold every SM and the collective's kernel would wait for them to finish."""
+        if self.overlap_sms <= 0 or not self.active():
+            return 0
+        total = torch.cuda.get_device_properties(device).multi_processor_count
+        return max(2, (total - self.overlap_sms) & ~1)
 
     def active(self) -> bool:
         return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
@@ -47,27 +58,37 @@ class GradientReducer:
             return
         self._work.append((dist.all_reduce(t, group=self.group, async_op=True), t))
 
-    def flush(self) -> None:
-        if not self.active():
+    def start_small(self) -> None:
+        """Start the all-reduce of the small gradients remembered so far (one flat bucket per dtype)
+        without waiting for it: called before a long kernel, the collective runs beside it."""
+        if not self.active() or not self._small:
             return
-        world = dist.get_world_size(self.group)
         by_dtype = {}
         for t in self._small:
             by_dtype.setdefault(t.dtype, []).append(t)
         for tensors in by_dtype.values():
             flat = _flatten_dense_tensors(tensors)
-            dist.all_reduce(flat, group=self.group)
+            self._buckets.append((dist.all_reduce(flat, group=self.group, async_op=True), flat, tensors))
+        self._small = []
+
+    def flush(self) -> None:
+        if not self.active():
+            return
+        world = dist.get_world_size(self.group)
+        self.start_small()
+        for work, flat, tensors in self._buckets:
+            work.wait()                       # the current stream waits for the collective
             if self.average:
                 flat.div_(world)
             for t, synced in zip(tensors, _unflatten_dense_tensors(flat, tensors)):
                 t.copy_(synced)
             self.bytes_reduced += flat.numel() * flat.element_size()
         for work, t in self._work:
-            work.wait()                       # the current stream waits for the collective
+            work.wait()
             if self.average:
                 t.div_(world)
             self.bytes_reduced += t.numel() * t.element_size()
-        self._work, self._small = [], []
+        self._work, self._small, self._buckets = [], [], []
 
     def attach(self) -> "GradientReducer":
         from fp4_post_b200.Metis.Metis import bitlinear

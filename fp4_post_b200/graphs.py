@@ -58,3 +58,9 @@ class GraphedStep:
 
     def pool(self):
         return self.graph.pool()
+
+    def release(self):
+        """Destroy the captured graph.  A process that captured NCCL collectives must do this before
+        `destroy_process_group()`, which otherwise waits forever for kernels the graphs still own."""
+        self.outputs = None
+        self.graph.reset()

@@ -229,6 +229,12 @@ def nvfp4_gemv(q: NVFP4Tensor, v: Optional[torch.Tensor] = None) -> torch.Tensor
     return out
 
 
+def set_gemm_sm_limit(sms: int) -> int:
+    """Cap the SMs the persistent GEMM kernels occupy (0: all); returns the previous cap.  Leaves room
+    for a collective's kernel that should run beside a GEMM."""
+    return int(cabi.lib().metis_set_gemm_sm_limit(int(sms)))
+
+
 def lowrank_scale(yv: torch.Tensor, s: torch.Tensor, unit_a: torch.Tensor, unit_b: torch.Tensor) -> torch.Tensor:
     """bf16( (yv * s).float() / (unit_a * unit_b) ) for bf16 yv [M, r]: torch.mul(self.s, y) of the
     low-rank branch, in the accumulator units of the GEMM whose side product it feeds (one kernel)."""

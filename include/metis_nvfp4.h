@@ -76,6 +76,12 @@ extern "C" {
  * device).  Any pointer may be NULL.  Replaces nothing in the reference. */
 int32_t metis_query(int32_t* abi_version, int32_t* compiled_sm, int32_t* device_sm_count);
 
+/* Upper bound on the SMs the persistent GEMM kernels occupy (0, the default: all of them).
+ * A data-parallel step that overlaps a collective with a GEMM leaves the collective's kernel
+ * some SMs this way.  Process-wide; returns the previous value.  Replaces nothing in the
+ * reference. */
+int32_t metis_set_gemm_sm_limit(int32_t sms);
+
 /* Thread-local text for the last non-zero status returned to this thread. */
 const char* metis_last_error_string(void);
 
