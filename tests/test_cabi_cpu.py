@@ -47,6 +47,15 @@ def test_size_helpers(L):
     assert L.metis_col_mean_workspace_bytes(1000, 64) == 8 * 64 * 4
 
 
+def test_gemm_sm_limit_is_a_process_wide_setting_that_returns_the_previous_value(L):
+    assert L.metis_set_gemm_sm_limit(116) == 0
+    assert L.metis_set_gemm_sm_limit(-5) == 116          # negative: no cap
+    assert L.metis_set_gemm_sm_limit(0) == 0
+    # split-K scratch: only for a single row block of A with few column tiles and a long K
+    assert L.metis_nvfp4_gemm_workspace_bytes(4096, 4096, 4096) == 0
+    assert L.metis_nvfp4_gemm_workspace_bytes(16, 64, 64) == 0
+
+
 def test_quantize_rejects_bad_arguments_without_a_device(L):
     from fp4_post_b200 import cabi
     buf = (C.c_uint8 * 4096)()
