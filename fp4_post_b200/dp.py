@@ -1,7 +1,9 @@
 """Data parallelism around the Metis layer: the token batch is sharded across ranks, weights are
 replicated, and nothing crosses GPUs inside the layer (per-tensor units and column means are per
 rank, as they are in the reference under DDP).  The one exchange of a training step is the
-all-reduce of the weight gradients, done here in one flat bucket per dtype over NCCL (gloo on CPU).
+all-reduce of the weight gradients over NCCL (gloo on CPU): large gradients in place, the small
+ones in one flat bucket per dtype; either after backward (`allreduce_gradients`) or started inside
+the fused backward, beside the input-gradient GEMM (`GradientReducer`).
 """
 from __future__ import annotations
 
