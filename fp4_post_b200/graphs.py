@@ -10,6 +10,10 @@ to the host, and the NCCL all-reduce of `fp4_post_b200.dp.GradientReducer` is ca
     x_static.copy_(batch); g_static.copy_(grad)                  # refill the static inputs
     out = step()                                                 # one graph launch
 
+Before capturing, drop (or detach) every tensor that still carries the autograd graph of an earlier
+eager step: its gradient accumulators belong to the stream of that step, and the capture is
+invalidated when backward has to synchronise with them.
+
 What a captured step freezes: shapes, the Python control flow taken during capture, and every
 host-side cache decision.  In particular a layer built with `cache_quantized_weight=True` that hit
 its cache during capture will keep using those packed weights: capture with the cache off (the weight
