@@ -63,6 +63,30 @@ def test_fused_low_rank_product(M, N, K, rank):
     assert rel_l2(got, want) <= 1e-5, rel_l2(got, want)
 
 
+# the projection shapes of the two decoder configurations (Qwen2-style 1.5B at rank 64, 7B at rank 128)
+DECODER_SHAPES = [(1536, 1536, 64), (256, 1536, 64), (8960, 1536, 64), (1536, 8960, 64),
+                  (3584, 3584, 128), (512, 3584, 128), (18944, 3584, 128), (3584, 18944, 128)]
+
+
+@pytest.mark.parametrize("N,K,rank", DECODER_SHAPES)
+def test_decoder_projection_shapes(N, K, rank):
+    M = 384
+    a = synthetic(M, K, "student", seed=N + K, dtype=torch.bfloat16)
+    b = synthetic(N, K, "weights", seed=N + K + 1, dtype=torch.bfloat16)
+    qa, qb = ops.nvfp4_quantize(a.to(DEV)), ops.nvfp4_quantize(b.to(DEV))
+    g = torch.Generator().manual_seed(rank)
+    t = (torch.randn(M, rank, generator=g) * 3).to(torch.bfloat16)
+    u = (torch.randn(N, rank, generator=g) / rank ** 0.5).to(torch.bfloat16)
+    scale = float(qa.unit.item()) * float(qb.unit.item())
+    t_acc = (t.float() / scale).to(torch.bfloat16)
+    got = run(qa, qb, lowrank=(t_acc.to(DEV), u.to(DEV)), out_dtype=torch.float32)
+    # float64 product of what the kernel was given (dequantized on the device: the decoder itself is
+    # pinned against the oracle by the quantizer tests)
+    want = qa.dequantize(torch.float32).double() @ qb.dequantize(torch.float32).double().t() \
+        + (t_acc.to(DEV).double() * scale) @ u.to(DEV).double().t()
+    assert rel_l2(got.double().cpu().numpy(), want.cpu().numpy()) <= 1e-5
+
+
 @pytest.mark.parametrize("single_cta", [False, True])
 def test_more_tiles_than_sms_ragged_edges_and_rank(single_cta):
     # every persistent CTA (or CTA pair) walks several tiles, so accumulator hand-over, stage ring
