@@ -217,6 +217,45 @@ def run_gemm_sweep(args):
         print(json.dumps(line), flush=True)
 
 
+RMSNORM_SWEEP = [(tokens, hidden) for hidden in (1536, 3584, 4096) for tokens in (1024, 8192, 65536)]
+
+
+def run_rmsnorm_sweep(args):
+    """`--only rmsnorm_sweep`: the fused RMSNorm -> NVFP4 quantizer (and the plain row quantizer on the
+    same input) over hidden x tokens; bf16 activations Student-t (nu = 3) plus a per-channel mean
+    ~N(0, 2), gamma ~N(1, 0.1), eps 1e-6.  Algorithmic GB/s: 2.5625 bytes per element."""
+    import torch
+    from fp4_post_b200 import ops
+    from fp4_post_b200.graphs import GraphedStep
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    for tokens, hidden in RMSNORM_SWEEP:
+        z = torch.randn(tokens, hidden, device=dev, generator=g)
+        chi = torch.randn(3, tokens, hidden, device=dev, generator=g).pow(2).sum(0)
+        x = (z / (chi / 3).sqrt() + 2.0 * torch.randn(1, hidden, device=dev, generator=g)).to(torch.bfloat16)
+        del z, chi
+        gamma = (1.0 + 0.1 * torch.randn(hidden, device=dev, generator=g)).to(torch.bfloat16)
+        line = {"only": "rmsnorm_sweep", "tokens": tokens, "hidden": hidden}
+        for name, fn in (("rmsnorm_quant", lambda: ops.rmsnorm_nvfp4_quantize(x, gamma, 1e-6)),
+                         ("quant_rows", lambda: ops.nvfp4_quantize(x))):
+            def burst():
+                for _ in range(args.steps):
+                    fn()
+            graphed = GraphedStep(burst, warmup=1)
+            graphed()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graphed()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            graphed.release()
+            line[name + "_us"] = round(ms * 1e3, 2)
+            line[name + "_gbs"] = round(tokens * hidden * BYTES_PER_ELEM_BF16 / ms / 1e6, 1)
+        print(json.dumps(line), flush=True)
+
+
 def run_single_kernel(args):
     """`--only K`: a few launches of one kernel on [rows, cols] bf16 (GEMM: M = rows, K = cols, N = n),
     timed with CUDA events.  Small enough to sit under an ncu capture."""
@@ -264,7 +303,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep", "rmsnorm_sweep"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
@@ -275,6 +314,8 @@ def main():
         return run_reference_arm(args)
     if args.only == "gemm_sweep":
         return run_gemm_sweep(args)
+    if args.only == "rmsnorm_sweep":
+        return run_rmsnorm_sweep(args)
     if args.only:
         return run_single_kernel(args)
 

@@ -324,8 +324,12 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
                         uint64_t seed, uint64_t offset, const uint64_t* ctr, uint32_t* codes, const WorkspaceView& ws,
                         cudaStream_t st) {
   const int bpr = (int)(cols >> 4);
-  int bx = 1;                                      // threads along the row: a power of two <= 256
+  // threads along the row: the power of two that pads the row least (hidden 1536 = 96 blocks runs
+  // as 3 x 32, not as 128 with a quarter of the lanes idle); ties go to the wider shape
+  int bx = 1;
   while (bx < bpr && bx < kQuantThreads) bx <<= 1;
+  for (int cand = bx >> 1; cand >= 32; cand >>= 1)
+    if ((bpr + cand - 1) / cand * cand < (bpr + bx - 1) / bx * bx) bx = cand;
   const int by = kQuantThreads / bx;
   const int gx = (bpr + bx - 1) / bx;
   int64_t gy = ceil_div(rows, by);

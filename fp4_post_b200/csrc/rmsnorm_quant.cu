@@ -19,7 +19,7 @@ __device__ __forceinline__ void round_bf16x2(float& a, float& b) {
   b = bf16_hi(w);
 }
 
-// A CTA is bx x by threads: bx threads (a power of two) share a row, each owning kBlocks
+// A CTA is bx x by threads: bx threads (a power of two, or a multiple of 32) share a row, each owning kBlocks
 // 16-element blocks tx, tx + bx, ...; by rows are in flight per CTA.  Row sums of squares are
 // reduced with shuffles inside a warp and through shared memory across the warps of a row.
 template <typename TX, typename TG, int kBlocks, bool kWriteNorm>
@@ -158,8 +158,8 @@ static void launch_norm(const TX* x, int64_t rows, int bpr, int bx, int64_t ld, 
   const int by = kNormThreads / bx;
   // persistent CTAs: exactly as many as are resident at once, so that all of them finish together
   int per_sm = 0;
-  if (norm_out) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_quantize_kernel<TX, TG, kBlocks, true>, kNormThreads, 0);
-  else          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_quantize_kernel<TX, TG, kBlocks, false>, kNormThreads, 0);
+  if (norm_out) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_quantize_kernel<TX, TG, kBlocks, true>, bx * by, 0);
+  else          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_quantize_kernel<TX, TG, kBlocks, false>, bx * by, 0);
   if (per_sm < 1) per_sm = 1;
   int64_t blocks = (int64_t)sms * per_sm;
   const int64_t need = ceil_div(rows, by);
@@ -179,8 +179,16 @@ static int32_t dispatch_chunks(const TX* x, int64_t rows, int64_t cols, int64_t 
                                float eps, uint32_t* codes, const WorkspaceView& ws, void* norm_out,
                                int sms, cudaStream_t st) {
   const int bpr = (int)(cols >> 4);
+  // threads along the row: whole warps, as many as the row has 32-block groups (hidden 1536 runs
+  // with 96 threads per row and two rows per CTA instead of 128 with a quarter of them idle);
+  // rows shorter than a warp take the next power of two
   int bx = 1;
-  while (bx < bpr && bx < kNormThreads) bx <<= 1;
+  if (bpr >= 32) {
+    bx = ((bpr + 31) / 32) * 32;
+    if (bx > kNormThreads) bx = kNormThreads;
+  } else {
+    while (bx < bpr) bx <<= 1;
+  }
   const int per_thread = (bpr + bx - 1) / bx;
   if (per_thread <= 1) launch_norm<TX, TG, 1>(x, rows, bpr, bx, ld, gamma, eps, codes, ws, norm_out, sms, st);
   else if (per_thread <= 2) launch_norm<TX, TG, 2>(x, rows, bpr, bx, ld, gamma, eps, codes, ws, norm_out, sms, st);
