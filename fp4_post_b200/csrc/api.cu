@@ -2,6 +2,7 @@
 #include "common.cuh"
 
 #include <atomic>
+#include <stdlib.h>
 
 namespace metis {
 
@@ -27,6 +28,14 @@ int gemm_sm_budget() {
   const int n = device_sm_count();
   const int32_t limit = g_gemm_sm_limit.load(std::memory_order_relaxed);
   return (limit > 0 && limit < n) ? (int)limit : n;
+}
+// METIS_LAUNCH_OVERLAP in the environment: a mask of the LaunchClass bits that get programmatic-serialization launches
+bool launch_overlap_enabled(int launch_class) {
+  static const int mask = [] {
+    const char* v = getenv("METIS_LAUNCH_OVERLAP");
+    return v ? atoi(v) : (kLaunchShort | kLaunchGemm | kLaunchStream);
+  }();
+  return (mask & launch_class) != 0;
 }
 }  // namespace metis
 

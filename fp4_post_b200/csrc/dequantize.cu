@@ -15,6 +15,7 @@ __global__ void __launch_bounds__(256)
 dequantize_kernel(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ scales,
                   const float* __restrict__ unit_ptr, int32_t sf_layout, int64_t R, int64_t C,
                   const float* __restrict__ add_row_vec, TO* __restrict__ out, int64_t ld) {
+  grid_dependency_wait();
   const float unit = __ldg(unit_ptr);
   const int64_t chunks_per_row = C >> 3;
   const int64_t total = R * chunks_per_row;
@@ -83,6 +84,7 @@ __global__ void __launch_bounds__(256)
 gemv_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
             const float* __restrict__ unit_ptr, int32_t sf_layout, int64_t R, int64_t C,
             const float* __restrict__ v, float* __restrict__ out) {
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= R) return;
@@ -139,6 +141,7 @@ __global__ void __launch_bounds__(256)
 lowrank_scale_kernel(const __nv_bfloat16* __restrict__ yv, int64_t M, int64_t r, int64_t ld,
                      const TS* __restrict__ s, const float* __restrict__ unit_a,
                      const float* __restrict__ unit_b, __nv_bfloat16* __restrict__ t) {
+  grid_dependency_wait();
   const int64_t groups_per_row = r >> 3;
   const float div = __fmul_rn(__ldg(unit_a), __ldg(unit_b));
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * groups_per_row;
@@ -180,9 +183,9 @@ extern "C" int32_t metis_lowrank_scale(const void* yv, int64_t M, int64_t r, int
   const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(yv);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(t);
   if (s_dtype == METIS_DTYPE_BF16)
-    lowrank_scale_kernel<<<(unsigned)blocks, 256, 0, st>>>(y, M, r, ld, static_cast<const __nv_bfloat16*>(s), unit_a, unit_b, o);
+    launch_overlapped(kLaunchShort, lowrank_scale_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, st, y, M, r, ld, static_cast<const __nv_bfloat16*>(s), unit_a, unit_b, o);
   else
-    lowrank_scale_kernel<<<(unsigned)blocks, 256, 0, st>>>(y, M, r, ld, static_cast<const float*>(s), unit_a, unit_b, o);
+    launch_overlapped(kLaunchShort, lowrank_scale_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, st, y, M, r, ld, static_cast<const float*>(s), unit_a, unit_b, o);
   METIS_CUDA_OK(cudaGetLastError());
   return METIS_OK;
 }
@@ -204,9 +207,9 @@ extern "C" int32_t metis_nvfp4_dequantize(const uint8_t* codes, const uint8_t* s
   if (blocks > cap) blocks = cap;
   const uint32_t* c32 = reinterpret_cast<const uint32_t*>(codes);
   if (out_dtype == METIS_DTYPE_BF16)
-    dequantize_kernel<<<(unsigned)blocks, 256, 0, st>>>(c32, scales, unit, sf_layout, R, C, add_row_vec, static_cast<__nv_bfloat16*>(out), ld);
+    launch_overlapped(kLaunchShort, dequantize_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, st, c32, scales, unit, sf_layout, R, C, add_row_vec, static_cast<__nv_bfloat16*>(out), ld);
   else
-    dequantize_kernel<<<(unsigned)blocks, 256, 0, st>>>(c32, scales, unit, sf_layout, R, C, add_row_vec, static_cast<float*>(out), ld);
+    launch_overlapped(kLaunchShort, dequantize_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, st, c32, scales, unit, sf_layout, R, C, add_row_vec, static_cast<float*>(out), ld);
   METIS_CUDA_OK(cudaGetLastError());
   return METIS_OK;
 }
@@ -221,8 +224,8 @@ extern "C" int32_t metis_nvfp4_gemv(const uint8_t* codes, const uint8_t* scales,
   if (v && !aligned16(v)) return fail(METIS_ERR_BAD_ALIGNMENT, "v must be 16-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const uint2* c4 = reinterpret_cast<const uint2*>(codes);
-  if (v) gemv_kernel<true><<<(unsigned)ceil_div(R, 8), 256, 0, st>>>(c4, scales, unit, sf_layout, R, C, v, out);
-  else   gemv_kernel<false><<<(unsigned)ceil_div(R, 8), 256, 0, st>>>(c4, scales, unit, sf_layout, R, C, v, out);
+  if (v) launch_overlapped(kLaunchShort, gemv_kernel<true>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
+  else   launch_overlapped(kLaunchShort, gemv_kernel<false>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
   METIS_CUDA_OK(cudaGetLastError());
   return METIS_OK;
 }

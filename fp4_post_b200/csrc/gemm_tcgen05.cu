@@ -89,6 +89,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();                                  // everything above touches shared and tensor memory only
 
   if (warp == 0) {
     // ===== TMA producer: the whole warp walks the pipeline, one elected lane issues the copies =====
@@ -144,6 +145,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
+    grid_launch_dependents();                                // the last loads of this CTA are on their way: let the next kernel's CTAs in
   } else if (warp == 1) {
     // ===== tensor-core issuer: the whole warp walks the pipeline, one elected lane issues =====
     // Keeping the loop warp-uniform lets the descriptors and addresses live in uniform registers;
@@ -351,6 +353,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 template <typename TD>
 __global__ void __launch_bounds__(256)
 splitk_finish_kernel(const GemmParams p) {
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int64_t groups_per_row = (p.N + 3) / 4;
   const float g = p.alpha * __ldg(p.a_unit) * __ldg(p.b_unit);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.M * groups_per_row; i += (int64_t)gridDim.x * blockDim.x) {
@@ -410,14 +414,12 @@ static int32_t launch_gemm(const metis_gemm_args* a, const CUtensorMap& ma, cons
   int64_t grid = gemm_sm_budget();
   if (grid > work) grid = work;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
-  kern<<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ma, mb, mt, mu, p);
-  METIS_CUDA_OK(cudaGetLastError());
+  METIS_CUDA_OK(launch_overlapped(kLaunchGemm, kern, dim3((unsigned)grid), dim3(kGemmThreads), Cfg::kSmemBytes, st, ma, mb, mt, mu, p));
   if (p.splits > 1) {
     const int64_t threads = a->M * ceil_div(a->N, 4);
     int64_t blocks = ceil_div(threads, 256);
     if (blocks > (int64_t)device_sm_count() * 8) blocks = (int64_t)device_sm_count() * 8;
-    splitk_finish_kernel<TD><<<(unsigned)blocks, 256, 0, st>>>(p);
-    METIS_CUDA_OK(cudaGetLastError());
+    METIS_CUDA_OK(launch_overlapped(kLaunchGemm, splitk_finish_kernel<TD>, dim3((unsigned)blocks), dim3(256), 0, st, p));
   }
   return METIS_OK;
 }

@@ -169,6 +169,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   cluster_sync_all();                                      // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dependency_wait();                                  // everything above touches shared and tensor memory only
 
   if (warp == 0) {
     // ===== TMA producer (both CTAs): every copy reports to the leader's barrier =====
@@ -227,6 +228,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
+    grid_launch_dependents();                                // the last loads of this CTA are on their way: let the next kernel's CTAs in
   } else if (warp == 1) {
     // ===== tensor-core issuer (leader only) =====
     if (cta == 0) {
@@ -382,13 +384,15 @@ static int32_t launch_pair_t(const metis_gemm_args* a, const CUtensorMap* maps, 
   cfg.blockDim = dim3(PairCfg::kThreads, 1, 1);
   cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
   cfg.stream = reinterpret_cast<cudaStream_t>(a->stream);
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.numAttrs = launch_overlap_enabled(kLaunchGemm) ? 2 : 1;
   METIS_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p));
   return METIS_OK;
 }

@@ -36,6 +36,7 @@ quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int6
                      const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
                      const uint64_t* __restrict__ offset_ctr, uint2* __restrict__ codes, float* __restrict__ amax_out,
                      unsigned int* __restrict__ gmax) {
+  grid_dependency_wait();
   if (kSR && offset_ctr) offset += *offset_ctr;             // per-device call counter (graph-safe stream of offsets)
   const int bc = blockIdx.x * blockDim.x + threadIdx.x;     // column block of this thread
   const int row_step = gridDim.y * blockDim.y;
@@ -113,6 +114,7 @@ quantize_cols_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, in
   uint64_t* full = reinterpret_cast<uint64_t*>(s_amax + TT::kCols * TT::kRowBlocks);   // [2]
   __shared__ int s_failed;
 
+  grid_dependency_wait();
   if (kSR && offset_ctr) offset += *offset_ctr;
   const int tid = threadIdx.x;
   const int64_t row_tiles = (rows + TT::kRows - 1) / TT::kRows;
@@ -213,6 +215,7 @@ __global__ void __launch_bounds__(kQuantThreads)
 finalize_scales_kernel(const float* __restrict__ amax, const unsigned int* __restrict__ gmax,
                        int64_t R, int64_t sf_cols, int32_t sf_layout, uint8_t* __restrict__ scales,
                        float* __restrict__ unit_out, uint64_t* __restrict__ offset_ctr) {
+  grid_dependency_wait();
   const float smax = block_scale_from_amax(__uint_as_float(*gmax));
   // quant.py:21-22; a pass-1 kernel that gave up on a load raises gmax[1]: publish NaN so that it shows
   const float unit = gmax[1] ? __uint_as_float(0x7FC00000u) : __fdiv_rn(smax, 448.0f);
@@ -268,6 +271,7 @@ template <typename T>
 __global__ void __launch_bounds__(kMeanThreads)
 col_partial_sum_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
                        int64_t rows_per_split, float* __restrict__ partial) {
+  grid_dependency_wait();
   // 32 lanes x 8 columns = 256 columns per CTA; 8 warps stride over the rows.
   __shared__ float s_part[kMeanThreads / 32][256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -296,6 +300,7 @@ col_partial_sum_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int6
 
 __global__ void col_mean_finish_kernel(const float* __restrict__ partial, int64_t splits, int64_t rows,
                                        int64_t cols, float* __restrict__ mean) {
+  grid_dependency_wait();
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   float sum = 0.0f;
@@ -347,8 +352,8 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
   if (gy < 1) gy = 1;
   const dim3 g((unsigned)gx, (unsigned)gy), b((unsigned)bx, (unsigned)by);
 #define METIS_LAUNCH_ROWS(MEAN, SR)                                                              \
-  quantize_rows_kernel<T, MEAN, SR><<<g, b, 0, st>>>(x, (int)rows, bpr, ld, mean, seed, offset, ctr, \
-                                                     reinterpret_cast<uint2*>(codes), ws.amax, ws.gmax)
+  launch_overlapped(kLaunchStream, quantize_rows_kernel<T, MEAN, SR>, g, b, 0, st, x, (int)rows, bpr, ld, mean, seed, offset, ctr, \
+                    reinterpret_cast<uint2*>(codes), ws.amax, ws.gmax)
   if (mean) { if (sr) METIS_LAUNCH_ROWS(true, true); else METIS_LAUNCH_ROWS(true, false); }
   else      { if (sr) METIS_LAUNCH_ROWS(false, true); else METIS_LAUNCH_ROWS(false, false); }
 #undef METIS_LAUNCH_ROWS
@@ -370,8 +375,8 @@ static int32_t launch_cols(const T* x, int64_t rows, int64_t cols, int64_t ld, c
   do {                                                                                                      \
     auto kern = quantize_cols_kernel<T, MEAN, SR>;                                                          \
     METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TT::kSmemBytes)); \
-    kern<<<(unsigned)grid, kQuantThreads, TT::kSmemBytes, st>>>(map, rows, cols, mean, seed, offset, ctr, codes, \
-                                                                ws.amax, ws.gmax);                          \
+    METIS_CUDA_OK(launch_overlapped(kLaunchStream, kern, dim3((unsigned)grid), dim3(kQuantThreads), TT::kSmemBytes, st, map, rows, cols, \
+                                    mean, seed, offset, ctr, codes, ws.amax, ws.gmax));                     \
   } while (0)
   if (mean) { if (sr) METIS_LAUNCH_COLS(true, true); else METIS_LAUNCH_COLS(true, false); }
   else      { if (sr) METIS_LAUNCH_COLS(false, true); else METIS_LAUNCH_COLS(false, false); }
@@ -389,9 +394,8 @@ int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t s
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  finalize_scales_kernel<<<(unsigned)blocks, kQuantThreads, 0, st>>>(ws.amax, ws.gmax, R, sf_cols,
-                                                                    sf_layout, scales, unit, offset_ctr);
-  METIS_CUDA_OK(cudaGetLastError());
+  METIS_CUDA_OK(launch_overlapped(kLaunchShort, finalize_scales_kernel, dim3((unsigned)blocks), dim3(kQuantThreads), 0, st,
+                                  ws.amax, ws.gmax, R, sf_cols, sf_layout, scales, unit, offset_ctr));
   return METIS_OK;
 }
 
@@ -495,11 +499,14 @@ extern "C" int32_t metis_col_mean(const void* x, int32_t x_dtype, int64_t rows, 
   const dim3 g((unsigned)ceil_div(cols, 256), (unsigned)splits);
   float* partial = static_cast<float*>(workspace);
   if (x_dtype == METIS_DTYPE_BF16)
-    col_partial_sum_kernel<<<g, kMeanThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, rows_per_split, partial);
+    METIS_CUDA_OK(launch_overlapped(kLaunchStream, col_partial_sum_kernel<__nv_bfloat16>, g, dim3(kMeanThreads), 0, st,
+                                    static_cast<const __nv_bfloat16*>(x), rows, cols, ld, rows_per_split, partial));
   else
-    col_partial_sum_kernel<<<g, kMeanThreads, 0, st>>>(static_cast<const float*>(x), rows, cols, ld, rows_per_split, partial);
+    METIS_CUDA_OK(launch_overlapped(kLaunchStream, col_partial_sum_kernel<float>, g, dim3(kMeanThreads), 0, st,
+                                    static_cast<const float*>(x), rows, cols, ld, rows_per_split, partial));
   METIS_CUDA_OK(cudaGetLastError());
-  col_mean_finish_kernel<<<(unsigned)ceil_div(cols, 256), 256, 0, st>>>(partial, splits, rows, cols, mean);
+  METIS_CUDA_OK(launch_overlapped(kLaunchShort, col_mean_finish_kernel, dim3((unsigned)ceil_div(cols, 256)), dim3(256), 0, st,
+                                  partial, splits, rows, cols, mean));
   METIS_CUDA_OK(cudaGetLastError());
   return METIS_OK;
 }

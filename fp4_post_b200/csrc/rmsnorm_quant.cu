@@ -28,6 +28,7 @@ rmsnorm_quantize_kernel(const TX* __restrict__ x, int rows, int blocks_per_row, 
                         const TG* __restrict__ gamma, float eps, uint2* __restrict__ codes,
                         float* __restrict__ amax_out, unsigned int* __restrict__ gmax,
                         void* __restrict__ norm_out) {
+  grid_dependency_wait();
   // The product normalised(x) * gamma has the promoted dtype: bf16 only if both are bf16.
   constexpr bool kProductBf16 = (sizeof(TX) == 2) && (sizeof(TG) == 2);
   __shared__ float s_red[kNormThreads / 32];
@@ -167,11 +168,11 @@ static void launch_norm(const TX* x, int64_t rows, int bpr, int bx, int64_t ld, 
   const dim3 b((unsigned)bx, (unsigned)by);
   uint2* c2 = reinterpret_cast<uint2*>(codes);
   if (norm_out)
-    rmsnorm_quantize_kernel<TX, TG, kBlocks, true><<<(unsigned)blocks, b, 0, st>>>(
-        x, (int)rows, bpr, ld, gamma, eps, c2, ws.amax, ws.gmax, norm_out);
+    launch_overlapped(kLaunchStream, rmsnorm_quantize_kernel<TX, TG, kBlocks, true>, dim3((unsigned)blocks), b, 0, st,
+                      x, (int)rows, bpr, ld, gamma, eps, c2, ws.amax, ws.gmax, norm_out);
   else
-    rmsnorm_quantize_kernel<TX, TG, kBlocks, false><<<(unsigned)blocks, b, 0, st>>>(
-        x, (int)rows, bpr, ld, gamma, eps, c2, ws.amax, ws.gmax, norm_out);
+    launch_overlapped(kLaunchStream, rmsnorm_quantize_kernel<TX, TG, kBlocks, false>, dim3((unsigned)blocks), b, 0, st,
+                      x, (int)rows, bpr, ld, gamma, eps, c2, ws.amax, ws.gmax, norm_out);
 }
 
 template <typename TX, typename TG>
