@@ -218,10 +218,12 @@ def run_gemm_sweep(args):
 
 
 RMSNORM_SWEEP = [(tokens, hidden) for hidden in (1536, 3584, 4096) for tokens in (1024, 8192, 65536)]
+# rollout-sized inputs: up to 32 rows take the one-launch cluster kernels, 33 and more the streaming ones
+DECODE_QUANT_SWEEP = [(tokens, hidden) for hidden in (1536, 3584, 4096) for tokens in (1, 16, 32, 33, 128)]
 
 
-def run_rmsnorm_sweep(args):
-    """`--only rmsnorm_sweep`: the fused RMSNorm -> NVFP4 quantizer (and the plain row quantizer on the
+def run_rmsnorm_sweep(args, shapes=None, tag="rmsnorm_sweep"):
+    """`--only rmsnorm_sweep` (training token counts) and `--only decode_quant_sweep` (rollout sizes): the fused RMSNorm -> NVFP4 quantizer (and the plain row quantizer on the
     same input) over hidden x tokens; bf16 activations Student-t (nu = 3) plus a per-channel mean
     ~N(0, 2), gamma ~N(1, 0.1), eps 1e-6.  Algorithmic GB/s: 2.5625 bytes per element."""
     import torch
@@ -229,13 +231,13 @@ def run_rmsnorm_sweep(args):
     from fp4_post_b200.graphs import GraphedStep
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(0)
-    for tokens, hidden in RMSNORM_SWEEP:
+    for tokens, hidden in (shapes or RMSNORM_SWEEP):
         z = torch.randn(tokens, hidden, device=dev, generator=g)
         chi = torch.randn(3, tokens, hidden, device=dev, generator=g).pow(2).sum(0)
         x = (z / (chi / 3).sqrt() + 2.0 * torch.randn(1, hidden, device=dev, generator=g)).to(torch.bfloat16)
         del z, chi
         gamma = (1.0 + 0.1 * torch.randn(hidden, device=dev, generator=g)).to(torch.bfloat16)
-        line = {"only": "rmsnorm_sweep", "tokens": tokens, "hidden": hidden}
+        line = {"only": tag, "tokens": tokens, "hidden": hidden}
         for name, fn in (("rmsnorm_quant", lambda: ops.rmsnorm_nvfp4_quantize(x, gamma, 1e-6)),
                          ("quant_rows", lambda: ops.nvfp4_quantize(x))):
             def burst():
@@ -303,7 +305,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep", "rmsnorm_sweep"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep", "rmsnorm_sweep", "decode_quant_sweep"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
@@ -316,6 +318,8 @@ def main():
         return run_gemm_sweep(args)
     if args.only == "rmsnorm_sweep":
         return run_rmsnorm_sweep(args)
+    if args.only == "decode_quant_sweep":
+        return run_rmsnorm_sweep(args, DECODE_QUANT_SWEEP, "decode_quant_sweep")
     if args.only:
         return run_single_kernel(args)
 

@@ -346,6 +346,82 @@ template <> struct RawBlock<float> {
   }
 };
 
+// ---- one-cluster kernels for small tensors ------------------------------------------------------
+// The tensor-wide maximum of a kernel that runs as ONE thread-block cluster: warp shuffle, shared
+// memory of the CTA, then every CTA reads its peers' maxima through distributed shared memory between
+// two hardware cluster barriers.  All threads of all CTAs call cluster_fmax() once, and
+// cluster_leave() before they exit (no CTA may go while a peer can still read its shared memory).
+struct ClusterMaxSmem {
+  float warp[32];
+  float cta;
+  float all;
+};
+__device__ __forceinline__ uint32_t cluster_cta_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_cta_count() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ float cluster_fmax(float v, ClusterMaxSmem& sm) {
+  const uint32_t tid = threadIdx.y * blockDim.x + threadIdx.x;
+  const uint32_t warps = (blockDim.x * blockDim.y + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((tid & 31u) == 0) sm.warp[tid >> 5] = v;
+  __syncthreads();
+  if (tid < 32) {
+    float m = tid < warps ? sm.warp[tid] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (tid == 0) sm.cta = m;
+  }
+  __syncthreads();
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (tid < 32) {
+    float m = 0.0f;
+    if (tid < cluster_cta_count()) {
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(&sm.cta)), "r"(tid));
+      asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(m) : "r"(remote) : "memory");
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (tid == 0) sm.all = m;
+  }
+  __syncthreads();
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");     // this CTA has read its peers
+  return sm.all;
+}
+__device__ __forceinline__ void cluster_leave() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// METIS_SF_MMA pads rows to a multiple of 128 and scale columns to whole tiles of 4: thread t of
+// `stride` clears those bytes (padded_words = 32-bit words of the whole scale array).  The walk is over
+// the 16-byte pieces of the layout: piece p holds rows l, l+32, l+64, l+96 (l = p % 32) of one tile, so
+// a piece whose first row is past the end is padding as a whole.
+__device__ __forceinline__ void zero_scale_padding(uint8_t* scales, int rows, int blocks_per_row, int tiles,
+                                                   int padded_words, int t, int stride) {
+  const int pieces = padded_words >> 2;
+  for (int p = t; p < pieces; p += stride) {
+    const int l = p & 31, tu = p >> 5;
+    const int rb = tu / tiles, u = tu - rb * tiles;
+    uint8_t* piece = scales + (int64_t)p * 16;
+    const int r0 = rb * 128 + l;
+    if (u * 4 >= blocks_per_row || r0 >= rows) {
+      *reinterpret_cast<uint4*>(piece) = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (r0 + 32 * c >= rows) {
+          *reinterpret_cast<uint32_t*>(piece + 4 * c) = 0u;
+        } else {
+          for (int k = 1; k < 4; ++k) if (u * 4 + k >= blocks_per_row) piece[4 * c + k] = 0;
+        }
+      }
+    }
+  }
+}
+
+// Limits of the one-cluster kernels (shared by the stand-alone and the RMSNorm-fused quantizer).
+constexpr int kSmallCtas = 8;                      // portable cluster size
+constexpr int64_t kSmallMaxPaddedWords = 16384;    // words of the tiled scale array, zero-filled padding included
+
 #endif  // __CUDACC__
 
 }  // namespace metis

@@ -153,6 +153,224 @@ rmsnorm_quantize_kernel(const TX* __restrict__ x, int rows, int blocks_per_row, 
   if (lane == 0 && running > 0.0f) atomicMax(gmax, __float_as_uint(running));
 }
 
+// ---- decode-sized inputs: one launch ---------------------------------------------------------------
+// The same row arithmetic for a handful of rows, run as ONE thread-block cluster of up to 8 CTAs: a CTA
+// of bx x by = 512 threads takes up to kNormSmallPasses groups of `by` rows, every block maximum stays in a
+// register, the tensor-wide maximum crosses the cluster through shared memory, and the threads write
+// their own E4M3 bytes: no zero-fill node, no scale pass, no scratch in global memory.
+
+// normalised(x) * gamma for one 16-element block, with the reference's roundings (llama.py:28, 31);
+// returns the block maximum.
+template <typename TX, typename TG>
+__device__ __forceinline__ float norm_block(const float (&v)[16], float rs, const TG* __restrict__ gamma16, float (&y)[16]) {
+  constexpr bool kProductBf16 = (sizeof(TX) == 2) && (sizeof(TG) == 2);
+  if constexpr (kProductBf16) {
+    RawBlock<__nv_bfloat16> graw;
+    graw.load(reinterpret_cast<const __nv_bfloat16*>(gamma16));
+    const uint32_t gw[8] = {graw.a.x, graw.a.y, graw.a.z, graw.a.w, graw.b.x, graw.b.y, graw.b.z, graw.b.w};
+    __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const __nv_bfloat162 n2 = __floats2bfloat162_rn(__fmul_rn(v[2 * i], rs), __fmul_rn(v[2 * i + 1], rs));
+      const __nv_bfloat162 p2 = __hmul2(n2, *reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+      amax2 = __hmax2(amax2, __habs2(p2));
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(&p2);
+      y[2 * i] = bf16_lo(w);
+      y[2 * i + 1] = bf16_hi(w);
+    }
+    const uint32_t aw = *reinterpret_cast<const uint32_t*>(&amax2);
+    return fmaxf(bf16_lo(aw), bf16_hi(aw));
+  } else {
+    float g[16];
+    Load16<TG>::load(gamma16, g);
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      float n0 = __fmul_rn(v[i], rs), n1 = __fmul_rn(v[i + 1], rs);
+      if (sizeof(TX) == 2) round_bf16x2(n0, n1);
+      y[i] = __fmul_rn(n0, g[i]);
+      y[i + 1] = __fmul_rn(n1, g[i + 1]);
+    }
+    return abs_max16(y);
+  }
+}
+
+constexpr int kNormSmallPasses = 2;
+constexpr int kNormSmallThreads = 512;             // twice the rows per CTA of the streaming kernel: 16 rows of 4096 in one pass
+constexpr int kNormSmallBlocks = 2;                // blocks per thread and row: rows of up to 8192 elements
+
+template <typename TX, typename TG, int kBlocks, bool kWriteNorm>
+__global__ void __launch_bounds__(kNormSmallThreads)
+rmsnorm_quantize_small_kernel(const TX* __restrict__ x, int rows, int blocks_per_row, int64_t ld,
+                              const TG* __restrict__ gamma, float eps, uint2* __restrict__ codes, int32_t sf_layout,
+                              int tiles, int padded_words, uint8_t* __restrict__ scales, float* __restrict__ unit_out,
+                              void* __restrict__ norm_out) {
+  constexpr bool kProductBf16 = (sizeof(TX) == 2) && (sizeof(TG) == 2);
+  __shared__ ClusterMaxSmem s_max;
+  __shared__ float s_red[kNormSmallPasses][kNormSmallThreads / 32];
+  __shared__ float s_rs[kNormSmallPasses][kNormSmallThreads / 32];
+  grid_dependency_wait();
+  const int bx = blockDim.x, by = blockDim.y;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int tid = ty * bx + tx;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int seg = bx < 32 ? bx : 32;                 // lanes of one row inside a warp
+  const int warps_per_row = bx >> 5;                 // 0 when a warp holds several rows
+  const float n_cols = (float)(blocks_per_row * 16);
+  const int ncta = (int)cluster_cta_count(), rank = (int)cluster_cta_rank();
+  if (sf_layout == METIS_SF_MMA)
+    zero_scale_padding(scales, rows, blocks_per_row, tiles, padded_words, rank * bx * by + tid, ncta * bx * by);
+
+  // every row of this thread is on its way before the first one is worked on
+  RawBlock<TX> raw[kNormSmallPasses][kBlocks];
+#pragma unroll
+  for (int p = 0; p < kNormSmallPasses; ++p) {
+    const int r = (p * ncta + rank) * by + ty;
+#pragma unroll
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (r < rows && bc < blocks_per_row) raw[p][j].load(x + (int64_t)r * ld + (int64_t)bc * 16);
+    }
+  }
+  // sums of squares of all passes, then one round through shared memory for all of them
+  float ss[kNormSmallPasses];
+#pragma unroll
+  for (int p = 0; p < kNormSmallPasses; ++p) {
+    const int r = (p * ncta + rank) * by + ty;
+    ss[p] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (r < rows && bc < blocks_per_row) {
+        float v[16];
+        raw[p][j].unpack(v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ss[p] = __fmaf_rn(v[i], v[i], ss[p]);
+      }
+    }
+    for (int o = seg >> 1; o > 0; o >>= 1) ss[p] += __shfl_xor_sync(0xffffffffu, ss[p], o);
+    if (warps_per_row > 1 && lane == 0) s_red[p][warp] = ss[p];
+  }
+  float rs[kNormSmallPasses];
+  if (warps_per_row > 1) {                             // uniform over the CTA
+    __syncthreads();
+    if (tx == 0) {
+#pragma unroll
+      for (int p = 0; p < kNormSmallPasses; ++p) {
+        if ((p * ncta + rank) * by + ty >= rows) continue;
+        float tot = 0.0f;
+        for (int w = 0; w < warps_per_row; ++w) tot += s_red[p][ty * warps_per_row + w];
+        s_rs[p][ty] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, n_cols), eps)));   // llama.py:23-24
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int p = 0; p < kNormSmallPasses; ++p) rs[p] = s_rs[p][ty];
+  } else {
+#pragma unroll
+    for (int p = 0; p < kNormSmallPasses; ++p) rs[p] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss[p], n_cols), eps)));
+  }
+
+  float amax[kNormSmallPasses][kBlocks];
+  float running = 0.0f;
+#pragma unroll
+  for (int p = 0; p < kNormSmallPasses; ++p) {
+    const int r = (p * ncta + rank) * by + ty;
+#pragma unroll
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      amax[p][j] = 0.0f;
+      if (!(r < rows && bc < blocks_per_row)) continue;
+      float v[16], y[16];
+      raw[p][j].unpack(v);
+      const float a = norm_block<TX, TG>(v, rs[p], gamma + (int64_t)bc * 16, y);
+      uint32_t packed[2];
+      quantize_rn<2>(y, block_scale_from_amax(a), packed);
+      const int64_t b = (int64_t)r * blocks_per_row + bc;
+      codes[b] = make_uint2(packed[0], packed[1]);
+      amax[p][j] = a;
+      running = fmaxf(running, a);
+      if (kWriteNorm) {
+        if (kProductBf16) {
+          __nv_bfloat162 o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);   // exact: already bf16 values
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(norm_out) + b * 16);
+          dst[0] = reinterpret_cast<uint4*>(o)[0];
+          dst[1] = reinterpret_cast<uint4*>(o)[1];
+        } else {
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(norm_out) + b * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
+        }
+      }
+    }
+  }
+
+  const float unit = __fdiv_rn(block_scale_from_amax(cluster_fmax(running, s_max)), 448.0f);   // quant.py:21-22
+  if (rank == 0 && tid == 0) *unit_out = unit;
+#pragma unroll
+  for (int p = 0; p < kNormSmallPasses; ++p) {
+    const int r = (p * ncta + rank) * by + ty;
+#pragma unroll
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (!(r < rows && bc < blocks_per_row)) continue;
+      const float ratio = __fdiv_rn(block_scale_from_amax(amax[p][j]), unit);                 // quant.py:23
+      const int64_t off = (sf_layout == METIS_SF_MMA) ? sf_mma_offset(r, bc, tiles) : (int64_t)r * blocks_per_row + bc;
+      scales[off] = float_to_e4m3(ratio);
+    }
+  }
+  cluster_leave();
+}
+
+// Launches the one-cluster kernel if [rows, cols] fits it; *taken says whether it did.
+template <typename TX, typename TG>
+static int32_t try_small(const TX* x, int64_t rows, int64_t cols, int64_t ld, const TG* gamma, float eps, uint8_t* codes,
+                         int32_t sf_layout, uint8_t* scales, float* unit, void* norm_out, cudaStream_t st, bool* taken) {
+  *taken = false;
+  const int bpr = (int)(cols >> 4);
+  int bx = 1;
+  if (bpr >= 32) {
+    bx = ((bpr + 31) / 32) * 32;
+    if (bx > kNormThreads) bx = kNormThreads;
+  } else {
+    while (bx < bpr) bx <<= 1;
+  }
+  const int by = kNormSmallThreads / bx;
+  const int per_thread = (bpr + bx - 1) / bx;
+  const int64_t tiles = sf_tiles_per_row(cols);
+  const int64_t padded_words = sf_layout == METIS_SF_MMA ? ceil_div(rows, 128) * 128 * tiles : 0;
+  if (per_thread > kNormSmallBlocks || rows > (int64_t)kSmallCtas * kNormSmallPasses * by ||
+      padded_words > kSmallMaxPaddedWords || !aligned16(scales))
+    return METIS_OK;
+  int64_t ctas = ceil_div(rows, by);
+  const int64_t for_padding = ceil_div(padded_words / 4, kNormSmallThreads);     // CTAs without rows still clear padding
+  if (ctas < for_padding) ctas = for_padding;
+  if (ctas > kSmallCtas) ctas = kSmallCtas;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3((unsigned)bx, (unsigned)by);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)ctas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = launch_overlap_enabled(kLaunchShort) ? 2 : 1;
+  uint2* c2 = reinterpret_cast<uint2*>(codes);
+#define METIS_NORM_SMALL(KB, WN)                                                                                       \
+  METIS_CUDA_OK(cudaLaunchKernelEx(&cfg, rmsnorm_quantize_small_kernel<TX, TG, KB, WN>, x, (int)rows, bpr, ld, gamma, eps, c2, \
+                                   sf_layout, (int)tiles, (int)padded_words, scales, unit, norm_out))
+  if (per_thread <= 1) { if (norm_out) METIS_NORM_SMALL(1, true); else METIS_NORM_SMALL(1, false); }
+  else                 { if (norm_out) METIS_NORM_SMALL(2, true); else METIS_NORM_SMALL(2, false); }
+#undef METIS_NORM_SMALL
+  *taken = true;
+  return METIS_OK;
+}
+
 template <typename TX, typename TG, int kBlocks>
 static void launch_norm(const TX* x, int64_t rows, int bpr, int bx, int64_t ld, const TG* gamma, float eps,
                         uint32_t* codes, const WorkspaceView& ws, void* norm_out, int sms, cudaStream_t st) {
@@ -220,11 +438,21 @@ extern "C" int32_t metis_rmsnorm_nvfp4_quantize(const void* x, int32_t x_dtype, 
     return fail(METIS_ERR_BAD_ALIGNMENT, "x, gamma and norm_out must be 16-byte aligned and ld a multiple of 8");
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int32_t rc;
+  bool taken = false;
+  if (x_dtype == METIS_DTYPE_BF16 && gamma_dtype == METIS_DTYPE_BF16)
+    rc = try_small(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, static_cast<const __nv_bfloat16*>(gamma), eps, codes, sf_layout, scales, unit, norm_out, st, &taken);
+  else if (x_dtype == METIS_DTYPE_BF16)
+    rc = try_small(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, static_cast<const float*>(gamma), eps, codes, sf_layout, scales, unit, norm_out, st, &taken);
+  else if (gamma_dtype == METIS_DTYPE_BF16)
+    rc = try_small(static_cast<const float*>(x), rows, cols, ld, static_cast<const __nv_bfloat16*>(gamma), eps, codes, sf_layout, scales, unit, norm_out, st, &taken);
+  else
+    rc = try_small(static_cast<const float*>(x), rows, cols, ld, static_cast<const float*>(gamma), eps, codes, sf_layout, scales, unit, norm_out, st, &taken);
+  if (rc || taken) return rc;
   const WorkspaceView ws = view_workspace(workspace);
   METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, 2 * sizeof(unsigned int), st));   // running maximum and error word
   const int sms = device_sm_count();
   uint32_t* c32 = reinterpret_cast<uint32_t*>(codes);
-  int32_t rc;
   if (x_dtype == METIS_DTYPE_BF16 && gamma_dtype == METIS_DTYPE_BF16)
     rc = dispatch_chunks(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, static_cast<const __nv_bfloat16*>(gamma), eps, c32, ws, norm_out, sms, st);
   else if (x_dtype == METIS_DTYPE_BF16)

@@ -85,6 +85,28 @@ def test_mean_subtraction_matches_oracle(transpose, dtype):
         assert_packed_equal(q, x.float().numpy(), cabi.SF_ROWMAJOR, mean=mean.numpy(), what="row mean")
 
 
+# Decode-sized tensors (at most 16384 blocks, round to nearest) take the one-launch cluster kernel;
+# these shapes sit on its limits: one block, one CTA, the largest tensor it takes, the widest decode
+# rows, row counts and widths that leave padding in the tiled layout (two row blocks; 17 scale columns:
+# a partly filled word), and the first shape past the limit (the streaming path).
+@pytest.mark.parametrize("rows,cols", [(1, 16), (1, 4096), (16, 4096), (64, 4096), (16, 8192), (16, 14336), (129, 1536),
+                                       (100, 272), (7, 1536), (65, 4096)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("layout", [cabi.SF_ROWMAJOR, cabi.SF_MMA])
+def test_one_launch_path_for_small_tensors(rows, cols, dtype, layout):
+    x = synthetic(rows, cols, "outliers", seed=rows + 3 * cols, dtype=dtype)
+    torch.empty(1 << 22, device=DEV, dtype=torch.uint8).fill_(0xA5)       # stale bytes where the outputs will land
+    q = ops.nvfp4_quantize(x.to(DEV), sf_layout=layout)
+    assert_packed_equal(q, x.float().numpy(), layout, what=f"small {rows}x{cols}")
+    if rows >= 7 and layout == cabi.SF_ROWMAJOR:
+        mean = x.float().mean(0)
+        wide = torch.zeros(rows, cols + 64, dtype=dtype)
+        wide[:, :cols] = x
+        view = wide.to(DEV)[:, :cols]                                     # leading dimension cols + 64
+        q = ops.nvfp4_quantize(view, mean=mean.to(DEV), sf_layout=layout)
+        assert_packed_equal(q, x.float().numpy(), layout, mean=mean.numpy(), what=f"small centred {rows}x{cols}")
+
+
 def test_bf16_inputs_sitting_exactly_on_rounding_ties():
     # With bf16 data an element is often an exact fraction of the block maximum that lands on a
     # rounding boundary of the reference (x = amax/8 gives |x|/(s/2) = 1.5 up to the rounding of

@@ -65,6 +65,25 @@ def test_bf16_rows(rows, cols, gdtype):
     assert mism < 2e-3
 
 
+# Decode-sized inputs (a handful of rows of up to 8192 elements) take the one-launch cluster kernel:
+# one row, rows that fill one pass / all four passes of the 8 CTAs, two blocks per thread, a hidden
+# size that is not a power of two, and the first row count past the limit (the streaming kernels).
+@pytest.mark.parametrize("rows,cols", [(1, 4096), (8, 4096), (16, 4096), (32, 4096), (33, 4096), (16, 3584),
+                                       (9, 8192), (3, 1536), (2, 64)])
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("layout", [cabi.SF_ROWMAJOR, cabi.SF_MMA])
+def test_one_launch_path_for_decode_sizes(rows, cols, gdtype, layout):
+    x = synthetic(rows, cols, "student", seed=rows * 31 + cols, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(cols + rows)
+    gamma = (1.0 + 0.1 * torch.randn(cols, generator=g)).to(gdtype)
+    torch.empty(1 << 22, device=DEV, dtype=torch.uint8).fill_(0xA5)       # stale bytes where the outputs will land
+    frac_equal, mism = check(x, gamma, 1e-6, layout)
+    assert mism < 4e-3
+    q1 = ops.rmsnorm_nvfp4_quantize(x.to(DEV), gamma.to(DEV), 1e-6, sf_layout=layout)
+    q2, _ = ops.rmsnorm_nvfp4_quantize(x.to(DEV), gamma.to(DEV), 1e-6, sf_layout=layout, return_norm=True)
+    assert torch.equal(q1.codes, q2.codes) and torch.equal(q1.scales, q2.scales) and torch.equal(q1.unit, q2.unit)
+
+
 def test_fp32_rows_and_strided_input():
     x = synthetic(40, 1024, "normal", seed=2, dtype=torch.float32)
     gamma = torch.ones(1024)
