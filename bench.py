@@ -258,6 +258,54 @@ def run_rmsnorm_sweep(args, shapes=None, tag="rmsnorm_sweep"):
         print(json.dumps(line), flush=True)
 
 
+DECODE_LAYER_SWEEP = [(4096, 4096), (4096, 14336), (14336, 4096)]     # (K, N): attention and MLP projections
+
+
+def run_decode_layer(args):
+    """`--only decode_layer`: the rollout forward of one Metis layer (no_grad: shared activation
+    quantizer, FP4 product with V, rank-r scale, FP4 residual product with the fused bf16 side
+    product; weights from the packed cache) at 1-128 tokens, `steps` forwards replayed as one CUDA
+    graph.  `weights_gbs`: packed weight bytes (R and V: 0.5625 B per element) over the time."""
+    import torch
+    import fp4_post_b200
+    from fp4_post_b200.graphs import GraphedStep
+    fp4_post_b200.install_reference_aliases()
+    from Metis.Metis.bitlinear import BitLinear
+    from grpo.grpo import MetisArgs
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    for K, N in DECODE_LAYER_SWEEP:
+        margs = MetisArgs(forward_svd_rank=RANK, activation_lowrank_svd=RANK, backward_lowrank_svd=RANK, cache_quantized_weight=True)
+        margs.device = dev
+        layer = BitLinear(K, N, args=margs, bias=False, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+        with torch.no_grad():
+            layer.warmup_linear.weight.copy_(torch.randn(N, K, device=dev) / K ** 0.5)
+        layer.layer_name = f"decode.{K}x{N}"
+        layer.split()
+        for tokens in (1, 16, 32, 128):
+            x = torch.randn(1, tokens, K, device=dev, dtype=torch.bfloat16)
+
+            def burst():
+                with torch.no_grad():
+                    for _ in range(args.steps):
+                        y = layer(x)
+                return y
+            graphed = GraphedStep(burst, warmup=2)
+            graphed()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graphed()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            graphed.release()
+            print(json.dumps({"only": "decode_layer", "tokens": tokens, "K": K, "N": N, "rank": RANK,
+                              "forward_us": round(ms * 1e3, 2),
+                              "weights_gbs": round((N * K + RANK * K) * 0.5625 / ms / 1e6, 1)}), flush=True)
+        del layer
+
+
 def run_single_kernel(args):
     """`--only K`: a few launches of one kernel on [rows, cols] bf16 (GEMM: M = rows, K = cols, N = n),
     timed with CUDA events.  Small enough to sit under an ncu capture."""
@@ -305,7 +353,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep", "rmsnorm_sweep", "decode_quant_sweep"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
@@ -318,6 +366,8 @@ def main():
         return run_gemm_sweep(args)
     if args.only == "rmsnorm_sweep":
         return run_rmsnorm_sweep(args)
+    if args.only == "decode_layer":
+        return run_decode_layer(args)
     if args.only == "decode_quant_sweep":
         return run_rmsnorm_sweep(args, DECODE_QUANT_SWEEP, "decode_quant_sweep")
     if args.only:

@@ -648,14 +648,24 @@ class MetisFusedFunction(torch.autograd.Function):
         N = rq.q.shape[0]
         act = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
         rank1_v, rank1_r = [], []
+        join_residual = None
         if xa.mean is not None:
             # mu_x V^T and mu_x R^T need the mean only: on the second stream they run beside the
             # quantization of x instead of after it
             # (only with weights from the cache: fresh ones are still being quantized on this stream)
             overlap = MetisFusedFunction.concurrent_branches and not vq.fresh and not rq.fresh
             with _beside(xa.mean_event if overlap else None, xa.mean.device) as join:
-                row_v, row_r = ops.nvfp4_gemv(vq.q, xa.mean), ops.nvfp4_gemv(rq.q, xa.mean)
-            join(row_v, row_r)
+                row_v = ops.nvfp4_gemv(vq.q, xa.mean)
+                # the product with V needs only this one: the pass over the (much larger) residual
+                # weight stays off the critical path until the residual product
+                v_ready = torch.cuda.Event() if overlap else None
+                if v_ready is not None:
+                    v_ready.record()
+                row_r = ops.nvfp4_gemv(rq.q, xa.mean)
+            if v_ready is not None:
+                torch.cuda.current_stream(xa.mean.device).wait_event(v_ready)
+                row_v.record_stream(torch.cuda.current_stream(xa.mean.device))
+                join_residual = lambda: join(row_r)
             rank1_v.append((None, row_v))
             rank1_r.append((None, row_r))
         if bias is not None:
@@ -667,6 +677,8 @@ class MetisFusedFunction(torch.autograd.Function):
         else:
             ts = yv * s.to(act)
             lowrank = _bf16_factors(ts.float() / (xa.q.unit * rq.q.unit), u_weight.detach(), act)
+        if join_residual is not None:
+            join_residual()
         y = _packed_matmul(xa.q, rq.q, rank1=rank1_r, lowrank=lowrank, out_dtype=act)
         ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
         ctx.has_bias = bias is not None

@@ -1,6 +1,8 @@
 // NVFP4 -> dense conversion and the quantized matrix x vector product.
 #include "common.cuh"
 
+#include <cuda_fp16.h>
+
 namespace metis {
 
 __device__ __forceinline__ float scale_at(const uint8_t* scales, int32_t sf_layout, int64_t r,
@@ -135,6 +137,68 @@ gemv_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
   if (lane == 0) out[row] = acc * (0.5f * __ldg(unit_ptr));
 }
 
+// The same product for a tall matrix (12288 rows and more: the wide MLP projections at rollout, where
+// this pass over the whole weight sits on the critical path of a step).  Two e2m1 codes become two
+// halves with one cvt (exact), and the 16 floats of v for a lane's block stay in registers across the
+// 4 rows of the warp (v otherwise costs 8 times the bytes of the codes in L1 traffic).  Shorter
+// matrices keep gemv_kernel: with four rows per warp they would not fill the SMs.
+__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t byte) {
+  uint32_t h2;
+  asm("{ .reg .b8 lo, hi; mov.b16 {lo, hi}, %1; cvt.rn.f16x2.e2m1x2 %0, lo; }" : "=r"(h2) : "h"((unsigned short)byte));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h2));
+}
+
+constexpr int kGemvTallRows = 4;          // rows per warp
+constexpr int64_t kGemvTallMinRows = 12288;
+
+__global__ void __launch_bounds__(256)
+gemv_tall_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
+                 const float* __restrict__ unit_ptr, int32_t sf_layout, int64_t R, int64_t C,
+                 const float* __restrict__ v, float* __restrict__ out) {
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t row0 = ((int64_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * kGemvTallRows;
+  if (row0 >= R) return;
+  const int64_t sf_cols = C >> 4;                          // blocks per row
+  const int64_t tiles = sf_tiles_per_row(C);
+  float acc[kGemvTallRows];
+#pragma unroll
+  for (int j = 0; j < kGemvTallRows; ++j) acc[j] = 0.0f;
+  for (int64_t k = lane; k < sf_cols; k += 32) {
+    float f[16];
+    const float4* v4 = reinterpret_cast<const float4*>(v + k * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 q = __ldg(v4 + i);
+      f[4 * i] = q.x; f[4 * i + 1] = q.y; f[4 * i + 2] = q.z; f[4 * i + 3] = q.w;
+    }
+#pragma unroll
+    for (int j = 0; j < kGemvTallRows; ++j) {
+      const int64_t row = row0 + j;
+      if (row >= R) break;                                 // uniform over the warp
+      const uint2 w2 = __ldg(codes + row * sf_cols + k);
+      const int64_t off = (sf_layout == METIS_SF_MMA) ? sf_mma_offset(row, k, tiles) : row * sf_cols + k;
+      const float sc = e4m3_to_float(__ldg(scales + off));
+      const uint32_t w[2] = {w2.x, w2.y};
+      float part = 0.0f;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        const float2 c = e2m1x2_to_float2((w[b >> 2] >> (8 * (b & 3))) & 0xFFu);
+        part = fmaf(c.x, f[2 * b], part);
+        part = fmaf(c.y, f[2 * b + 1], part);
+      }
+      acc[j] = fmaf(part, sc, acc[j]);
+    }
+  }
+  const float unit = __ldg(unit_ptr);
+#pragma unroll
+  for (int j = 0; j < kGemvTallRows; ++j) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    if (lane == 0 && row0 + j < R) out[row0 + j] = acc[j] * unit;
+  }
+}
+
 // t = bf16( float(bf16(yv * s)) / (unit_a * unit_b) ), 8 elements per thread
 template <typename TS>
 __global__ void __launch_bounds__(256)
@@ -224,7 +288,8 @@ extern "C" int32_t metis_nvfp4_gemv(const uint8_t* codes, const uint8_t* scales,
   if (v && !aligned16(v)) return fail(METIS_ERR_BAD_ALIGNMENT, "v must be 16-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const uint2* c4 = reinterpret_cast<const uint2*>(codes);
-  if (v) launch_overlapped(kLaunchShort, gemv_kernel<true>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
+  if (v && R >= kGemvTallMinRows) launch_overlapped(kLaunchShort, gemv_tall_kernel, dim3((unsigned)ceil_div(R, 8 * kGemvTallRows)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
+  else if (v) launch_overlapped(kLaunchShort, gemv_kernel<true>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
   else   launch_overlapped(kLaunchShort, gemv_kernel<false>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
   METIS_CUDA_OK(cudaGetLastError());
   return METIS_OK;

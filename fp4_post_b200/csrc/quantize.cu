@@ -384,7 +384,8 @@ constexpr int kMeanThreads = 256;
 template <typename T>
 __global__ void __launch_bounds__(kMeanThreads)
 col_partial_sum_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int64_t ld,
-                       int64_t rows_per_split, float* __restrict__ partial) {
+                       int64_t rows_per_split, float* __restrict__ partial, int64_t mean_of_rows) {
+  // mean_of_rows > 0 (a single split): `partial` is the mean itself, sum / mean_of_rows, as stage 2 would write it
   grid_dependency_wait();
   // 32 lanes x 8 columns = 256 columns per CTA; 8 warps stride over the rows.
   __shared__ float s_part[kMeanThreads / 32][256];
@@ -409,7 +410,7 @@ col_partial_sum_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int6
 #pragma unroll
   for (int w = 0; w < kMeanThreads / 32; ++w) sum += s_part[w][c];
   const int64_t oc = (int64_t)blockIdx.x * 256 + c;
-  if (oc < cols) partial[(int64_t)blockIdx.y * cols + oc] = sum;
+  if (oc < cols) partial[(int64_t)blockIdx.y * cols + oc] = mean_of_rows > 0 ? __fdiv_rn(__fadd_rn(0.0f, sum), (float)mean_of_rows) : sum;
 }
 
 __global__ void col_mean_finish_kernel(const float* __restrict__ partial, int64_t splits, int64_t rows,
@@ -617,17 +618,19 @@ extern "C" int32_t metis_col_mean(const void* x, int32_t x_dtype, int64_t rows, 
   const int64_t splits = col_mean_splits(rows);
   const int64_t rows_per_split = ceil_div(rows, splits);
   const dim3 g((unsigned)ceil_div(cols, 256), (unsigned)splits);
-  float* partial = static_cast<float*>(workspace);
+  // up to 128 rows there is one split: stage 1 writes the mean itself (0 + sum, then the same division)
+  const bool single = splits == 1;
+  float* partial = single ? mean : static_cast<float*>(workspace);
+  const int64_t mean_of_rows = single ? rows : 0;
   if (x_dtype == METIS_DTYPE_BF16)
     METIS_CUDA_OK(launch_overlapped(kLaunchStream, col_partial_sum_kernel<__nv_bfloat16>, g, dim3(kMeanThreads), 0, st,
-                                    static_cast<const __nv_bfloat16*>(x), rows, cols, ld, rows_per_split, partial));
+                                    static_cast<const __nv_bfloat16*>(x), rows, cols, ld, rows_per_split, partial, mean_of_rows));
   else
     METIS_CUDA_OK(launch_overlapped(kLaunchStream, col_partial_sum_kernel<float>, g, dim3(kMeanThreads), 0, st,
-                                    static_cast<const float*>(x), rows, cols, ld, rows_per_split, partial));
-  METIS_CUDA_OK(cudaGetLastError());
-  METIS_CUDA_OK(launch_overlapped(kLaunchShort, col_mean_finish_kernel, dim3((unsigned)ceil_div(cols, 256)), dim3(256), 0, st,
-                                  partial, splits, rows, cols, mean));
-  METIS_CUDA_OK(cudaGetLastError());
+                                    static_cast<const float*>(x), rows, cols, ld, rows_per_split, partial, mean_of_rows));
+  if (!single)
+    METIS_CUDA_OK(launch_overlapped(kLaunchShort, col_mean_finish_kernel, dim3((unsigned)ceil_div(cols, 256)), dim3(256), 0, st,
+                                    partial, splits, rows, cols, mean));
   return METIS_OK;
 }
 
