@@ -20,6 +20,11 @@
  *    describes the last non-zero status of the calling thread.
  *  - Device-side bounded waits (mbarrier, TMEM allocation) never spin forever: on expiry
  *    the kernel writes a positive code to the caller's optional `status` word and exits.
+ *  - Kernels are launched with programmatic stream serialization: a kernel's CTAs may become
+ *    resident while the previous kernel of the stream drains, and wait on the device
+ *    (griddepcontrol.wait) before their first global access, so ordering on the stream is
+ *    what it would be with plain launches.  METIS_LAUNCH_OVERLAP=0 in the environment of the
+ *    process (read once) gives plain launches.
  *
  * NVFP4 tensor representation (what the quantizers write and the GEMM reads)
  *  - codes : uint8 [R, C/2]; element 2i of a row is the low nibble of byte i, element
@@ -121,6 +126,11 @@ int64_t metis_nvfp4_quantize_workspace_bytes(int64_t R, int64_t C);
  * stream draw fresh bits although their arguments are identical, which is what a captured
  * CUDA graph needs when it is replayed (the reference's torch.rand advances a device-side
  * Philox offset in the same situation).
+ *
+ * Launches: large tensors take a zero-fill of the workspace header, one streaming pass and a scale
+ * pass.  Round-to-nearest, untransposed tensors of at most 16384 blocks (rollout-sized
+ * activations) take ONE kernel that runs as a single thread-block cluster and does not touch the
+ * workspace (it must still be passed and large enough); results are bit-identical.
  */
 int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
                              const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,
@@ -159,6 +169,8 @@ int32_t metis_nvfp4_quantize_static(const void* x, int32_t x_dtype, int64_t rows
  * gamma is bf16 or fp32 [cols]; when x and gamma are both bf16 the product is rounded to
  * bf16 as torch does.  norm_out (optional, dtype of that product, [rows, cols]) receives y.
  * Round-to-nearest only; other outputs as metis_nvfp4_quantize without METIS_Q_TRANSPOSE.
+ * Up to 32 rows of 4096 elements (more rows when they are shorter, none past 8192 elements) run as
+ * one cluster kernel like the small tensors of metis_nvfp4_quantize.
  */
 int32_t metis_rmsnorm_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64_t cols,
                                      int64_t ld, const void* gamma, int32_t gamma_dtype, float eps,
@@ -179,7 +191,7 @@ int32_t metis_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales, cons
 /*
  * Column means of x [rows, cols]: mean[c] = (sum_r x[r][c]) / rows in fp32
  * (input_flat.mean(dim=0), bitlinear.py:326).  Deterministic summation order.
- * workspace: at least metis_col_mean_workspace_bytes(rows, cols) bytes.
+ * workspace: at least metis_col_mean_workspace_bytes(rows, cols) bytes (unused, one launch, up to 128 rows).
  */
 int64_t metis_col_mean_workspace_bytes(int64_t rows, int64_t cols);
 int32_t metis_col_mean(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
