@@ -393,6 +393,9 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("NCCL_MAX_CTAS", str(OVERLAP_SMS))       # the collective fits beside the capped GEMM
+        # plain launches beside captured collectives: the configuration the multi-GPU numbers were taken in
+        # (programmatic serialization changes nothing for the training step on one GPU)
+        os.environ.setdefault("METIS_LAUNCH_OVERLAP", "0")
         dist.init_process_group("nccl", device_id=dev)
     warmup = max(3, args.warmup)
     peaks = measured_peaks()
