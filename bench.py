@@ -20,10 +20,16 @@ The JSON line also carries
                rate, the dense NVFP4 : bf16 ratio of the part
   quant        the HBM-bound kernels alone: fused RMSNorm->NVFP4 and the plain quantizer at hidden
                4096 x 65536 tokens, algorithmic GB/s against the measured copy bandwidth
-  cpu_baseline the CPU oracle of the same layer (the reference's fake-quant algorithm restated,
-               oracle/metis_layer.py) timed on this host's cores on a slice of the same workload
+  cpu_baseline the same layer on this host's cores on a slice of the same workload: the reference's own
+               BitLinear where oracle/build_ref.py has placed its modules in oracle/_ref ("reference"), else
+               the restated oracle oracle/metis_layer.py ("port"); `config1` adds the baseline's first
+               configuration (2048^3, rank 64, fp32), forward and backward, all threads and one thread
+  value_cached_weights  the step with the opt-in packed-weight cache (the headline re-quantizes the weights
+               every step, the reference's default)
 
 `--impl reference` times that CPU implementation as the whole job (rank 0 only).
+`--only gemm_yardstick` times the vendor library's block-scaled NVFP4 GEMM (torch._scaled_mm) at the
+benchmark's shapes: what a library kernel reaches on the same box and clocks (never on the product path).
 """
 from __future__ import annotations
 
@@ -49,7 +55,8 @@ BYTES_PER_ELEM_BF16 = 2.5625          # 2 (bf16 in) + 0.5 (codes) + 1/16 (E4M3 s
 # M = 8192 (31.6 MB read + 21.8 MB written) scaled by the rows processed; the profile summary
 # profiles/nvfp4_gemm_pair_8192x4096x4096_r128.md holds the capture and its command.
 GEMM_DRAM_BYTES_PER_LAUNCH = int(53.4e6 * M_TOKENS / 8192)
-GEMM_DRAM_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum at M = 8192, scaled by M"
+GEMM_DRAM_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum at M = 8192, scaled by M; below the algorithmic bytes "
+                    "because the part of the output still in L2 when the kernel ends is not counted")
 
 
 def layer_flops(M, N, K, r):
@@ -117,46 +124,110 @@ class ClockSampler:
 
 # ---- CPU arm ------------------------------------------------------------------------------------------------
 
-def cpu_layer_step_seconds(tokens, steps, warmup, threads):
-    """fwd+bwd of the same layer on the CPU oracle for `tokens` tokens; median seconds per step."""
+def _cpu_factors(N, K, r, g):
+    """A rank-r split without the (slow, one-time) exact SVD: random factors of the right scale."""
     import torch
-    from oracle import metis_layer as ML
+    W = torch.randn(N, K, generator=g) / K ** 0.5
+    U = torch.randn(N, r, generator=g) / N ** 0.5
+    V = torch.randn(r, K, generator=g) / K ** 0.5
+    s = torch.rand(r, generator=g) + 0.5
+    return U, s, V, W - U @ torch.diag(s) @ V
+
+
+def cpu_kind():
+    """"reference": the reference's own BitLinear (oracle/_ref, placed there by oracle/build_ref.py where a
+    checkout exists); "port": the restated oracle (oracle/metis_layer.py)."""
+    from oracle import build_ref
+    return "reference" if build_ref.available() else "port"
+
+
+def cpu_layer_times(tokens, K, N, r, steps, warmup, threads, kind, outliers=True):
+    """fwd and bwd of one Metis layer on the host for `tokens` tokens, fp32, mean mode, RTN forward and
+    stochastic-rounding backward (the port rounds to nearest in the backward too); median seconds of
+    the forward and of the backward."""
+    import torch
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
-    x = torch.randn(1, tokens, HIDDEN_K, generator=g)
-    x[..., torch.randperm(HIDDEN_K, generator=g)[: HIDDEN_K // 100]] *= 20
-    W = torch.randn(HIDDEN_N, HIDDEN_K, generator=g) / HIDDEN_K ** 0.5
-    grad = torch.randn(1, tokens, HIDDEN_N, generator=g)
-    # a rank-r split without the (slow, one-time) exact SVD: random orthogonal-ish factors
-    U = torch.randn(HIDDEN_N, RANK, generator=g) / HIDDEN_N ** 0.5
-    V = torch.randn(RANK, HIDDEN_K, generator=g) / HIDDEN_K ** 0.5
-    s = torch.rand(RANK, generator=g) + 0.5
-    R = W - U @ torch.diag(s) @ V
-    times = []
-    for i in range(warmup + steps):
-        t0 = time.perf_counter()
-        y, saved = ML.forward(x, U, s, V, R, None, threads=threads)
-        ML.backward(grad, saved, U, s, has_bias=False, threads=threads)
-        if i >= warmup:
-            times.append(time.perf_counter() - t0)
-    return statistics.median(times)
+    x = torch.randn(1, tokens, K, generator=g)
+    if outliers:
+        x[..., torch.randperm(K, generator=g)[: max(1, K // 100)]] *= 20
+    grad = torch.randn(1, tokens, N, generator=g)
+    U, s, V, R = _cpu_factors(N, K, r, g)
+    fwd, bwd = [], []
+    if kind == "reference":
+        from oracle import ref_layer
+        layer = ref_layer.assemble(U, s, V, R)
+        xin = x.requires_grad_(True)
+        for i in range(warmup + steps):
+            for p in layer.parameters():
+                p.grad = None
+            xin.grad = None
+            t0 = time.perf_counter()
+            y = layer(xin)
+            t1 = time.perf_counter()
+            y.backward(grad)
+            t2 = time.perf_counter()
+            if i >= warmup:
+                fwd.append(t1 - t0); bwd.append(t2 - t1)
+    else:
+        from oracle import metis_layer as ML
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            y, saved = ML.forward(x, U, s, V, R, None, threads=threads)
+            t1 = time.perf_counter()
+            ML.backward(grad, saved, U, s, has_bias=False, threads=threads)
+            t2 = time.perf_counter()
+            if i >= warmup:
+                fwd.append(t1 - t0); bwd.append(t2 - t1)
+    return statistics.median(fwd), statistics.median(bwd)
+
+
+def cpu_c1_lines(kind, threads):
+    """Configuration 1 of the baseline (x [2048 x 2048] fp32 with 1 % outlier channels, rank 64) on the
+    host: forward and backward separately, all threads and one thread."""
+    M = K = N = 2048
+    r = 64
+    f_fwd = 2 * M * N * K + 2 * M * r * (K + N)
+    out = {"shape": "M=K=N=2048, rank 64, fp32", "kind": kind}
+    for label, thr, steps, warm in (("all_threads", threads, 5, 2), ("one_thread", 1, 2, 1)):
+        fwd, bwd = cpu_layer_times(M, K, N, r, steps, warm, thr, kind)
+        out[label] = {"threads": thr, "fwd_ms": round(fwd * 1e3, 1), "bwd_ms": round(bwd * 1e3, 1),
+                      "fwd_tflops": round(f_fwd / fwd / 1e12, 4), "bwd_tflops": round(2 * f_fwd / bwd / 1e12, 4),
+                      "timed_steps": steps}
+    return out
 
 
 def run_reference_arm(args):
+    """The CPU implementation of the path as the whole job: every step is forward + backward of the same
+    layer on a sample of the token batch, sized from one probe step so that the run ends within about
+    two minutes; ms_per_step is the time of what ran."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = len(os.sched_getaffinity(0))
-    tokens = 2048                                  # bounded sample: 1/8 of the token batch per step
-    sec = cpu_layer_step_seconds(tokens, max(1, args.steps), max(0, min(args.warmup, 1)), threads)
+    kind = cpu_kind()
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    probe_tokens = 1024
+    f, b = cpu_layer_times(probe_tokens, HIDDEN_K, HIDDEN_N, RANK, 1, 1, threads, kind)
+    per_token = (f + b) / probe_tokens
+    tokens = M_TOKENS
+    while tokens > probe_tokens and per_token * tokens * (steps + warmup) > 120.0:
+        tokens //= 2
+    fwd, bwd = cpu_layer_times(tokens, HIDDEN_K, HIDDEN_N, RANK, steps, warmup, threads, kind)
+    sec = fwd + bwd
     tf = layer_flops(tokens, HIDDEN_N, HIDDEN_K, RANK) / sec / 1e12
+    sample = (f"{tokens} of {M_TOKENS} tokens per step, same N, K, r, fp32 on {threads} host threads; "
+              f"ms_per_step is the time of that sample")
+    config = workload_config(1)
+    config["sample_tokens_per_step"] = tokens
+    config["parallelism"] = "one host process (the CPU arm does not shard)"
     line = {
         "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * (M_TOKENS / tokens),
+        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (simulated in fp32)",
-        "data": "synthetic", "config": workload_config(1),
-        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                         "sample": f"{tokens} of {M_TOKENS} tokens per step, same N, K, r; ms_per_step is scaled to the full batch"},
+        "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample,
+                         "fwd_ms": fwd * 1e3, "bwd_ms": bwd * 1e3},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -306,6 +377,41 @@ def run_decode_layer(args):
         del layer
 
 
+def run_gemm_yardstick(args):
+    """`--only gemm_yardstick`: cuBLASLt's NVFP4 GEMM (e2m1 codes, E4M3 scales per 16 elements, through
+    torch._scaled_mm) on random codes and unit scales; one JSON line per shape.  A yardstick for the
+    tensor-core roofline on this box, not part of the library."""
+    import torch
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    fp4, e4m3 = getattr(torch, "float4_e2m1fn_x2", None), torch.float8_e4m3fn
+    for M, N, K in ((16384, 4096, 4096), (16384, 14336, 4096), (16384, 4096, 14336), (4096, 4096, 4096)):
+        line = {"only": "gemm_yardstick", "M": M, "N": N, "K": K}
+        try:
+            if fp4 is None:
+                raise RuntimeError("this torch has no float4_e2m1fn_x2")
+            a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev).view(fp4)
+            b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev).view(fp4)
+            pad = lambda rows: (rows + 127) // 128 * 128
+            sa = torch.ones(pad(M) * ((K // 16 + 3) // 4 * 4), device=dev).to(e4m3)
+            sb = torch.ones(pad(N) * ((K // 16 + 3) // 4 * 4), device=dev).to(e4m3)
+            fn = lambda: torch._scaled_mm(a, b.t(), sa, sb, out_dtype=torch.bfloat16)
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            line.update(ms_per_call=round(ms, 4), tflops=round(2 * M * N * K / ms / 1e9, 1))
+        except Exception as exc:                      # the yardstick is optional: say why it is missing
+            line["unavailable"] = f"{type(exc).__name__}: {str(exc)[:200]}"
+        print(json.dumps(line), flush=True)
+
+
 def run_single_kernel(args):
     """`--only K`: a few launches of one kernel on [rows, cols] bf16 (GEMM: M = rows, K = cols, N = n),
     timed with CUDA events.  Small enough to sit under an ncu capture."""
@@ -353,7 +459,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
@@ -364,6 +470,8 @@ def main():
         return run_reference_arm(args)
     if args.only == "gemm_sweep":
         return run_gemm_sweep(args)
+    if args.only == "gemm_yardstick":
+        return run_gemm_yardstick(args)
     if args.only == "rmsnorm_sweep":
         return run_rmsnorm_sweep(args)
     if args.only == "decode_layer":
@@ -402,8 +510,11 @@ def main():
 
     # ---- the layer ----------------------------------------------------------------------------------------------
     torch.manual_seed(0)
+    # The reference's default flags (src/grpo/grpo.py:62-103): the packed-weight cache is OFF, so every step
+    # quantizes R and V again (row-major for the forward, transposed for the input gradient), as a training
+    # loop whose optimizer changes the weights every step has to.
     margs = MetisArgs(forward_svd_rank=RANK, activation_lowrank_svd=RANK, backward_lowrank_svd=RANK,
-                      cache_quantized_weight=True)
+                      cache_quantized_weight=False)
     margs.device = dev
     layer = BitLinear(HIDDEN_K, HIDDEN_N, args=margs, bias=False, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
     with torch.no_grad():
@@ -474,6 +585,33 @@ def main():
             graphed()
         ms_step = timed(graphed, args.steps)
         launches = launches_per_step * args.steps
+
+        # the same step with the opt-in packed-weight cache (weights that do not change between steps:
+        # evaluation, rollout, frozen layers): their four quantizations leave the step
+        def set_weight_cache(on):
+            for m in (layer.warmup_linear, layer.vlinear):
+                m.cache_quantized_weight = on
+                m._quantized_weight_cache = None
+        set_weight_cache(True)
+        for _ in range(2):
+            step(x_dev, g_dev)
+        cached = GraphedStep(lambda: step(x_dev, g_dev), warmup=1, pool=graphed.pool())
+        graphs.append(cached)
+        cached()
+        ms_cached = timed(cached, max(3, args.steps // 2))
+        set_weight_cache(False)
+        # and in the mode whose gradients meet the 1e-3 bar against the reference's own (the reference's
+        # wiring: native quantizers, dequantized operands, torch.matmul), issued from Python
+        ms_dense = None
+        if world == 1:
+            from fp4_post_b200.Metis.Metis.bitlinear import LinearLowbitFunction
+            LinearLowbitFunction.gemm_mode = "dense"
+            try:
+                for _ in range(2):
+                    step(x_dev, g_dev)
+                ms_dense = timed(eager_step, 3)
+            finally:
+                LinearLowbitFunction.gemm_mode = "packed"
 
         # ---- end to end: host inputs, checksum back -------------------------------------------------------------
         # Inputs arrive the way a training input pipeline delivers them: two device buffers, the copy
@@ -557,10 +695,11 @@ def main():
     cpu = None
     if rank == 0 and world == 1:
         threads = len(os.sched_getaffinity(0))
-        tokens = 2048
-        sec = cpu_layer_step_seconds(tokens, steps=2, warmup=1, threads=threads)
-        cpu = {"value": layer_flops(tokens, HIDDEN_N, HIDDEN_K, RANK) / sec / 1e12, "unit": "TFLOP/s", "cores": threads,
-               "kind": "port", "sample": f"{tokens} of {M_TOKENS} tokens, same N, K, r, 2 timed steps after 1 warm-up"}
+        tokens, kind = 2048, cpu_kind()
+        fwd, bwd = cpu_layer_times(tokens, HIDDEN_K, HIDDEN_N, RANK, steps=2, warmup=1, threads=threads, kind=kind)
+        cpu = {"value": layer_flops(tokens, HIDDEN_N, HIDDEN_K, RANK) / (fwd + bwd) / 1e12, "unit": "TFLOP/s", "cores": threads,
+               "kind": kind, "sample": f"{tokens} of {M_TOKENS} tokens, same N, K, r, fp32, 2 timed steps after 1 warm-up",
+               "config1": cpu_c1_lines(kind, threads)}
 
     if rank == 0:
         fp4_peak = 4.0 * peaks["bf16_tflops"]
@@ -573,12 +712,20 @@ def main():
             "e2e": {"value": world * flops / ms_e2e / 1e9, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": x_host.numel() * 2 + g_host.numel() * 2, "d2h_bytes_per_step": 8,
                     "ms_per_step": ms_e2e},
+            "value_cached_weights": world * flops / ms_cached / 1e9, "ms_per_step_cached_weights": ms_cached,
+            "gemm_mode": {"timed": "packed: FP4 operands on the tensor-core GEMM; dX and dW contract over operands re-quantized along "
+                                   "N and along tokens (same expectation as the reference's gradients, rel-L2 up to 0.25 from them; "
+                                   "tests/test_layer_gpu.py)",
+                          "dense_ms_per_step": ms_dense,
+                          "dense": "reference wiring (fake-quantized operands, torch.matmul): gradients within 1e-3 of the reference's"},
             "gpu_launches": launches, "launch_mode": "one CUDA graph per step" + (" (NCCL all-reduce of the weight gradients captured inside)" if world > 1 else ""), "ms_per_step_eager": ms_eager,
             "clocks": clock_summary,
             "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_pair_kernel (CTA pairs, 256x256 tiles) forward residual GEMM + fused rank-128 product",
                          "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
                          "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "traffic_source": GEMM_DRAM_SOURCE, "peak_source": f"4 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s)",
-                         "frac_of_nominal_9000": achieved / 9000.0, "ms_per_launch": ms_gemm},
+                         "frac_of_nominal_9000": achieved / 9000.0, "ms_per_launch": ms_gemm,
+                         "step_frac": flops / ms_step / 1e9 / fp4_peak, "step_frac_of_nominal_9000": flops / ms_step / 1e9 / 9000.0,
+                         "hbm_kernels": quant_lines, "hbm_peak_gbs": peaks["hbm_gbs"]},
             "quant": quant_lines,
             "hbm_peak_gbs": peaks["hbm_gbs"],
             "cpu_baseline": cpu,

@@ -318,7 +318,8 @@ def test_decode_keeps_a_running_mean_and_rollout_uses_the_fp4_weights():
         me1, n1 = layer.mean_cache["dec.shared"]
     assert n1 == 68 and y.shape == (4, 1, 256)
     want = (me0.float() * 64 + step.float().reshape(-1, 256).mean(0) * 4) / 68
-    assert torch.allclose(me1.float().reshape(-1), want.reshape(-1), atol=1e-2)
+    assert me1.dtype == torch.float32       # the cache entry is the kernel's fp32 mean, not a bf16 copy
+    assert torch.allclose(me1.reshape(-1), want.reshape(-1), rtol=1e-6, atol=1e-6)
     # same answer as the dense merged-weight path of the reference, up to bf16 rounding
     F.gemm_mode = "dense"
     layer.mean_cache.clear()

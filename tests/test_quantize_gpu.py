@@ -218,3 +218,31 @@ def test_stochastic_rounding_depends_on_seed_and_offset_only():
     deq = ops.nvfp4_quantize(x, stochastic=True, seed=9, offset=3, sf_layout=cabi.SF_ROWMAJOR).dequantize(torch.float32)
     err = (deq - x.float()).mean().abs().item()
     assert err < 5e-3
+
+
+def test_every_bf16_value_below_a_block_maximum():
+    # Exact ties are what an approximate division gets wrong, and with bf16 inputs they are common (a
+    # quotient of two 8-bit mantissas).  For 4096 block maxima spread over the bf16 range, every bf16
+    # value of the seven binades below the maximum (both signs) shares a block with it: 896 magnitudes
+    # per maximum, 15 per block beside the maximum.  Codes, scales and unit against the oracle.
+    top = torch.arange(0x0F80, 0x7000, 6, dtype=torch.int32)[:4096]              # bf16 bit patterns: normal, far from the ends
+    rows = []
+    for t in top.tolist():
+        mags = torch.arange(t - 896, t, dtype=torch.int32).clamp(min=0)          # the 7 binades below (and up to) t
+        signs = (torch.arange(896) % 3 == 0).int() << 15
+        vals = (mags | signs).to(torch.int16).view(torch.bfloat16)
+        vals = torch.cat([vals, vals[:4]])                                       # 900 = 60 blocks x 15
+        block = torch.empty(60, 16, dtype=torch.bfloat16)
+        block[:, 0] = torch.tensor([t], dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+        block[:, 1:] = vals.view(60, 15)
+        rows.append(block.view(-1))
+    x = torch.stack(rows)                                                        # [4096, 960]
+    q = ops.nvfp4_quantize(x.to(DEV), sf_layout=cabi.SF_ROWMAJOR)
+    codes, scales, unit = packed_to_numpy(q)
+    ocodes, oscales, ounit, _ = O.quantize(x.float().numpy(), threads=4)
+    assert unit == ounit
+    assert np.array_equal(codes, ocodes), f"{int((codes != ocodes).sum())} code bytes differ"
+    assert np.array_equal(scales, oscales.reshape(-1))
+    # the transposed kernel sees the same blocks as columns
+    qt = ops.nvfp4_quantize(x.t().contiguous().to(DEV), transpose=True, sf_layout=cabi.SF_ROWMAJOR)
+    assert np.array_equal(qt.codes.cpu().numpy(), ocodes) and np.array_equal(qt.scales.cpu().numpy(), oscales.reshape(-1))
