@@ -51,6 +51,7 @@ OVERLAP_SMS = 32                      # SMs the input-gradient GEMM leaves to th
 QUANT_ROWS, QUANT_COLS = 65536, 4096
 METRIC = "metis_nvfp4_linear_fwd_bwd_tflops"
 BYTES_PER_ELEM_BF16 = 2.5625          # 2 (bf16 in) + 0.5 (codes) + 1/16 (E4M3 scale)
+BYTES_PER_ELEM_DUAL_BF16 = 3.125      # one read, two packed outputs (row-major and transposed)
 # DRAM bytes (read + write) of one forward GEMM launch, from an ncu capture of the same kernel on
 # M = 8192 (31.6 MB read + 21.8 MB written) scaled by the rows processed; the profile summary
 # profiles/nvfp4_gemm_pair_8192x4096x4096_r128.md holds the capture and its command.
@@ -433,10 +434,13 @@ def run_single_kernel(args):
         work, unit = 2 * rows * args.n * (cols + args.rank) / 1e12, "TFLOP/s"
     else:
         gamma = torch.ones(cols, device=dev, dtype=torch.bfloat16)
+        x_mean = ops.col_mean(x)
         fn = {"quant_rows": lambda: ops.nvfp4_quantize(x),
               "quant_transposed": lambda: ops.nvfp4_quantize(x, transpose=True),
+              "quant_dual": lambda: ops.nvfp4_quantize_dual(x),
+              "quant_dual_sr": lambda: ops.nvfp4_quantize_dual(x, stochastic=True, seed=1, offset=1, mean=x_mean),
               "rmsnorm_quant": lambda: ops.rmsnorm_nvfp4_quantize(x, gamma, 1e-6)}[args.only]
-        work, unit = rows * cols * BYTES_PER_ELEM_BF16 / 1e9, "GB/s"
+        work, unit = rows * cols * (BYTES_PER_ELEM_DUAL_BF16 if args.only.startswith("quant_dual") else BYTES_PER_ELEM_BF16) / 1e9, "GB/s"
     for _ in range(max(1, args.warmup)):
         fn()
     torch.cuda.synchronize()
@@ -459,7 +463,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
@@ -684,9 +688,10 @@ def main():
         quant_lines = {}
         for name, fn in (("rmsnorm_quant", lambda: ops.rmsnorm_nvfp4_quantize(xq, gamma, 1e-6)),
                          ("quant_rows", lambda: ops.nvfp4_quantize(xq)),
-                         ("quant_transposed", lambda: ops.nvfp4_quantize(xq, transpose=True))):
+                         ("quant_transposed", lambda: ops.nvfp4_quantize(xq, transpose=True)),
+                         ("quant_dual", lambda: ops.nvfp4_quantize_dual(xq))):
             ms = burst_ms(fn, 10)
-            gbs = QUANT_ROWS * QUANT_COLS * BYTES_PER_ELEM_BF16 / ms / 1e6
+            gbs = QUANT_ROWS * QUANT_COLS * (BYTES_PER_ELEM_DUAL_BF16 if name == "quant_dual" else BYTES_PER_ELEM_BF16) / ms / 1e6
             quant_lines[name] = {"gbs": round(gbs, 1), "ms": round(ms, 4), "frac_of_hbm_copy": round(gbs / peaks["hbm_gbs"], 4)}
         del xq
     clock_summary = clocks.summary()

@@ -98,6 +98,11 @@ def _bf16_factors(t32: torch.Tensor, u: torch.Tensor, act: torch.dtype):
     return torch.cat([t_hi, t_lo, t_hi], dim=1), torch.cat([u_hi, u_hi, u_lo], dim=1)
 
 
+def _dual_ok(flat: torch.Tensor) -> bool:
+    """Shapes the one-pass row + transposed quantizer takes."""
+    return flat.shape[0] % 16 == 0 and flat.shape[1] % 16 == 0
+
+
 def _gemm_ok(M, N, K):
     """Shapes the packed GEMM takes (rows of packed codes must be multiples of 16 bytes)."""
     return K % 32 == 0 and M > 0 and N > 0
@@ -303,9 +308,11 @@ class LinearLowbitFunction(torch.autograd.Function):
                 and not F.tp_simulate and tensor.shape[-1] % 16 == 0)
 
     @staticmethod
-    def _pack_centred(tensor, quantizer, centred: bool, mean_cache=None, cache_key="default"):
+    def _pack_centred(tensor, quantizer, centred: bool, mean_cache=None, cache_key="default", both=False):
         """NVFP4 of `tensor` ([..., C] viewed as rows), optionally after subtracting the column
-        mean (rolling at decode).  The native counterpart of svd_quant(metis_mode="mean")."""
+        mean (rolling at decode).  The native counterpart of svd_quant(metis_mode="mean").
+        `both`: the transposed quantization (needed by the backward products) comes out of the same
+        pass over the tensor, where both dimensions are multiples of 16."""
         flat = tensor.reshape(-1, tensor.shape[-1])
         mean = None
         if centred:
@@ -325,8 +332,12 @@ class LinearLowbitFunction(torch.autograd.Function):
         if mean is not None and flat.is_cuda:
             mean_event = torch.cuda.Event()
             mean_event.record()             # work that needs only the mean may overlap the quantization
-        q = quantizer.quantize_packed(flat, mean=mean)
+        if both and _dual_ok(flat):
+            q, qt = quantizer.quantize_packed_dual(flat, mean=mean)
+        else:
+            q, qt = quantizer.quantize_packed(flat, mean=mean), None
         packed = PackedOperand(q, flat, quantizer, tensor.shape)
+        packed._qt = qt
         packed.mean_event = mean_event
         return packed
 
@@ -351,7 +362,9 @@ class LinearLowbitFunction(torch.autograd.Function):
         input_ = input_.to(F.compute_dtype)
         centred = F.enable_activation_svd
         if F._use_packed(input_, F.q_forward_input) and (not centred or F.metis_mode == "mean"):
-            return F._pack_centred(input_, F.q_forward_input, centred, mean_cache, cache_key)
+            # with autograd recording, the weight-gradient product will want x quantized along the tokens
+            return F._pack_centred(input_, F.q_forward_input, centred, mean_cache, cache_key,
+                                   both=torch.is_grad_enabled())
         if centred:
             return F.svd_quant(input_, quant_func=F.q_forward_input, rank=F.activation_lowrank_svd,
                                niter=F.activation_lowrank_niter, broadcast_dim=F.activation_broadcast_dim,
@@ -416,7 +429,7 @@ class LinearLowbitFunction(torch.autograd.Function):
             xa, wq = ctx.xa, ctx.wq
             M, N, K = d0 * d1, d2, xa.q.shape[1]
             if F._packed_backward_ok(grad_output) and _gemm_ok(M, K, N) and _gemm_ok(N, K, M):
-                da = F._pack_centred(grad_output, F.q_backward_outputgrad, F._backward_centred())
+                da = F._pack_centred(grad_output, F.q_backward_outputgrad, F._backward_centred(), both=True)
                 grad_input, grad_weight = _packed_backward(da, xa, wq, M, N, K)
                 grad_input = grad_input.reshape(d0, d1, K)
                 grad_bias = grad_bias.to(torch.float32) if grad_bias is not None else None
@@ -535,8 +548,8 @@ def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, sid
     return _packed_matmul(da.q, w_t, rank1=rank1, lowrank=lowrank, c=addend, out_dtype=out_dtype)
 
 
-def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int):
-    """dW = D^T @ x^ on the FP4 GEMM (bitlinear.py:502-505), fp32: contraction over tokens, so
+def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int, out_dtype=torch.float32):
+    """dW = D^T @ x^ on the FP4 GEMM (bitlinear.py:502-505), fp32 unless told otherwise: contraction over tokens, so
     A = Q(D)^T [N, M] and B = Q(x)^T [K, M], both from the transposed quantizer, plus the two
     rank-1 terms of  dW = Qd^T Qx + (Qd^T 1) mu_x^T + mu_D (Qx^T 1 + M mu_x)^T."""
     d_t = da.transposed()                                   # [N, M], col_vec = mu_D
@@ -550,7 +563,14 @@ def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int):
         if mu_x is not None:
             tail = tail + float(M) * mu_x
         rank1.append((mu_d, tail))
-    return _packed_matmul(d_t, x_t, rank1=rank1, out_dtype=torch.float32)
+    return _packed_matmul(d_t, x_t, rank1=rank1, out_dtype=out_dtype)
+
+
+def _grad_dtype(param: torch.Tensor):
+    """The reference hands autograd an fp32 weight gradient (bitlinear.py:510), which autograd casts to the
+    parameter's dtype.  For a bf16 parameter the product is rounded to bf16 in its own epilogue instead:
+    the same single rounding of the fp32 sum, without a 4-byte round trip through memory."""
+    return torch.bfloat16 if param.dtype == torch.bfloat16 else torch.float32
 
 
 def _packed_backward(da: PackedOperand, xa: PackedOperand, wq: PackedOperand, M: int, N: int, K: int, addend=None):
@@ -590,11 +610,16 @@ class LinearLowbit(torch.nn.Module):
         quantized_weight = self._get_quantized_weight(weight_compute)
         return LinearLowbitFunction.apply(input, weight_compute, bias_compute, quantized_weight, quantized_input)
 
-    @torch.no_grad()
     def _get_quantized_weight(self, weight_compute):
         """Quantized weight with a one-entry cache keyed on the parameter version.  In packed
-        mode the entry is a PackedOperand (codes + scales, later also the transposed
-        quantization), otherwise the dequantized tensor."""
+        mode the entry is a PackedOperand (codes + scales and the transposed quantization: made in
+        the same pass when autograd is recording, on demand otherwise), otherwise the dequantized
+        tensor."""
+        training = torch.is_grad_enabled()
+        with torch.no_grad():
+            return self._quantized_weight(weight_compute, training)
+
+    def _quantized_weight(self, weight_compute, training):
         F = LinearLowbitFunction
         packed = F._use_packed(weight_compute, F.q_forward_weight) and not F.enable_nv_recipe
         cache_key = (self.weight._version, weight_compute.device, weight_compute.dtype, F.q_forward_weight,
@@ -607,8 +632,12 @@ class LinearLowbit(torch.nn.Module):
                 return cached_weight
         if packed:
             source = weight_compute.detach()
-            quantized_weight = PackedOperand(F.q_forward_weight.quantize_packed(source), source,
-                                             F.q_forward_weight, source.shape)
+            if training and _dual_ok(source):        # the input-gradient product contracts over the other dimension
+                q, qt = F.q_forward_weight.quantize_packed_dual(source)
+            else:
+                q, qt = F.q_forward_weight.quantize_packed(source), None
+            quantized_weight = PackedOperand(q, source, F.q_forward_weight, source.shape)
+            quantized_weight._qt = qt
         else:
             quant_input = weight_compute
             if F.enable_nv_recipe:
@@ -639,6 +668,7 @@ class MetisFusedFunction(torch.autograd.Function):
     backward of LinearLowbitFunction."""
 
     fuse_dx_side_product = True      # bf16 only; False keeps the two dX products as separate launches
+    native_lowrank_backward = True   # bf16 only; False leaves the unquantized U branch's backward to torch.matmul
     concurrent_branches = True       # backward of the low-rank branch on a second CUDA stream
 
     @staticmethod
@@ -683,6 +713,7 @@ class MetisFusedFunction(torch.autograd.Function):
         ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
         ctx.has_bias = bias is not None
         ctx.dims = (M, N, K)
+        ctx.v_weight, ctx.r_weight = v_weight, r_weight        # for their dtypes only
         ctx.save_for_backward(yv, s, u_weight)
         return y.reshape(*xa.shape[:-1], N).to(xa.dtype)
 
@@ -691,6 +722,7 @@ class MetisFusedFunction(torch.autograd.Function):
         F = LinearLowbitFunction
         yv, s, u_weight = ctx.saved_tensors
         xa, vq, rq = ctx.xa, ctx.vq, ctx.rq
+        v_weight, r_weight = ctx.v_weight, ctx.r_weight
         M, N, K = ctx.dims
         r = yv.shape[1]
         act = yv.dtype
@@ -704,24 +736,34 @@ class MetisFusedFunction(torch.autograd.Function):
 
         def low_rank_branch():
             # ulinear: plain linear on ts = s . yv; vlinear: quantized backward with grad_output = d_yv
-            ts = yv * s.to(act)
-            u = u_weight.to(act)
-            grad_u = (g.T @ ts).to(u_weight.dtype)
-            d_ts = g @ u                                                            # [M, r]
-            grad_s = (d_ts * yv).sum(dim=0).to(s.dtype)
-            d_yv = d_ts * s.to(act)
-            dv = F._pack_centred(d_yv, quantizer, centred)
+            if act == torch.bfloat16 and g.is_cuda and r % 8 == 0 and N % 8 == 0 and MetisFusedFunction.native_lowrank_backward:
+                # autograd's bf16 ops on the tensor core, one pass over g per product and no transposed copy:
+                # dU = g^T ts, then d_ts = g U with d_yv = d_ts . s and ds = sum d_ts . yv in its finishing pass
+                one = _one(yv)
+                ts = ops.lowrank_scale(yv, s, one, one)
+                out_dtype = u_weight.dtype if u_weight.dtype in (torch.bfloat16, torch.float32) else torch.float32
+                grad_u = ops.lowrank_du(g, ts, out_dtype=out_dtype).to(u_weight.dtype)
+                d_yv, ds32 = ops.lowrank_dts(g, u_weight.detach().to(torch.bfloat16), yv, s)
+                grad_s = ds32.to(s.dtype)
+            else:
+                ts = yv * s.to(act)
+                u = u_weight.to(act)
+                grad_u = (g.T @ ts).to(u_weight.dtype)
+                d_ts = g @ u                                                            # [M, r]
+                grad_s = (d_ts * yv).sum(dim=0).to(s.dtype)
+                d_yv = d_ts * s.to(act)
+            dv = F._pack_centred(d_yv, quantizer, centred, both=True)
             side = None
             if fuse_dx:
                 # operands of the bf16 side product of the fused dX launch that depend on this branch only
                 v_t = vq.transposed()
                 u_side = ops.nvfp4_dequantize(v_t, torch.bfloat16, add_mean=False, unit=_one(v_t.unit))
                 side = (u_side, ops.nvfp4_gemv(v_t, dv.mean) if dv.mean is not None else None)
-            return grad_u, grad_s, dv, _packed_dw(dv, xa, M), side
+            return grad_u, grad_s, dv, _packed_dw(dv, xa, M, _grad_dtype(v_weight)), side
 
         def residual_weight_gradient(dg):
             # warmup_linear (the residual): quantized backward with grad_output = g
-            grad_r = _packed_dw(dg, xa, M)
+            grad_r = _packed_dw(dg, xa, M, _grad_dtype(r_weight))
             if reducer is not None:
                 reducer.ready(grad_r)       # the big all-reduce starts here and runs beside the dX product
             return grad_r
@@ -736,7 +778,7 @@ class MetisFusedFunction(torch.autograd.Function):
                 _row_sums(x_t)              # cached on x_t and read by both branches
             main, aux = torch.cuda.current_stream(), _aux_stream(g.device)
             aux.wait_stream(main)
-            dg = F._pack_centred(g, quantizer, centred)
+            dg = F._pack_centred(g, quantizer, centred, both=True)
             with torch.cuda.stream(aux), random_lane(1):
                 grad_u, grad_s, dv, grad_v, side = low_rank_branch()
                 if dg.mean is not None:
@@ -749,7 +791,7 @@ class MetisFusedFunction(torch.autograd.Function):
                 t.record_stream(main)       # allocated on the second stream, consumed by autograd on this one
         else:
             grad_u, grad_s, dv, grad_v, side = low_rank_branch()
-            dg = F._pack_centred(g, quantizer, centred)
+            dg = F._pack_centred(g, quantizer, centred, both=True)
             grad_r = residual_weight_gradient(dg)
         if reducer is not None:
             # the small gradients are final too: their bucket goes out before the input-gradient GEMM

@@ -314,6 +314,16 @@ class _NativeNVFP4(BlockQuantFunc):
 
     @classmethod
     @torch.no_grad()
+    def quantize_packed_dual(cls, x: torch.Tensor, *, mean: torch.Tensor | None = None, sf_layout: int = cabi.SF_MMA):
+        """(quantize_packed(x), quantize_packed(x, transpose=True)) from one pass over x: what a training
+        step needs of every operand (the products of the backward contract over the other dimension)."""
+        cls._check(x)
+        return ops.nvfp4_quantize_dual(cls._native_input(x), stochastic=cls.stochastic,
+                                       seed=cls._seed + _NativeNVFP4._lane, sf_layout=sf_layout, mean=mean,
+                                       offset_counter=cls._offset_counter(x.device) if cls.stochastic else None)
+
+    @classmethod
+    @torch.no_grad()
     def quantize_dequantize(cls, x: torch.Tensor):
         cls._check(x)
         q = cls.quantize_packed(x, sf_layout=cabi.SF_ROWMAJOR)

@@ -16,7 +16,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT_DIR = PKG / "_lib"
 LIB = OUT_DIR / "libmetis_nvfp4.so"
-SOURCES = ["api.cu", "quantize.cu", "rmsnorm_quant.cu", "dequantize.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu"]
+SOURCES = ["api.cu", "quantize.cu", "rmsnorm_quant.cu", "dequantize.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "lowrank_bwd.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

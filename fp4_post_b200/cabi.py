@@ -28,6 +28,9 @@ EXPORTS = (
     "metis_nvfp4_dequantize", "metis_col_mean_workspace_bytes", "metis_col_mean", "metis_nvfp4_gemv",
     "metis_nvfp4_gemm", "metis_nvfp4_quantize_static", "metis_nvfp4_gemm_workspace_bytes",
     "metis_lowrank_scale", "metis_set_gemm_sm_limit",
+    "metis_nvfp4_quantize_dual_workspace_bytes", "metis_nvfp4_quantize_dual",
+    "metis_bf16_panel_gemm_workspace_bytes", "metis_bf16_panel_gemm",
+    "metis_lowrank_dts_workspace_bytes", "metis_lowrank_dts", "metis_lowrank_du_workspace_bytes", "metis_lowrank_du",
 )
 
 
@@ -78,6 +81,10 @@ def lib() -> C.CDLL:
     L.metis_nvfp4_quantize_workspace_bytes.restype = i64
     L.metis_nvfp4_quantize.argtypes = [vp, i32, i64, i64, i64, vp, u32, u64, u64, i32, vp, vp, vp, vp, i64, vp]
     L.metis_nvfp4_quantize.restype = i32
+    L.metis_nvfp4_quantize_dual_workspace_bytes.argtypes = [i64, i64]
+    L.metis_nvfp4_quantize_dual_workspace_bytes.restype = i64
+    L.metis_nvfp4_quantize_dual.argtypes = [vp, i32, i64, i64, i64, vp, u32, u64, u64, i32, vp, vp, vp, vp, vp, vp, vp, i64, vp]
+    L.metis_nvfp4_quantize_dual.restype = i32
     L.metis_nvfp4_quantize_static.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, vp, vp]
     L.metis_nvfp4_quantize_static.restype = i32
     L.metis_rmsnorm_nvfp4_quantize.argtypes = [vp, i32, i64, i64, i64, vp, i32, f32, i32, vp, vp, vp, vp, vp, i64, vp]
@@ -96,6 +103,15 @@ def lib() -> C.CDLL:
     L.metis_set_gemm_sm_limit.restype = i32
     L.metis_lowrank_scale.argtypes = [vp, i64, i64, i64, vp, i32, vp, vp, vp, vp]
     L.metis_lowrank_scale.restype = i32
+    for name in ("metis_bf16_panel_gemm_workspace_bytes", "metis_lowrank_dts_workspace_bytes", "metis_lowrank_du_workspace_bytes"):
+        getattr(L, name).argtypes = [i64, i64, i64]
+        getattr(L, name).restype = i64
+    L.metis_bf16_panel_gemm.argtypes = [vp, i32, i64, vp, i32, i64, i64, i64, i64, vp, i64, vp, i64, vp, vp]
+    L.metis_bf16_panel_gemm.restype = i32
+    L.metis_lowrank_dts.argtypes = [vp, i64, i64, i64, vp, i64, i64, vp, i64, vp, i32, vp, i64, vp, vp, i64, vp, vp]
+    L.metis_lowrank_dts.restype = i32
+    L.metis_lowrank_du.argtypes = [vp, i64, i64, i64, vp, i64, i64, vp, i32, i64, vp, i64, vp, vp]
+    L.metis_lowrank_du.restype = i32
     L.metis_nvfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     L.metis_nvfp4_gemm_workspace_bytes.restype = i64
     _lib = L

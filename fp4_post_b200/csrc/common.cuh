@@ -170,7 +170,7 @@ __device__ __forceinline__ float folded_index(float q) {
   return min3(q, __fmaf_rn(q, 0.5f, 2.0f), __fmaf_rn(q, 0.25f, 4.0f));
 }
 
-// Correctly rounded a / h for 0 <= a <= 12.1 h from a refined reciprocal r of h: one
+// Correctly rounded a / h for |a| <= 12.1 h from a refined reciprocal r of h: one
 // multiplication, the exact remainder and one correction (Markstein).  A remainder that
 // underflows only occurs for quotients far below the first rounding boundary.
 __device__ __forceinline__ float refine_reciprocal(float h) {
@@ -182,35 +182,55 @@ __device__ __forceinline__ float divide_exact(float a, float h, float r) {
   return __fmaf_rn(__fmaf_rn(-h, q0, a), r, q0);
 }
 
+// 8 values -> 8 e2m1 nibbles, element 0 in the low nibble: round to nearest, ties to the even code,
+// saturating, sign bit included (-0.0 and negative values that round to zero keep theirs).
+__device__ __forceinline__ uint32_t pack_e2m1x8(const float (&v)[8]) {
+  uint32_t out;
+  asm("{ .reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3}; }"
+      : "=r"(out)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return out;
+}
+
+// The reference rounds twice (quant.py:27-30): the folded index q/2 + 2 (or q/4 + 4) is rounded to
+// fp32 before it is rounded to an integer, which drops the last bit of v = x/s for |v| >= 2.  The
+// conversion to e2m1 rounds v itself, once.  Over all fp32 v in [0, 6.5] the two differ at exactly three
+// values, the fp32 neighbours nextafter(2.5), prev(3.5) and nextafter(5) of a tie, which the reference
+// sends to the tie's even code.  Dropping that bit the same way first, (v + t) - t with t = 2 on [2, 4)
+// and 4 on [4, 8) (round to nearest even in the binade of the sum, as the reference's addition does),
+// makes them agree everywhere.  t comes from the exponent bits of v: 0x40000000 is 2.0, 0x40800000 is
+// 4.0; below 2, bit 30 is clear and what is left (0 or 2^-126) changes nothing; the sign is kept.
+__device__ __forceinline__ float round_like_folded(float v) {
+  const float t = __uint_as_float(__float_as_uint(v) & 0xC0800000u);
+  return __fsub_rn(__fadd_rn(v, t), t);
+}
+
 // Round-to-nearest codes of kGroups*8 consecutive values sharing the block scale `s`
 // (kGroups = 1: half a block, 2: a whole block); out[g] holds elements 8g..8g+7, element 0 in
 // the low nibble.  Every element goes through the reference's own arithmetic: the correctly
-// rounded quotient |x|/(s/2), the folded index, round half to even (adding the rounding magic
-// leaves the integer in the low mantissa bits).  There is no approximate fast path because with
-// bf16 inputs exact ties (an element equal to amax/8, 5/24 amax, ...) are common.  The integer
-// codes are summed into nibbles with shifted adds (the magic's own bits are subtracted once at the
-// end); the sign bits, 0/1 floats from a saturating multiply, are summed with multiply-adds.
+// rounded quotient x/s (half the reference's |x|/(s/2), exactly), its second rounding, and round
+// half to even onto the e2m1 grid by the hardware conversion, which packs two codes with their
+// sign bits per instruction.  (The conversion runs on the special-function unit at about 26 cycles
+// per warp; sending half of every block down an FMA/ALU-only path of the folded index, magic-number
+// rounding and shifted adds instead was measured slower: 4 more instructions per element cost more
+// than the relieved unit gives back.)  There is no approximate fast path because with bf16
+// inputs exact ties (an element equal to amax/8, 5/24 amax, ...) are common.  The division is
+// signed: -0.0 comes out as +0.0 (the remainder +0 wins the final sum), any negative x keeps its
+// sign down to -0.0, which is the reference's sign bit (x < 0).
 template <int kGroups>
 __device__ __forceinline__ void quantize_rn(const float (&x)[8 * kGroups], float s, uint32_t (&out)[kGroups]) {
-  const float h = 0.5f * s;
-  const float r = refine_reciprocal(h);
-  const uint32_t magic_sum = 0x4B400000u * 0x11111111u;   // sum over i of magic bits << 4i, mod 2^32
+  const float r = refine_reciprocal(s);
 #pragma unroll
   for (int g = 0; g < kGroups; ++g) {
-    uint32_t acc = 0;
-    float sign_lo = 0.0f, sign_hi = 0.0f;      // 16 bits each, exact in fp32
+    float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float v = x[8 * g + i];
-      const float m = folded_index(divide_exact(fabsf(v), h, r));
-      acc += __float_as_uint(__fadd_rn(m, METIS_ROUND_MAGIC)) << (4 * i);
-      const float neg = is_negative(v);
-      if (i < 4) sign_lo = __fmaf_rn(neg, (float)(8u << (4 * i)), sign_lo);
-      else       sign_hi = __fmaf_rn(neg, (float)(8u << (4 * (i - 4))), sign_hi);
-    }
-    const uint32_t slo = __float_as_uint(sign_lo + 8388608.0f) & 0xFFFFu;   // 2^23: integer in the low bits
-    const uint32_t shi = __float_as_uint(sign_hi + 8388608.0f) << 16;
-    out[g] = (acc - magic_sum) | slo | shi;
+    for (int i = 0; i < 8; ++i) v[i] = round_like_folded(divide_exact(x[8 * g + i], s, r));
+    out[g] = pack_e2m1x8(v);
   }
 }
 
@@ -240,32 +260,37 @@ struct Philox {
   }
 };
 
-// Stochastic-rounding codes of 8 values sharing scale s: floor(folded index + U) with U uniform on
-// [0, 1) in steps of 2^-16, which rounds up with probability frac(index) (quant.py:139-147: the
-// reference adds rand - 0.5 and rounds to nearest).  Fixed point: index * 2^16 lands in the low
-// mantissa bits of a 2^23 magic add, the 16 random bits are added as an integer, bits [16, 19) are
-// the code (the index is at most 7, so the sum stays below 8 * 2^16 and the magic's own bits 0x4B00
-// do not reach the nibble).  No exact division here: the quotient only enters in distribution.
-__device__ __forceinline__ uint32_t quantize8_sr(const float* x, float s, uint4 rnd) {
+// Stochastic-rounding codes of one block (16 values sharing scale s): floor(folded index + U) with
+// U uniform on [0, 1) in steps of 2^-16, which rounds up with probability frac(index) (quant.py:139-147:
+// the reference adds rand - 0.5 and rounds to nearest).  No exact division here: the quotient only
+// enters in distribution.  One Philox call (128 bits) serves the 16 elements: element 4w + j takes bytes
+// j and j+1 (mod 4) of word w.  Each 16-bit window is exactly uniform; neighbours share one byte, the
+// low byte of one being the high byte of the next, which moves the other's rounding probability by
+// less than 2^-8.  Per element: one byte permute builds the float 2^23 + window (window in the low
+// mantissa bits under the exponent of 2^23); index + window * 2^-16 + 128 is one multiply-add (the
+// window's 16 bits survive exactly in [128, 256)); + 8 for x < 0; an addition of 2^23 rounding down
+// leaves floor(index + U) + 8 [x < 0] + 128 in the low mantissa bits, and the integers are summed
+// into nibbles with shifted adds (the constant bits are subtracted once at the end).
+__device__ __forceinline__ void quantize16_sr(const float (&x)[16], float s, uint4 rnd, uint32_t (&out)[2]) {
   const float two_over_s = 2.0f * rcp_approx(s);
   const uint32_t rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
-  uint32_t acc = 0;
-  float sign_lo = 0.0f, sign_hi = 0.0f;
+  const uint32_t magic_sum = 0x4B000080u * 0x11111111u;                  // (2^23 + 128) << 4i summed, mod 2^32
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float m = folded_index(fabsf(x[i]) * two_over_s);
-    const uint32_t bits = (i & 1) ? (rw[i >> 1] >> 16) : (rw[i >> 1] & 0xFFFFu);
-    const uint32_t v = __float_as_uint(__fmaf_rn(m, 65536.0f, 8388608.0f)) + bits;
-    // code = (v >> 16) & 7, moved to nibble i
-    const uint32_t placed = (4 * i <= 16) ? (v >> (16 - 4 * i)) : (v << (4 * i - 16));
-    acc |= placed & (0x7u << (4 * i));
-    const float neg = is_negative(x[i]);
-    if (i < 4) sign_lo = __fmaf_rn(neg, (float)(8u << (4 * i)), sign_lo);
-    else       sign_hi = __fmaf_rn(neg, (float)(8u << (4 * (i - 4))), sign_hi);
+  for (int g = 0; g < 2; ++g) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int e = 8 * g + i;
+      const float m = folded_index(fabsf(x[e]) * two_over_s);
+      constexpr uint32_t kWindow[4] = {0x7610u, 0x7621u, 0x7632u, 0x7603u};     // bytes (j, j+1 mod 4) below 0x4B00
+      const float rf = __uint_as_float(__byte_perm(rw[e >> 2], 0x4B000000u, kWindow[e & 3]));
+      const float s1 = __fmaf_rn(rf, 0x1p-16f, m);                       // index + 128 + U
+      const float s2 = __fmaf_rn(is_negative(x[e]), 8.0f, s1);
+      const float t = __fadd_rd(s2, 8388608.0f);                         // floor
+      acc += __float_as_uint(t) << (4 * i);
+    }
+    out[g] = acc - magic_sum;
   }
-  const uint32_t slo = __float_as_uint(sign_lo + 8388608.0f) & 0xFFFFu;
-  const uint32_t shi = __float_as_uint(sign_hi + 8388608.0f) << 16;
-  return acc | slo | shi;
 }
 
 // ---- loads ------------------------------------------------------------------------------------------------

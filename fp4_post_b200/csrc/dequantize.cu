@@ -208,9 +208,12 @@ lowrank_scale_kernel(const __nv_bfloat16* __restrict__ yv, int64_t M, int64_t r,
   grid_dependency_wait();
   const int64_t groups_per_row = r >> 3;
   const float div = __fmul_rn(__ldg(unit_a), __ldg(unit_b));
+  const bool small = M * groups_per_row < ((int64_t)1 << 31);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * groups_per_row;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t m = i / groups_per_row, j0 = (i - m * groups_per_row) * 8;
+    // 32-bit index arithmetic where it fits (a 64-bit division is a subroutine of ~100 instructions)
+    const int64_t m = small ? (int64_t)((uint32_t)i / (uint32_t)groups_per_row) : i / groups_per_row;
+    const int64_t j0 = (i - m * groups_per_row) * 8;
     const uint4 w = __ldg(reinterpret_cast<const uint4*>(yv + m * ld + j0));
     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
     uint32_t out[4];

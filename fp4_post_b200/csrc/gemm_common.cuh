@@ -21,9 +21,16 @@ constexpr int kSfBufCols = 48;
 // debug knob carried in metis_gemm_args.reserved: the producer arms the first stage's barrier
 // for the scale bytes of A but never issues that copy, so the consumer's bounded wait expires.
 constexpr int kDebugDropFirstSfa = 1;
-// timing experiments (results are meaningless): issue no MMAs / request no data
+// timing experiments (results are meaningless): issue no MMAs / request no data.  They exist only in a
+// build with -DMETIS_TIMING_KNOBS; the shipped library rejects the bits (they are outside kDebugMask)
+// and the code they guard is compiled out.
+#ifdef METIS_TIMING_KNOBS
 constexpr int kDebugNoMma = 2;
 constexpr int kDebugNoLoad = 4;
+#else
+constexpr int kDebugNoMma = 0;
+constexpr int kDebugNoLoad = 0;
+#endif
 // run the single-CTA kernel where the CTA-pair kernel would be chosen (tests cover both)
 constexpr int kDebugSingleCta = 8;
 constexpr int kDebugMask = kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad | kDebugSingleCta;

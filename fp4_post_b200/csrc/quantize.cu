@@ -1,4 +1,4 @@
-// NVFP4 block quantizer kernels (row-major and transposed, round-to-nearest and stochastic),
+// NVFP4 block quantizer kernels (row-major, transposed and both at once, round-to-nearest and stochastic),
 // the scale finalisation pass, column means, and the C entry points that launch them.
 //
 // The work is split in two launches because of one global dependency: the E4M3 block
@@ -55,8 +55,7 @@ quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int6
       const int64_t b = (int64_t)r * blocks_per_row + bc;
       uint32_t packed[2];
       if (kSR) {
-        packed[0] = quantize8_sr(v, s, rng((uint64_t)b * 2, offset));
-        packed[1] = quantize8_sr(v + 8, s, rng((uint64_t)b * 2 + 1, offset));
+        quantize16_sr(v, s, rng((uint64_t)b, offset), packed);      // one counter per block
       } else {
         quantize_rn<2>(v, s, packed);
       }
@@ -81,184 +80,348 @@ quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int6
   fold_global_max(gmax, running);
 }
 
-// ---- pass 1, transposed ---------------------------------------------------------------------------
-// Output Q = quantize(x^T): blocks of 16 run along the rows of x.  A CTA walks tiles of 256 rows x
-// 128 bytes of x (64 bf16 or 32 fp32 columns).  One thread issues the TMA load of the next tile
-// into the other shared-memory stage while all threads work on the current one: a thread reads a
-// column block (16 rows of one column) from shared memory -- consecutive lanes read consecutive
-// columns, so the reads are conflict free -- quantizes it exactly like a row block, and parks 8 code
-// bytes and one maximum in a staging area from which whole 128-byte runs of the output rows are
-// written.  A tile load that does not arrive within the wait limit raises the error word of the
+// ---- pass 1 on shared-memory tiles: the transposed quantization, alone or together with the row-major one ----
+// Output Qt = quantize(x^T): blocks of 16 run along the rows of x.  A persistent CTA walks tiles of
+// 128 rows x 128 bytes of x (64 bf16 or 32 fp32 columns) that one thread fetches with TMA (128-byte
+// swizzle) into a ring of three stages, two tiles ahead of the arithmetic.
+//   column phase  lane w of warp rb reads word w of the 16 rows of row block rb: one (fp32) or two (bf16)
+//                 columns of x, i.e. whole blocks of Qt, quantized in registers like a row block.  The 8
+//                 code bytes per block are parked in shared memory so that global stores are 64-byte
+//                 runs along the token dimension.
+//   row phase     (kRowsOut: the "dual" mode) the same tile is read once more along its rows, 16 columns
+//                 per thread, and the row-major quantization goes straight to global memory.  The tensor
+//                 is read from HBM once for both orientations.
+// Both phases read shared memory without bank conflicts thanks to the swizzle (16-byte chunk c of row
+// r sits at chunk c ^ (r & 7)).  One __syncthreads per tile: staging and the column means are double
+// buffered.  A tile load that does not arrive within the wait limit raises the error word of the
 // workspace header (the scale pass then publishes NaN as the unit) instead of hanging.
-template <typename T> struct TransposeTile {
-  static constexpr int kCols = 128 / sizeof(T);           // 64 (bf16) or 32 (fp32): 128 bytes per row
-  static constexpr int kRows = 256;
-  static constexpr int kRowBlocks = kRows / 16;           // 16
-  static constexpr int kUnits = kCols * kRowBlocks / kQuantThreads;   // column blocks per thread: 4 or 2
-  static constexpr int kStageBytes = kRows * 128;         // 32 KiB
-  static constexpr int kCodePitch = kRows / 2 + 8;        // staged code bytes per output row (+8: bank spread)
-  static constexpr int kSmemBytes = 2 * kStageBytes + kCols * kCodePitch + kCols * kRowBlocks * 4 + 64 + 128;
+template <typename T> struct TileCfg {
+  static constexpr int kRows = 128;
+  static constexpr int kCols = 128 / sizeof(T);            // 64 (bf16) or 32 (fp32): 128 bytes per row
+  static constexpr int kStages = 3;
+  static constexpr int kStageBytes = kRows * 128;          // 16 KiB
+  static constexpr int kRowBlocks = kRows / 16;            // 8 = warps per CTA
+  static constexpr int kColsPerWord = 4 / sizeof(T);       // columns in one 32-bit word of a row: 2 or 1
+  static constexpr int kBlocksPerRow = kCols / 16;         // row-phase blocks per tile row: 4 or 2
+  static constexpr int kRowUnits = kRows * kBlocksPerRow / kQuantThreads;   // row-phase blocks per thread: 2 or 1
+  // staged codes of Qt: per 32-bit word of a row and per column of that word, 64 bytes (128 tokens) at a
+  // pitch of 72; the second column's array starts 16 banks off the first
+  static constexpr int kCodePitch = 72;
+  static constexpr int kCodeArray = 32 * kCodePitch + 64;
+  static constexpr int kStagingBytes = kColsPerWord * kCodeArray + kRowBlocks * kCols * 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2 * kStagingBytes + 2 * kCols * 4 + 64 + 1024;
+};
+constexpr int64_t kTileRowsMinElements = 1 << 20;          // row-major tensors from this size on go through the tile kernel
+constexpr uint64_t kColumnStream = 1ull << 63;             // Philox counter space of the transposed output in dual mode
+
+struct TileOutputs {
+  uint8_t* codes_t;  float* amax_t;  unsigned int* gmax_t;        // Qt [cols, rows]
+  uint8_t* codes_r;  float* amax_r;  unsigned int* gmax_r;        // Q  [rows, cols] (dual mode)
+  unsigned int* error;
 };
 
-template <typename T, bool kMean, bool kSR>
-__global__ void __launch_bounds__(kQuantThreads)
-quantize_cols_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, int64_t cols,
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+template <typename T, bool kMean, bool kSR, bool kRowsOut, bool kColsOut>
+__global__ void __launch_bounds__(kQuantThreads, 3)
+quantize_tile_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, int64_t cols,
                      const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
-                     const uint64_t* __restrict__ offset_ctr, uint8_t* __restrict__ codes, float* __restrict__ amax_out,
-                     unsigned int* __restrict__ gmax) {
-  using TT = TransposeTile<T>;
+                     const uint64_t* __restrict__ offset_ctr, const TileOutputs out) {
+  using TC = TileCfg<T>;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
-  uint8_t* s_codes = smem + 2 * TT::kStageBytes;                               // [kCols][kCodePitch]
-  float* s_amax = reinterpret_cast<float*>(s_codes + TT::kCols * TT::kCodePitch);   // [kCols][kRowBlocks]
-  uint64_t* full = reinterpret_cast<uint64_t*>(s_amax + TT::kCols * TT::kRowBlocks);   // [2]
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* s_staging = smem + TC::kStages * TC::kStageBytes;                    // [2][kStagingBytes]
+  float* s_mean = reinterpret_cast<float*>(s_staging + 2 * TC::kStagingBytes);  // [2][kCols]
+  uint64_t* full = reinterpret_cast<uint64_t*>(s_mean + 2 * TC::kCols);         // [kStages]
   __shared__ int s_failed;
 
   grid_dependency_wait();
   if (kSR && offset_ctr) offset += *offset_ctr;
   const int tid = threadIdx.x;
-  const int64_t row_tiles = (rows + TT::kRows - 1) / TT::kRows;
-  const int64_t col_tiles = (cols + TT::kCols - 1) / TT::kCols;
-  const int64_t tiles = row_tiles * col_tiles;      // tile id = column tile * row_tiles + row tile
+  const int lane = tid & 31, warp = tid >> 5;
+  const int64_t row_tiles = (rows + TC::kRows - 1) / TC::kRows;
+  const int64_t col_tiles = (cols + TC::kCols - 1) / TC::kCols;
+  const int64_t tiles = row_tiles * col_tiles;       // tile id = row tile * col_tiles + column tile
+  const int64_t bpr = cols >> 4;                     // blocks per row of Q
+  const int64_t bpc = rows >> 4;                     // blocks per row of Qt
 
   if (tid == 0) {
-    mbar_init(&full[0], 1);
-    mbar_init(&full[1], 1);
+    for (int s = 0; s < TC::kStages; ++s) mbar_init(&full[s], 1);
     s_failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  auto fill_mean = [&](int64_t tile, int buf) {
+    if (kMean && tid < TC::kCols) {
+      const int64_t c = (tile % col_tiles) * TC::kCols + tid;
+      s_mean[buf * TC::kCols + tid] = c < cols ? __ldg(col_mean + c) : 0.0f;
+    }
+  };
+  if ((int64_t)blockIdx.x < tiles) fill_mean(blockIdx.x, 0);
   __syncthreads();
 
   auto issue = [&](int64_t tile, int stage) {
-    const int64_t ct = tile / row_tiles, rt = tile - ct * row_tiles;
-    mbar_expect_tx(&full[stage], TT::kStageBytes);
-    tma_load_2d(smem + stage * TT::kStageBytes, &map_x, (int32_t)(ct * TT::kCols), (int32_t)(rt * TT::kRows), &full[stage]);
+    const int64_t rt = tile / col_tiles, ct = tile - rt * col_tiles;
+    mbar_expect_tx(&full[stage], TC::kStageBytes);
+    tma_load_2d(smem + stage * TC::kStageBytes, &map_x, (int32_t)(ct * TC::kCols), (int32_t)(rt * TC::kRows), &full[stage]);
   };
-
-  const int c = tid % TT::kCols;                    // column of this thread inside the tile
-  const int rb0 = tid / TT::kCols;                  // its first row block; the others follow every kQuantThreads/kCols
-  const Philox rng(seed);
-  float running = 0.0f;
-  int stage = 0;
-  uint32_t phases = 0;                              // bit s: parity to wait for on full[s]
-  int64_t tile = blockIdx.x;
-  if (tid == 0 && tile < tiles) issue(tile, 0);
-
-  for (; tile < tiles; tile += gridDim.x) {
-    const int64_t next = tile + gridDim.x;
-    if (tid == 0 && next < tiles) issue(next, stage ^ 1);     // that stage was released by the barrier below
-    volatile int* failed = &s_failed;
-    if (!mbar_wait(&full[stage], (phases >> stage) & 1u, failed)) {
-      *failed = 1;
+  if (tid == 0) {
+    for (int s = 0; s < TC::kStages; ++s) {
+      const int64_t t = (int64_t)blockIdx.x + (int64_t)s * gridDim.x;
+      if (t < tiles) issue(t, s);
     }
-    phases ^= 1u << stage;
-    if (*failed) break;                                       // uniform: every thread sees the same barrier outcome or flag
+  }
 
-    const int64_t ct = tile / row_tiles, rt = tile - ct * row_tiles;
-    const int64_t out_row = ct * TT::kCols + c;               // row of Q = column of x
-    const int64_t row0 = rt * TT::kRows;
-    const bool col_live = out_row < cols;
-    const float m = (kMean && col_live) ? __ldg(col_mean + out_row) : 0.0f;
-    const T* tile_smem = reinterpret_cast<const T*>(smem + stage * TT::kStageBytes);
+  const Philox rng(seed);
+  float running_t = 0.0f, running_r = 0.0f;
+  const uint32_t smem_base = smem_u32(smem);
+  // column phase: this lane's word of a row, as chunk and offset inside the chunk
+  const uint32_t word_chunk = (uint32_t)lane >> 2, word_in_chunk = ((uint32_t)lane & 3u) * 4u;
+  volatile int* failed = &s_failed;
+  int stage = 0;
+  uint32_t it = 0;
+  for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+    const int buf = it & 1;
+    if (!mbar_wait(&full[stage], (it / TC::kStages) & 1u, failed)) *failed = 1;
+    if (*failed) break;                               // every thread sees the same outcome of the barrier, or the flag
+
+    const int64_t rt = tile / col_tiles, ct = tile - rt * col_tiles;
+    const int64_t row0 = rt * TC::kRows, col0 = ct * TC::kCols;
+    const uint32_t tile_smem = smem_base + stage * TC::kStageBytes;
+    uint8_t* staging = s_staging + buf * TC::kStagingBytes;
+    float* s_amax = reinterpret_cast<float*>(staging + TC::kColsPerWord * TC::kCodeArray);   // [kRowBlocks][kCols]
+    const float* mean = s_mean + buf * TC::kCols;
+
+    // ---- column phase: warp = row block, lane = 32-bit word of the row ----
+    if (kColsOut) {
+      const int rb = warp;
+      float v[TC::kColsPerWord][16];
+      float m[TC::kColsPerWord];
 #pragma unroll
-    for (int u = 0; u < TT::kUnits; ++u) {
-      const int rb = rb0 + u * (kQuantThreads / TT::kCols);
-      float v[16];
+      for (int c = 0; c < TC::kColsPerWord; ++c) m[c] = kMean ? mean[lane * TC::kColsPerWord + c] : 0.0f;
+      const uint32_t row_base = tile_smem + (uint32_t)(rb * 16) * 128u + word_in_chunk;
 #pragma unroll
       for (int r = 0; r < 16; ++r) {
-        float e = (float)tile_smem[(rb * 16 + r) * TT::kCols + c];
-        if (kMean) e = __fsub_rn(e, m);
-        v[r] = e;
+        const uint32_t w = lds32(row_base + r * 128 + ((word_chunk ^ (uint32_t)(r & 7)) << 4));
+        if constexpr (sizeof(T) == 2) { v[0][r] = bf16_lo(w); v[1][r] = bf16_hi(w); }
+        else                          { v[0][r] = __uint_as_float(w); }
+        if (kMean) {
+#pragma unroll
+          for (int c = 0; c < TC::kColsPerWord; ++c) v[c][r] = __fsub_rn(v[c][r], m[c]);
+        }
       }
-      const float a = abs_max16(v);
-      const float s = block_scale_from_amax(a);
-      uint32_t packed[2];
-      if (kSR) {
-        // one counter per 8 output elements: output row out_row, output column row0 + 16 rb (+8)
-        const uint64_t e0 = ((uint64_t)out_row * (uint64_t)rows + (uint64_t)(row0 + rb * 16)) >> 3;
-        packed[0] = quantize8_sr(v, s, rng(e0, offset));
-        packed[1] = quantize8_sr(v + 8, s, rng(e0 + 1, offset));
-      } else {
-        quantize_rn<2>(v, s, packed);
+      const bool rows_live = row0 + rb * 16 < rows;
+      float amax[TC::kColsPerWord];
+#pragma unroll
+      for (int c = 0; c < TC::kColsPerWord; ++c) {
+        const int64_t out_row = col0 + lane * TC::kColsPerWord + c;           // row of Qt = column of x
+        const float a = abs_max16(v[c]);
+        const float s = block_scale_from_amax(a);
+        uint32_t packed[2];
+        if (kSR) {
+          const uint64_t b = (uint64_t)out_row * (uint64_t)bpc + (uint64_t)((row0 >> 4) + rb);
+          quantize16_sr(v[c], s, rng(b, kRowsOut ? (offset ^ kColumnStream) : offset), packed);   // alone: the transposed call's own stream
+        } else {
+          quantize_rn<2>(v[c], s, packed);
+        }
+        *reinterpret_cast<uint2*>(staging + c * TC::kCodeArray + lane * TC::kCodePitch + rb * 8) = make_uint2(packed[0], packed[1]);
+        amax[c] = a;
+        if (rows_live && out_row < cols) running_t = fmaxf(running_t, a);
       }
-      *reinterpret_cast<uint2*>(s_codes + c * TT::kCodePitch + rb * 8) = make_uint2(packed[0], packed[1]);
-      s_amax[c * TT::kRowBlocks + rb] = a;
-      if (col_live && row0 + rb * 16 < rows) running = fmaxf(running, a);
+      if constexpr (sizeof(T) == 2) *reinterpret_cast<float2*>(s_amax + rb * TC::kCols + 2 * lane) = make_float2(amax[0], amax[1]);
+      else                          s_amax[rb * TC::kCols + lane] = amax[0];
     }
-    __syncthreads();
-    // write-out: output row (tile column) j owns kRows/2 = 128 contiguous code bytes and 16 maxima
-    const int64_t valid_rows = min((int64_t)TT::kRows, rows - row0);            // multiple of 16
-    for (int i = tid; i < TT::kCols * 16; i += kQuantThreads) {                 // 8-byte pieces: 16 per output row
-      const int j = i >> 4, piece = i & 15;
-      const int64_t orow = ct * TT::kCols + j;
+
+    // ---- row phase: a thread owns blocks (row, b) with b fixed, straight to global memory ----
+    if (kRowsOut) {
+      const int b = tid & (TC::kBlocksPerRow - 1);
+      const bool cols_live = col0 + b * 16 < cols;
+      float mb[16];
+      if (kMean) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 f = *reinterpret_cast<const float4*>(mean + b * 16 + 4 * i);
+          mb[4 * i] = f.x; mb[4 * i + 1] = f.y; mb[4 * i + 2] = f.z; mb[4 * i + 3] = f.w;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < TC::kRowUnits; ++u) {
+        const int r = (tid + u * kQuantThreads) / TC::kBlocksPerRow;
+        const uint32_t row_addr = tile_smem + (uint32_t)r * 128u;
+        const uint32_t swz = (uint32_t)(r & 7);
+        RawBlock<T> raw;
+        if constexpr (sizeof(T) == 2) {
+          raw.a = lds128(row_addr + (((uint32_t)(2 * b) ^ swz) << 4));
+          raw.b = lds128(row_addr + (((uint32_t)(2 * b + 1) ^ swz) << 4));
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint4 w = lds128(row_addr + (((uint32_t)(4 * b + k) ^ swz) << 4));
+            raw.q[k] = make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z), __uint_as_float(w.w));
+          }
+        }
+        float v[16];
+        raw.unpack(v);
+        if (kMean) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __fsub_rn(v[i], mb[i]);
+        }
+        const float a = abs_max16(v);
+        const float s = block_scale_from_amax(a);
+        const int64_t blk = (row0 + r) * bpr + (col0 >> 4) + b;
+        uint32_t packed[2];
+        if (kSR) quantize16_sr(v, s, rng((uint64_t)blk, offset), packed);
+        else     quantize_rn<2>(v, s, packed);
+        if (cols_live && row0 + r < rows) {
+          reinterpret_cast<uint2*>(out.codes_r)[blk] = make_uint2(packed[0], packed[1]);
+          out.amax_r[blk] = a;
+          running_r = fmaxf(running_r, a);
+        }
+      }
+    }
+
+    const int64_t next = tile + gridDim.x;
+    if (next < tiles) fill_mean(next, buf ^ 1);        // its last readers passed the previous barrier
+    __syncthreads();                                   // staging complete; this tile's stage is free
+    if (tid == 0) {
+      const int64_t ahead = tile + (int64_t)TC::kStages * gridDim.x;
+      if (ahead < tiles) issue(ahead, stage);
+    }
+
+    // ---- write-out of Qt: out row j owns 64 contiguous code bytes and 8 maxima of this tile ----
+    const int64_t valid_rows = min((int64_t)TC::kRows, rows - row0);            // multiple of 16
+#pragma unroll
+    for (int k = 0; kColsOut && k < TC::kCols * 8 / kQuantThreads; ++k) {                   // 8-byte pieces: 8 per out row
+      const int i = tid + k * kQuantThreads;
+      const int j = i >> 3, piece = i & 7;
+      const int64_t orow = col0 + j;
       if (orow < cols && piece * 16 < valid_rows)
-        *reinterpret_cast<uint2*>(codes + orow * (rows >> 1) + (row0 >> 1) + piece * 8) =
-            *reinterpret_cast<const uint2*>(s_codes + j * TT::kCodePitch + piece * 8);
+        *reinterpret_cast<uint2*>(out.codes_t + orow * (rows >> 1) + (row0 >> 1) + piece * 8) =
+            *reinterpret_cast<const uint2*>(staging + (j % TC::kColsPerWord) * TC::kCodeArray + (j / TC::kColsPerWord) * TC::kCodePitch + piece * 8);
     }
-    for (int i = tid; i < TT::kCols * TT::kRowBlocks; i += kQuantThreads) {
-      const int j = i / TT::kRowBlocks, g = i % TT::kRowBlocks;
-      const int64_t orow = ct * TT::kCols + j;
-      if (orow < cols && g * 16 < valid_rows) amax_out[orow * (rows >> 4) + (row0 >> 4) + g] = s_amax[j * TT::kRowBlocks + g];
+    if (kColsOut && tid < TC::kCols * 2) {
+      const int j = tid & (TC::kCols - 1), h = tid / TC::kCols;                 // half h: row blocks 4h .. 4h+3
+      const int64_t orow = col0 + j;
+      if (orow < cols) {
+        float* dst = out.amax_t + orow * bpc + (row0 >> 4) + 4 * h;
+        float a4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a4[k] = s_amax[(4 * h + k) * TC::kCols + j];
+        if (valid_rows == TC::kRows && (bpc & 3) == 0) {
+          *reinterpret_cast<float4*>(dst) = make_float4(a4[0], a4[1], a4[2], a4[3]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) if ((4 * h + k) * 16 < valid_rows) dst[k] = a4[k];
+        }
+      }
     }
-    __syncthreads();          // staging and this tile's stage may be overwritten from here on
-    stage ^= 1;
+    if (++stage == TC::kStages) stage = 0;
   }
-  if (s_failed && tid == 0) gmax[1] = 1u;           // error word of the workspace header
-  fold_global_max(gmax, running);
+  if (s_failed) {
+    // loads of this CTA may still be in flight: give each a bounded chance to land before the CTA leaves
+    if (tid == 0) {
+      int st = stage;
+      for (int64_t t = blockIdx.x + (int64_t)it * gridDim.x, k = 0; t < tiles && k < TC::kStages; t += gridDim.x, ++k) {
+        const uint64_t t0 = global_ns();
+        while (!mbar_try(&full[st], ((it + k) / TC::kStages) & 1u) && global_ns() - t0 < kWaitLimitNs) {}
+        if (++st == TC::kStages) st = 0;
+      }
+      *out.error = 1u;                                 // error word of the workspace header
+    }
+  }
+  if (kColsOut) fold_global_max(out.gmax_t, running_t);
+  if (kRowsOut) fold_global_max(out.gmax_r, running_r);
 }
 
 // ---- pass 2: block maxima -> E4M3 bytes + unit ------------------------------------------------------
 // One thread per group of 4 scale columns (one 128-bit read of maxima, one 32-bit write).
-// For METIS_SF_MMA the loop runs over the padded extent and pads with zero bytes.
-__global__ void __launch_bounds__(kQuantThreads)
-finalize_scales_kernel(const float* __restrict__ amax, const unsigned int* __restrict__ gmax,
-                       int64_t R, int64_t sf_cols, int32_t sf_layout, uint8_t* __restrict__ scales,
-                       float* __restrict__ unit_out, uint64_t* __restrict__ offset_ctr) {
-  grid_dependency_wait();
-  const float smax = block_scale_from_amax(__uint_as_float(*gmax));
-  // quant.py:21-22; a pass-1 kernel that gave up on a load raises gmax[1]: publish NaN so that it shows
-  const float unit = gmax[1] ? __uint_as_float(0x7FC00000u) : __fdiv_rn(smax, 448.0f);
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    *unit_out = unit;
-    if (offset_ctr) *offset_ctr += 1;       // pass 1 of this call has finished: the next call draws fresh bits
-  }
-  const int64_t elem_cols = sf_cols * 16;
-  const int64_t tiles = sf_tiles_per_row(elem_cols);
-  const int64_t groups_per_row = (sf_layout == METIS_SF_MMA) ? tiles : (sf_cols + 3) / 4;
-  const int64_t R_out = (sf_layout == METIS_SF_MMA) ? ((R + 127) / 128) * 128 : R;
-  const int64_t total = R_out * groups_per_row;
-  for (int64_t i = (int64_t)blockIdx.x * kQuantThreads + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * kQuantThreads) {
-    const int64_t r = i / groups_per_row;
-    const int64_t k0 = (i - r * groups_per_row) * 4;
-    uint32_t packed = 0;
-    if (r < R) {
-      float a[4] = {0.f, 0.f, 0.f, 0.f};
-      const float* src = amax + r * sf_cols + k0;
-      if (k0 + 4 <= sf_cols && ((sf_cols & 3) == 0)) {
-        const float4 w = *reinterpret_cast<const float4*>(src);
-        a[0] = w.x; a[1] = w.y; a[2] = w.z; a[3] = w.w;
-      } else {
-        for (int j = 0; j < 4; ++j) if (k0 + j < sf_cols) a[j] = src[j];
-      }
+// For METIS_SF_MMA the loop runs over the padded extent and pads with zero bytes.  blockIdx.y picks
+// the job: the dual quantizer finishes both orientations in one launch.
+struct FinalizeJob {
+  const float* amax;  const unsigned int* gmax;  const unsigned int* error;
+  int64_t R, sf_cols;
+  int32_t sf_layout;
+  uint8_t* scales;  float* unit;
+  int32_t bx;                 // threads along a row of groups (a power of two up to the CTA size)
+};
+struct FinalizeJobs { FinalizeJob job[2]; };
+
+// E4M3 bytes of 4 neighbouring blocks from their maxima (quant.py:23): two packed conversions
+__device__ __forceinline__ uint32_t scale_bytes4(const float (&a)[4], int live, float unit) {
+  float ratio[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (k0 + j < sf_cols) {
-          const float ratio = __fdiv_rn(block_scale_from_amax(a[j]), unit);   // quant.py:23
-          packed |= (uint32_t)float_to_e4m3(ratio) << (8 * j);
-        }
-      }
+  for (int j = 0; j < 4; ++j) ratio[j] = j < live ? __fdiv_rn(block_scale_from_amax(a[j]), unit) : 0.0f;
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(ratio[0], ratio[1]), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(ratio[2], ratio[3]), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// Thread (tx, ty) of a bx x by CTA (bx per job) walks the groups tx, tx + bx, ... of the rows ty,
+// ty + by * gridDim.x, ...: no index divisions, and two rows are in flight per thread.
+__global__ void __launch_bounds__(kQuantThreads)
+finalize_scales_kernel(const FinalizeJob job0, const FinalizeJob job1, uint64_t* __restrict__ offset_ctr) {
+  grid_dependency_wait();
+  const FinalizeJob& J = blockIdx.y == 0 ? job0 : job1;
+  const int bx = J.bx, by = kQuantThreads / bx;
+  const int tx = threadIdx.x & (bx - 1), ty = threadIdx.x / bx;
+  const float* __restrict__ amax = J.amax;
+  uint8_t* __restrict__ scales = J.scales;
+  const int64_t R = J.R, sf_cols = J.sf_cols;
+  const bool tiled = J.sf_layout == METIS_SF_MMA;
+  const float smax = block_scale_from_amax(__uint_as_float(*J.gmax));
+  // quant.py:21-22; a pass-1 kernel that gave up on a load raises the error word: publish NaN so that it shows
+  const float unit = *J.error ? __uint_as_float(0x7FC00000u) : __fdiv_rn(smax, 448.0f);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *J.unit = unit;
+    if (offset_ctr && blockIdx.y == 0) *offset_ctr += 1;       // pass 1 of this call has finished: the next call draws fresh bits
+  }
+  const int64_t tiles = sf_tiles_per_row(sf_cols * 16);
+  const int groups_per_row = (int)(tiled ? tiles : (sf_cols + 3) / 4);
+  const int64_t R_out = tiled ? ((R + 127) / 128) * 128 : R;
+  const bool vec = (sf_cols & 3) == 0;
+  const int64_t row_step = (int64_t)gridDim.x * by;
+
+  auto load = [&](int64_t r, int g, float (&a)[4]) -> int {       // maxima of group g of row r; returns how many are real
+    a[0] = a[1] = a[2] = a[3] = 0.0f;
+    const int64_t k0 = (int64_t)g * 4;
+    if (r >= R || k0 >= sf_cols) return 0;
+    const float* src = amax + r * sf_cols + k0;
+    if (vec) {
+      const float4 w = *reinterpret_cast<const float4*>(src);
+      a[0] = w.x; a[1] = w.y; a[2] = w.z; a[3] = w.w;
+      return 4;
     }
-    if (sf_layout == METIS_SF_MMA) {
-      *reinterpret_cast<uint32_t*>(scales + sf_mma_offset(r, k0, tiles)) = packed;
+    const int live = (int)(sf_cols - k0 < 4 ? sf_cols - k0 : 4);
+    for (int j = 0; j < live; ++j) a[j] = src[j];
+    return live;
+  };
+  auto store = [&](int64_t r, int g, uint32_t packed, int live) {
+    const int64_t k0 = (int64_t)g * 4;
+    if (tiled) {
+      *reinterpret_cast<uint32_t*>(scales + sf_mma_offset(r, k0, tiles)) = packed;      // padding bytes are zero
+    } else if (vec) {
+      *reinterpret_cast<uint32_t*>(scales + r * sf_cols + k0) = packed;
     } else {
-      uint8_t* dst = scales + r * sf_cols + k0;
-      if (k0 + 4 <= sf_cols && ((sf_cols & 3) == 0)) {
-        *reinterpret_cast<uint32_t*>(dst) = packed;
-      } else {
-        for (int j = 0; j < 4; ++j) if (k0 + j < sf_cols) dst[j] = (uint8_t)(packed >> (8 * j));
-      }
+      for (int j = 0; j < live; ++j) scales[r * sf_cols + k0 + j] = (uint8_t)(packed >> (8 * j));
+    }
+  };
+  for (int64_t r = (int64_t)blockIdx.x * by + ty; r < R_out; r += 2 * row_step) {
+    const int64_t r2 = r + row_step;
+    for (int g = tx; g < groups_per_row; g += bx) {
+      float a[4], b[4];
+      const int la = load(r, g, a);
+      const int lb = r2 < R_out ? load(r2, g, b) : 0;
+      store(r, g, scale_bytes4(a, la, unit), la);
+      if (r2 < R_out) store(r2, g, scale_bytes4(b, lb, unit), lb);
     }
   }
 }
@@ -475,43 +638,63 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
 }
 
 template <typename T>
-static int32_t launch_cols(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
-                           uint64_t seed, uint64_t offset, const uint64_t* ctr, uint8_t* codes, const WorkspaceView& ws,
-                           cudaStream_t st) {
-  using TT = TransposeTile<T>;
+static int32_t launch_tile(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
+                           uint64_t seed, uint64_t offset, const uint64_t* ctr, const TileOutputs& out, cudaStream_t st) {
+  using TC = TileCfg<T>;
   CUtensorMap map;
   const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  if (int32_t rc = make_map(&map, dt, sizeof(T), x, cols, rows, ld * (int64_t)sizeof(T), TT::kCols, TT::kRows, "x", false))
+  if (int32_t rc = make_map(&map, dt, sizeof(T), x, cols, rows, ld * (int64_t)sizeof(T), TC::kCols, TC::kRows, "x", true))
     return rc;
-  const int64_t tiles = ceil_div(cols, TT::kCols) * ceil_div(rows, TT::kRows);
-  int64_t grid = (int64_t)sm_count() * 2;          // two CTAs of ~78 KiB per SM
+  const int64_t tiles = ceil_div(cols, TC::kCols) * ceil_div(rows, TC::kRows);
+  int64_t grid = (int64_t)sm_count() * 3;          // three CTAs of ~63 KiB per SM
   if (grid > tiles) grid = tiles;
-#define METIS_LAUNCH_COLS(MEAN, SR)                                                                         \
+  const bool with_rows = out.codes_r != nullptr, with_cols = out.codes_t != nullptr;
+#define METIS_LAUNCH_TILE(MEAN, SR, ROWS, COLS)                                                             \
   do {                                                                                                      \
-    auto kern = quantize_cols_kernel<T, MEAN, SR>;                                                          \
-    METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TT::kSmemBytes)); \
-    METIS_CUDA_OK(launch_overlapped(kLaunchStream, kern, dim3((unsigned)grid), dim3(kQuantThreads), TT::kSmemBytes, st, map, rows, cols, \
-                                    mean, seed, offset, ctr, codes, ws.amax, ws.gmax));                     \
+    auto kern = quantize_tile_kernel<T, MEAN, SR, ROWS, COLS>;                                              \
+    METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TC::kSmemBytes)); \
+    METIS_CUDA_OK(launch_overlapped(kLaunchStream, kern, dim3((unsigned)grid), dim3(kQuantThreads), TC::kSmemBytes, st, map, rows, cols, \
+                                    mean, seed, offset, ctr, out));                                         \
   } while (0)
-  if (mean) { if (sr) METIS_LAUNCH_COLS(true, true); else METIS_LAUNCH_COLS(true, false); }
-  else      { if (sr) METIS_LAUNCH_COLS(false, true); else METIS_LAUNCH_COLS(false, false); }
-#undef METIS_LAUNCH_COLS
+#define METIS_LAUNCH_TILE_MS(MEAN, SR)                                  \
+  do {                                                                  \
+    if (with_rows && with_cols) METIS_LAUNCH_TILE(MEAN, SR, true, true); \
+    else if (with_cols) METIS_LAUNCH_TILE(MEAN, SR, false, true);       \
+    else METIS_LAUNCH_TILE(MEAN, SR, true, false);                      \
+  } while (0)
+  if (mean) { if (sr) METIS_LAUNCH_TILE_MS(true, true); else METIS_LAUNCH_TILE_MS(true, false); }
+  else      { if (sr) METIS_LAUNCH_TILE_MS(false, true); else METIS_LAUNCH_TILE_MS(false, false); }
+#undef METIS_LAUNCH_TILE_MS
+#undef METIS_LAUNCH_TILE
+  return METIS_OK;
+}
+
+static int32_t launch_finalize_jobs(FinalizeJobs jobs, int njobs, cudaStream_t st, uint64_t* offset_ctr) {
+  int64_t blocks = 1;
+  for (int j = 0; j < njobs; ++j) {
+    FinalizeJob& J = jobs.job[j];
+    const bool tiled = J.sf_layout == METIS_SF_MMA;
+    const int64_t groups = tiled ? sf_tiles_per_row(J.sf_cols * 16) : ceil_div(J.sf_cols, 4);
+    const int64_t rows = tiled ? ceil_div(J.R, 128) * 128 : J.R;
+    int bx = 1;
+    while (bx < groups && bx < kQuantThreads) bx <<= 1;
+    J.bx = bx;
+    const int64_t need = ceil_div(rows, 2 * (kQuantThreads / bx));           // two rows per thread
+    if (need > blocks) blocks = need;
+  }
+  if (njobs == 1) jobs.job[1] = jobs.job[0];
+  const int64_t cap = (int64_t)sm_count() * 8 / njobs;
+  if (blocks > cap) blocks = cap;
+  METIS_CUDA_OK(launch_overlapped(kLaunchShort, finalize_scales_kernel, dim3((unsigned)blocks, (unsigned)njobs), dim3(kQuantThreads), 0, st,
+                                  jobs.job[0], jobs.job[1], offset_ctr));
   return METIS_OK;
 }
 
 int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t sf_layout,
                         uint8_t* scales, float* unit, cudaStream_t st, uint64_t* offset_ctr) {
-  const int64_t sf_cols = C / 16;
-  const int64_t groups = (sf_layout == METIS_SF_MMA)
-                             ? ceil_div(R, 128) * 128 * sf_tiles_per_row(C)
-                             : R * ceil_div(sf_cols, 4);
-  int64_t blocks = ceil_div(groups, kQuantThreads);
-  const int64_t cap = (int64_t)sm_count() * 8;
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;
-  METIS_CUDA_OK(launch_overlapped(kLaunchShort, finalize_scales_kernel, dim3((unsigned)blocks), dim3(kQuantThreads), 0, st,
-                                  ws.amax, ws.gmax, R, sf_cols, sf_layout, scales, unit, offset_ctr));
-  return METIS_OK;
+  FinalizeJobs jobs = {};
+  jobs.job[0] = {ws.amax, ws.gmax, ws.gmax + 1, R, C / 16, sf_layout, scales, unit, 0};
+  return launch_finalize_jobs(jobs, 1, st, offset_ctr);
 }
 
 int32_t check_quant_outputs(int64_t R, int64_t C, int32_t sf_layout, const void* codes,
@@ -583,7 +766,16 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   }
   const WorkspaceView ws = view_workspace(workspace);
   METIS_CUDA_OK(cudaMemsetAsync(ws.gmax, 0, 2 * sizeof(unsigned int), st));   // running maximum and error word
-  if (!transpose) {
+  // Large row-major tensors take the tile kernel too (row phase only): its TMA ring keeps two tiles in
+  // flight per CTA, where the register-fed kernel waits on its loads.  Same arithmetic, same bytes.
+  const bool rows_by_tiles = !transpose && rows * cols >= kTileRowsMinElements && (ld * esz) % 16 == 0;
+  if (rows_by_tiles) {
+    const TileOutputs out = {nullptr, nullptr, nullptr, codes, ws.amax, ws.gmax, ws.gmax + 1};
+    const int32_t rc = x_dtype == METIS_DTYPE_BF16
+        ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
+        : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
+    if (rc) return rc;
+  } else if (!transpose) {
     if (x_dtype == METIS_DTYPE_BF16)
       launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr,
                   reinterpret_cast<uint32_t*>(codes), ws, st);
@@ -591,13 +783,65 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
       launch_rows(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr,
                   reinterpret_cast<uint32_t*>(codes), ws, st);
   } else {
+    const TileOutputs out = {codes, ws.amax, ws.gmax, nullptr, nullptr, nullptr, ws.gmax + 1};
     const int32_t rc = x_dtype == METIS_DTYPE_BF16
-        ? launch_cols(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, codes, ws, st)
-        : launch_cols(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, codes, ws, st);
+        ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
+        : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
     if (rc) return rc;
   }
   METIS_CUDA_OK(cudaGetLastError());
   return launch_finalize(ws, R, C, sf_layout, scales, unit, st, ctr);
+}
+
+extern "C" int64_t metis_nvfp4_quantize_dual_workspace_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return kHeaderBytes;
+  return kHeaderBytes + 2 * rows * ceil_div(cols, 16) * (int64_t)sizeof(float);
+}
+
+extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                             const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,
+                                             int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,
+                                             uint8_t* codes_t, uint8_t* scales_t, float* unit_t, void* workspace,
+                                             int64_t workspace_bytes, void* stream) {
+  const bool sr = flags & METIS_Q_STOCHASTIC;
+  uint64_t* ctr = (sr && (flags & METIS_Q_OFFSET_ON_DEVICE)) ? reinterpret_cast<uint64_t*>(static_cast<uintptr_t>(offset)) : nullptr;
+  if (ctr) offset = 0;
+  if ((flags & METIS_Q_OFFSET_ON_DEVICE) && (!sr || !ctr || (reinterpret_cast<uintptr_t>(ctr) & 7u)))
+    return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_OFFSET_ON_DEVICE needs METIS_Q_STOCHASTIC and an 8-byte aligned device address in offset");
+  if (flags & ~(METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x (the dual quantizer always writes both orientations)", flags);
+  if (!x) return fail(METIS_ERR_BAD_ARGUMENT, "x is null");
+  if (x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown x_dtype %d", x_dtype);
+  if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)rows, (long long)cols);
+  if (rows % 16 != 0 || cols % 16 != 0)
+    return fail(METIS_ERR_BAD_SHAPE, "NVFP4 block shape (1, 16) does not divide both dimensions of tensor shape (%lld, %lld)", (long long)rows, (long long)cols);
+  if (ld < cols) return fail(METIS_ERR_BAD_ARGUMENT, "ld %lld < cols %lld", (long long)ld, (long long)cols);
+  if (sf_layout != METIS_SF_ROWMAJOR && sf_layout != METIS_SF_MMA) return fail(METIS_ERR_BAD_ARGUMENT, "unknown sf_layout %d", sf_layout);
+  if (!codes || !scales || !unit || !codes_t || !scales_t || !unit_t || !workspace) return fail(METIS_ERR_BAD_ARGUMENT, "null output pointer");
+  const int64_t esz = x_dtype == METIS_DTYPE_BF16 ? 2 : 4;
+  if (ld % (16 / esz) != 0 || !aligned16(x) || !aligned16(codes) || !aligned16(scales) || !aligned16(codes_t) || !aligned16(scales_t) || !aligned16(workspace))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "x, codes, scales and workspace must be 16-byte aligned, rows of x too");
+  if (col_mean && !aligned16(col_mean)) return fail(METIS_ERR_BAD_ALIGNMENT, "col_mean must be 16-byte aligned");
+  if (workspace_bytes < metis_nvfp4_quantize_dual_workspace_bytes(rows, cols))
+    return fail(METIS_ERR_WORKSPACE, "workspace of %lld bytes, need %lld", (long long)workspace_bytes,
+                (long long)metis_nvfp4_quantize_dual_workspace_bytes(rows, cols));
+  if (rows >= ((int64_t)1 << 31) || cols >= ((int64_t)1 << 31)) return fail(METIS_ERR_TOO_LARGE, "tensor too large");
+
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // header: [0] largest block maximum of Q, [1] error word, [2] largest block maximum of Qt
+  unsigned int* head = static_cast<unsigned int*>(workspace);
+  float* amax_r = reinterpret_cast<float*>(static_cast<char*>(workspace) + kHeaderBytes);
+  float* amax_t = amax_r + rows * (cols / 16);
+  METIS_CUDA_OK(cudaMemsetAsync(head, 0, 3 * sizeof(unsigned int), st));
+  const TileOutputs out = {codes_t, amax_t, head + 2, codes, amax_r, head, head + 1};
+  const int32_t rc = x_dtype == METIS_DTYPE_BF16
+      ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
+      : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
+  if (rc) return rc;
+  METIS_CUDA_OK(cudaGetLastError());
+  FinalizeJobs jobs = {};
+  jobs.job[0] = {amax_r, head, head + 1, rows, cols / 16, sf_layout, scales, unit, 0};
+  jobs.job[1] = {amax_t, head + 2, head + 1, cols, rows / 16, sf_layout, scales_t, unit_t, 0};
+  return launch_finalize_jobs(jobs, 2, st, ctr);
 }
 
 extern "C" int64_t metis_col_mean_workspace_bytes(int64_t rows, int64_t cols) {

@@ -16,7 +16,7 @@ _DTYPES = {torch.bfloat16: cabi.DTYPE_BF16, torch.float32: cabi.DTYPE_F32}
 
 # Kernels of this library launched since import, by entry point (two per quantizer call: the
 # streaming pass and the scale pass; the memset between them is not a kernel).
-LAUNCHES = {"quantize": 0, "rmsnorm_quantize": 0, "dequantize": 0, "col_mean": 0, "gemv": 0, "gemm": 0}
+LAUNCHES = {"quantize": 0, "rmsnorm_quantize": 0, "dequantize": 0, "col_mean": 0, "gemv": 0, "gemm": 0, "lowrank_bwd": 0}
 
 
 def launch_count() -> int:
@@ -162,6 +162,47 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
         else:
             q.row_vec = mean
     return q
+
+
+def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int = 0, offset: int = 0,
+                        sf_layout: int = cabi.SF_MMA, mean: Optional[torch.Tensor] = None,
+                        offset_counter: Optional[torch.Tensor] = None):
+    """Both quantizations of x viewed as [rows, cols] from one pass over it: (Q of x, Q of x^T), each
+    bit-identical to the separate call (round to nearest).  rows and cols must be multiples of 16."""
+    _need_cuda(x, "x")
+    x2 = _rows2d(x)
+    rows, cols = x2.shape
+    if rows % 16 != 0 or cols % 16 != 0 or rows == 0:
+        raise ValueError(f"NVFP4 block shape (1, 16) does not divide both dimensions of tensor shape {(rows, cols)}")
+    L = cabi.lib()
+    flags = cabi.Q_STOCHASTIC if stochastic else 0
+    dev = x2.device
+    if stochastic and offset_counter is not None:
+        if offset_counter.dtype != torch.int64 or offset_counter.device != dev or offset_counter.numel() != 1:
+            raise ValueError("offset_counter must be an int64 tensor with one element on the device of x")
+        flags |= cabi.Q_OFFSET_ON_DEVICE
+        offset = offset_counter.data_ptr()
+    if mean is not None:
+        _need_cuda(mean, "mean")
+        mean = mean.reshape(-1).to(torch.float32).contiguous()
+        assert mean.numel() == cols
+    with _on_device(dev):
+        codes, scales, unit = _packed_buffers(L, rows, cols, sf_layout, dev)
+        codes_t, scales_t, unit_t = _packed_buffers(L, cols, rows, sf_layout, dev)
+        ws = torch.empty(L.metis_nvfp4_quantize_dual_workspace_bytes(rows, cols), dtype=torch.uint8, device=dev)
+        rc = L.metis_nvfp4_quantize_dual(x2.data_ptr(), _dtype_code(x2, "x"), rows, cols, x2.stride(0), _ptr(mean),
+                                         flags, seed & (2**64 - 1), offset & (2**64 - 1), sf_layout,
+                                         codes.data_ptr(), scales.data_ptr(), unit.data_ptr(),
+                                         codes_t.data_ptr(), scales_t.data_ptr(), unit_t.data_ptr(),
+                                         ws.data_ptr(), ws.numel(), _stream())
+    cabi.check(rc, "metis_nvfp4_quantize_dual")
+    LAUNCHES["quantize"] += 2
+    q = NVFP4Tensor(codes, scales, unit, (rows, cols), sf_layout)
+    qt = NVFP4Tensor(codes_t, scales_t, unit_t, (cols, rows), sf_layout)
+    if mean is not None:
+        q.row_vec = mean
+        qt.col_vec = mean
+    return q, qt
 
 
 def rmsnorm_nvfp4_quantize(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, *,
@@ -321,4 +362,76 @@ def nvfp4_gemm(a: NVFP4Tensor, b: NVFP4Tensor, *, lowrank=None, rank1=(), c: Opt
         rc = cabi.lib().metis_nvfp4_gemm(C.byref(args))
     cabi.check(rc, "metis_nvfp4_gemm")
     LAUNCHES["gemm"] += 2 if ws_bytes > 0 else 1
+    return out
+
+
+def _bf16_rows(t: torch.Tensor, what: str) -> torch.Tensor:
+    _need_cuda(t, what)
+    if t.dtype != torch.bfloat16 or t.dim() != 2:
+        raise TypeError(f"{what} must be a bf16 matrix")
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def bf16_panel_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
+                    status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """D = A_op B_op^T in bf16 on the tensor core, fp32 out, at most 256 columns.  a is [Mg, Kg], or
+    [Kg, Mg] with a_mn_major; b is [Ng, Kg], or [Kg, Ng] with b_mn_major."""
+    a, b = _bf16_rows(a, "a"), _bf16_rows(b, "b")
+    Mg, Kg = (a.shape[1], a.shape[0]) if a_mn_major else a.shape
+    Ng, Kb = (b.shape[1], b.shape[0]) if b_mn_major else b.shape
+    if Kg != Kb:
+        raise ValueError(f"inner dimensions differ: {Kg} vs {Kb}")
+    L = cabi.lib()
+    with _on_device(a.device):
+        out = torch.empty((Mg, Ng), dtype=torch.float32, device=a.device)
+        ws = torch.empty(max(16, L.metis_bf16_panel_gemm_workspace_bytes(Mg, Ng, Kg)), dtype=torch.uint8, device=a.device)
+        rc = L.metis_bf16_panel_gemm(a.data_ptr(), int(a_mn_major), a.stride(0), b.data_ptr(), int(b_mn_major), b.stride(0),
+                                     Mg, Ng, Kg, out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(), _ptr(status), _stream())
+    cabi.check(rc, "metis_bf16_panel_gemm")
+    LAUNCHES["lowrank_bwd"] += 2
+    return out
+
+
+def lowrank_dts(g: torch.Tensor, u: torch.Tensor, yv: torch.Tensor, s: torch.Tensor, status: Optional[torch.Tensor] = None):
+    """(d_yv, ds) of the low-rank branch from one pass over g [M, N]: d_ts = bf16(g @ u), d_yv = bf16(d_ts * s),
+    ds = sum over rows of bf16(d_ts * yv) in fp32.  u [N, r], yv [M, r] bf16; s [r] bf16 or fp32."""
+    g, u, yv = _bf16_rows(g, "g"), _bf16_rows(u, "u"), _bf16_rows(yv, "yv")
+    M, N = g.shape
+    r = u.shape[1]
+    if u.shape[0] != N or yv.shape != (M, r) or s.numel() != r:
+        raise ValueError(f"shapes do not fit: g {tuple(g.shape)}, u {tuple(u.shape)}, yv {tuple(yv.shape)}, s {tuple(s.shape)}")
+    if s.dtype not in (torch.bfloat16, torch.float32):
+        s = s.float()
+    s = s.reshape(-1).contiguous()
+    L = cabi.lib()
+    with _on_device(g.device):
+        d_yv = torch.empty((M, r), dtype=torch.bfloat16, device=g.device)
+        ds = torch.empty(r, dtype=torch.float32, device=g.device)
+        ws = torch.empty(L.metis_lowrank_dts_workspace_bytes(M, N, r), dtype=torch.uint8, device=g.device)
+        rc = L.metis_lowrank_dts(g.data_ptr(), g.stride(0), M, N, u.data_ptr(), u.stride(0), r, yv.data_ptr(), yv.stride(0),
+                                 s.data_ptr(), _dtype_code(s, "s"), d_yv.data_ptr(), d_yv.stride(0), ds.data_ptr(),
+                                 ws.data_ptr(), ws.numel(), _ptr(status), _stream())
+    cabi.check(rc, "metis_lowrank_dts")
+    LAUNCHES["lowrank_bwd"] += 2
+    return d_yv, ds
+
+
+def lowrank_du(g: torch.Tensor, ts: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dU = g^T @ ts [N, r] for g [M, N] and ts [M, r] (bf16), one pass over g, no transposed copies."""
+    g, ts = _bf16_rows(g, "g"), _bf16_rows(ts, "ts")
+    M, N = g.shape
+    r = ts.shape[1]
+    if ts.shape[0] != M:
+        raise ValueError(f"shapes do not fit: g {tuple(g.shape)}, ts {tuple(ts.shape)}")
+    L = cabi.lib()
+    with _on_device(g.device):
+        out = torch.empty((N, r), dtype=out_dtype, device=g.device)
+        ws = torch.empty(L.metis_lowrank_du_workspace_bytes(M, N, r), dtype=torch.uint8, device=g.device)
+        rc = L.metis_lowrank_du(g.data_ptr(), g.stride(0), M, N, ts.data_ptr(), ts.stride(0), r, out.data_ptr(), _DTYPES[out_dtype],
+                                out.stride(0), ws.data_ptr(), ws.numel(), _ptr(status), _stream())
+    cabi.check(rc, "metis_lowrank_du")
+    LAUNCHES["lowrank_bwd"] += 2
     return out

@@ -120,7 +120,7 @@ int64_t metis_nvfp4_quantize_workspace_bytes(int64_t R, int64_t C);
  * x.float()): s = amax/6 + 1e-9 per block; unit = max(s)/448; scale = e4m3(s/unit);
  * code = round-half-even of |x|/(s/2) folded onto the e2m1 grid; sign bit = (x < 0).
  * Stochastic mode adds U[-0.5, 0.5) to the folded index before rounding.  The random bits are
- * Philox4x32-10(seed; element index, offset).  With METIS_Q_OFFSET_ON_DEVICE the offset is not
+ * Philox4x32-10(seed; block index, offset), 16 bits per element.  With METIS_Q_OFFSET_ON_DEVICE the offset is not
  * the argument's value but the content of the device uint64 it points to (8-byte aligned),
  * and the call adds 1 to that counter when its kernels have read it: successive calls on one
  * stream draw fresh bits although their arguments are identical, which is what a captured
@@ -138,6 +138,28 @@ int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64
                              void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * Both quantizations of one tensor from ONE pass over it: Q = quantize(x) [rows, cols] (blocks along
+ * the columns) and Qt = quantize(x^T) [cols, rows] (blocks along the rows).  A training step needs
+ * both for every operand: the forward product and dX contract over the last dimension
+ * (bitlinear.py:435, :508), dW contracts over the tokens (bitlinear.py:502-505), so the reference's
+ * one fake-quantized tensor becomes two packed ones here (call sites bitlinear.py:392, :331,
+ * :400-402, :580).  Reads x from HBM once instead of twice; outputs are bit-identical to two calls of
+ * metis_nvfp4_quantize (round to nearest; stochastic rounding draws from two disjoint Philox
+ * counter spaces).  rows and cols must both be multiples of 16.  flags: METIS_Q_STOCHASTIC,
+ * METIS_Q_OFFSET_ON_DEVICE.  Launches: zero-fill of the workspace header, one tile pass, one scale
+ * pass that finishes both outputs.
+ *   codes    uint8 [rows, cols/2]   scales    metis_nvfp4_sf_bytes(rows, cols, sf_layout)   unit    fp32 [1]
+ *   codes_t  uint8 [cols, rows/2]   scales_t  metis_nvfp4_sf_bytes(cols, rows, sf_layout)   unit_t  fp32 [1]
+ *   workspace  metis_nvfp4_quantize_dual_workspace_bytes(rows, cols)
+ */
+int64_t metis_nvfp4_quantize_dual_workspace_bytes(int64_t rows, int64_t cols);
+int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                  const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,
+                                  int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,
+                                  uint8_t* codes_t, uint8_t* scales_t, float* unit_t,
+                                  void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * The same round-to-nearest, row-major quantizer for callers that cannot hand over a workspace
  * and must not trigger an allocation: a serving process whose device memory was divided up once
  * at start-up, a host binding that holds raw device pointers but no allocator, code for which
@@ -149,7 +171,9 @@ int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64
  * METIS_STATIC_MAX_ELEMENTS; larger tensors are rejected with METIS_ERR_TOO_LARGE.  The call
  * allocates nothing (no cudaMalloc/cudaFree, no allocating library routine).
  *  - The first call on each device looks the array's address up (cudaGetSymbolAddress) with that
- *    device current; make that first call before any stream capture begins.
+ *    device current; make that first call before any stream capture begins.  Under the runtime's
+ *    lazy module loading the array itself comes into being with the library's first kernel on a
+ *    device, whichever entry point launches it: "allocates nothing" is a statement about this call.
  *  - All calls on a device share the one array and it keeps the previous call's contents; the call
  *    clears the part that has to start at zero.  Two calls that overlap on the GPU (different
  *    streams, or threads) race on it: serialise them.
@@ -248,7 +272,9 @@ typedef struct metis_gemm_args {
   const void* c;  int64_t ldc;      /* optional addend, dtype d_dtype */
   void* d;        int64_t ldd;
   int32_t d_dtype;          /* METIS_DTYPE_BF16 or METIS_DTYPE_F32 */
-  int32_t reserved;
+  int32_t reserved;         /* 0.  Two test hooks are accepted: 1 makes the first bounded wait expire (the status
+                               word then reads METIS_DEV_TIMEOUT_TMA; results are not meaningful), 8 runs the
+                               single-CTA kernel where CTA pairs would be chosen.  Anything else is rejected. */
   int32_t* status;          /* optional device int32: 0, or a METIS_DEV_* code */
   void* stream;
   void* workspace;          /* optional scratch, 16-byte aligned: metis_nvfp4_gemm_workspace_bytes */
@@ -264,6 +290,46 @@ int32_t metis_nvfp4_gemm(const metis_gemm_args* args);
  * product runs unsplit on fewer SMs; the result is the same up to fp32 summation order.
  */
 int64_t metis_nvfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/* ---- backward of the unquantized low-rank branch ------------------------------------------------------ */
+
+/*
+ * D[Mg, Ng] = A B^T in bf16 with fp32 accumulation on tcgen05 (kind::f16), Ng <= 256: the skinny
+ * products of the rank-r branch.  Either operand may be stored with the contraction in its rows:
+ *   a_mn_major = 0: a is [Mg, Kg] (row pitch lda);  1: a is [Kg, Mg]
+ *   b_mn_major = 0: b is [Ng, Kg] (row pitch ldb);  1: b is [Kg, Ng]
+ * so neither grad_output nor a factor is transposed in memory first.  d is fp32 [Mg, ldd].  The K loop
+ * is split over the SMs; workspace holds the fp32 partial sums, added in a fixed order.
+ * Building block of the two entry points below; replaces torch.matmul in autograd's backward of
+ * ulinear (src/Metis/Metis/bitlinear.py:756-757).
+ */
+int64_t metis_bf16_panel_gemm_workspace_bytes(int64_t Mg, int64_t Ng, int64_t Kg);
+int32_t metis_bf16_panel_gemm(const void* a, int32_t a_mn_major, int64_t lda, const void* b, int32_t b_mn_major,
+                              int64_t ldb, int64_t Mg, int64_t Ng, int64_t Kg, float* d, int64_t ldd,
+                              void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+
+/*
+ * Gradient through ulinear and the scaling by s (bitlinear.py:752-757: y = torch.mul(self.s, y);
+ * y = self.ulinear(y)), as autograd computes it in bf16:
+ *   d_ts = bf16(G U)                   G = grad_output [M, N] bf16, U = ulinear.weight [N, r] bf16
+ *   d_yv = bf16(d_ts * bf16(s))        the output gradient of vlinear, bf16 [M, r]
+ *   ds   = sum_m bf16(d_ts * y_v)      fp32 [r]; y_v = vlinear's output, bf16 [M, r]
+ * One pass over G.  s is bf16 or fp32 [r].  r a multiple of 8 up to 256, N a multiple of 8.
+ */
+int64_t metis_lowrank_dts_workspace_bytes(int64_t M, int64_t N, int64_t r);
+int32_t metis_lowrank_dts(const void* g, int64_t ldg, int64_t M, int64_t N, const void* u, int64_t ldu, int64_t r,
+                          const void* yv, int64_t ldyv, const void* s, int32_t s_dtype, void* d_yv, int64_t ldd,
+                          float* ds, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+
+/*
+ * Weight gradient of ulinear: dU = G^T ts [N, r] with ts = bf16(s * y_v) [M, r] (bitlinear.py:756-757
+ * through autograd), contraction over the tokens, both operands read as they lie in memory.
+ * grad_u is bf16 or fp32 [N, ldgu].  One pass over G.
+ */
+int64_t metis_lowrank_du_workspace_bytes(int64_t M, int64_t N, int64_t r);
+int32_t metis_lowrank_du(const void* g, int64_t ldg, int64_t M, int64_t N, const void* ts, int64_t ldts, int64_t r,
+                         void* grad_u, int32_t u_dtype, int64_t ldgu, void* workspace, int64_t workspace_bytes,
+                         int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -185,6 +185,17 @@ def test_row_and_transposed_quantizers_at_sweep_sizes(tokens, hidden):
     del centred
     cols_c = _sample_with_top_row(centred_t, 16, seed=4)
     _assert_rows_equal_oracle(qct, centred_t[cols_c].cpu().numpy(), cols_c, tokens, "mean-centred transposed kernel")
+    # one pass for both orientations: the same bytes as the two separate kernels
+    qd, qdt = ops.nvfp4_quantize_dual(x, sf_layout=cabi.SF_ROWMAJOR)
+    assert torch.equal(qd.codes, q.codes) and torch.equal(qd.scales, q.scales) and torch.equal(qd.unit, q.unit)
+    assert torch.equal(qdt.codes, qt.codes) and torch.equal(qdt.scales, qt.scales) and torch.equal(qdt.unit, qt.unit)
+    qd, qdt = ops.nvfp4_quantize_dual(x, mean=mean, sf_layout=cabi.SF_ROWMAJOR)
+    assert torch.equal(qd.codes, qc.codes) and torch.equal(qd.scales, qc.scales) and torch.equal(qd.unit, qc.unit)
+    assert torch.equal(qdt.codes, qct.codes) and torch.equal(qdt.scales, qct.scales) and torch.equal(qdt.unit, qct.unit)
+    qd, qdt = ops.nvfp4_quantize_dual(x, stochastic=True, seed=5, offset=2, mean=mean, sf_layout=cabi.SF_ROWMAJOR)
+    _assert_stochastic_on_neighbours(qd, qc, x.float() - mean)
+    _assert_stochastic_on_neighbours(qdt, qct, centred_t, slab=256)
+    del qd, qdt
     # stochastic rounding, both orientations
     qs = ops.nvfp4_quantize(x, stochastic=True, seed=11, offset=5, sf_layout=cabi.SF_ROWMAJOR)
     _assert_stochastic_on_neighbours(qs, q, x)

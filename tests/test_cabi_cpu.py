@@ -100,3 +100,19 @@ def test_ops_refuse_cpu_tensors(built_library):
     from fp4_post_b200 import ops
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         ops.nvfp4_quantize(torch.zeros(4, 32))
+
+
+def test_gemm_rejects_reserved_bits_other_than_the_two_test_hooks(L):
+    # the timing knobs of development builds (issue no MMAs, request no data) do not exist in the shipped library
+    from fp4_post_b200 import cabi
+    buf = (C.c_uint8 * 1024)()
+    p = C.addressof(buf)
+    p += (-p) % 256
+    for bits in (2, 4, 6, 16, 2 | 8):
+        a = cabi.GemmArgs()
+        a.M, a.N, a.K = 256, 256, 256
+        for f in ("a_codes", "a_scales", "a_unit", "b_codes", "b_scales", "b_unit", "d"):
+            setattr(a, f, p)
+        a.ldd, a.d_dtype, a.alpha, a.reserved = 256, cabi.DTYPE_BF16, 1.0, bits
+        rc = L.metis_nvfp4_gemm(C.byref(a))
+        assert rc == -1 and b"reserved" in L.metis_last_error_string(), bits

@@ -132,8 +132,8 @@ def test_packed_backward_equals_the_chain_rule_on_the_operands_it_consumed(backw
     recorded = []
     real = F._pack_centred
 
-    def spy(tensor, quantizer, centred, mean_cache=None, cache_key="default"):
-        op = real(tensor, quantizer, centred, mean_cache, cache_key)
+    def spy(tensor, quantizer, centred, mean_cache=None, cache_key="default", **kw):
+        op = real(tensor, quantizer, centred, mean_cache, cache_key, **kw)
         recorded.append(op)
         return op
 
@@ -220,6 +220,39 @@ def test_bf16_input_gradient_fused_into_one_launch_matches_two_launches():
     assert rel_l2(grads[True], grads[False]) <= 1e-2
 
 
+def test_native_backward_of_the_unquantized_branch_matches_torch_matmul():
+    # dU, ds and d_yv from the tensor-core panel products against the same step with torch.matmul for
+    # the U branch; round to nearest everywhere, so that everything downstream of d_yv is deterministic
+    from Metis.Metis.bitlinear import MetisFusedFunction
+    torch.manual_seed(7)
+    args = metis_args(64, cache=True)
+    layer = BitLinear(1024, 768, args=args, bias=False, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+    layer.layer_name = "ubranch"
+    layer.split()
+    layer = layer.to(DEV)
+    x = torch.randn(2, 512, 1024, device=DEV, dtype=torch.bfloat16)
+    gout = torch.randn(2, 512, 768, device=DEV, dtype=torch.bfloat16)
+    res = {}
+    for native in (True, False):
+        MetisFusedFunction.native_lowrank_backward = native
+        try:
+            xin = x.clone().requires_grad_(True)
+            for p in layer.parameters():
+                p.grad = None
+            layer(xin).backward(gout)
+            res[native] = {k: v.float().cpu().numpy() for k, v in dict(
+                dx=xin.grad, dR=layer.warmup_linear.weight.grad, dV=layer.vlinear.weight.grad,
+                dU=layer.ulinear.weight.grad, ds=layer.s.grad).items()}
+        finally:
+            MetisFusedFunction.native_lowrank_backward = True
+    # same bf16 inputs, fp32 accumulation on both sides: only summation order and a rare last-bit flip differ
+    assert rel_l2(res[True]["dU"], res[False]["dU"]) <= 4e-3
+    assert rel_l2(res[True]["ds"], res[False]["ds"]) <= 1e-2
+    for name in ("dx", "dR"):
+        assert rel_l2(res[True][name], res[False][name]) <= 1e-2, name
+    assert rel_l2(res[True]["dV"], res[False]["dV"]) <= 5e-2       # d_yv is re-quantized: a flipped bf16 bit may move a code
+
+
 def test_second_stream_gives_the_gradients_of_the_single_stream_order_bit_for_bit():
     # round to nearest everywhere, cached weights (so that the forward overlaps too): a missing
     # dependency between the two streams would show as a difference
@@ -265,12 +298,18 @@ def test_grpo_defaults_bf16_stochastic_backward_and_shared_activation():
 
     calls = {"n": 0}
     real = Cast2NVFp4e2m1BlockNOSR.quantize_packed.__func__
+    real_dual = Cast2NVFp4e2m1BlockNOSR.quantize_packed_dual.__func__
 
     def counting(cls, x, **kw):
         calls["n"] += 1
         return real(cls, x, **kw)
 
+    def counting_dual(cls, x, **kw):             # autograd is recording: row-major and transposed from one pass
+        calls["n"] += 1
+        return real_dual(cls, x, **kw)
+
     Cast2NVFp4e2m1BlockNOSR.quantize_packed = classmethod(counting)
+    Cast2NVFp4e2m1BlockNOSR.quantize_packed_dual = classmethod(counting_dual)
     try:
         x = torch.randn(4, 64, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
         q, k = blk.q_proj(x), blk.k_proj(x)
@@ -288,6 +327,7 @@ def test_grpo_defaults_bf16_stochastic_backward_and_shared_activation():
         assert calls["n"] == before + 1           # only the changed weight
     finally:
         Cast2NVFp4e2m1BlockNOSR.quantize_packed = classmethod(real)
+        Cast2NVFp4e2m1BlockNOSR.quantize_packed_dual = classmethod(real_dual)
     for name, p in model.named_parameters():
         assert p.grad is not None and p.grad.dtype == torch.bfloat16 and torch.isfinite(p.grad).all(), name
     assert x.grad is not None and torch.isfinite(x.grad).all()

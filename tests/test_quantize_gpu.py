@@ -246,3 +246,59 @@ def test_every_bf16_value_below_a_block_maximum():
     # the transposed kernel sees the same blocks as columns
     qt = ops.nvfp4_quantize(x.t().contiguous().to(DEV), transpose=True, sf_layout=cabi.SF_ROWMAJOR)
     assert np.array_equal(qt.codes.cpu().numpy(), ocodes) and np.array_equal(qt.scales.cpu().numpy(), oscales.reshape(-1))
+
+
+# ---- row-major and transposed quantization from one pass --------------------------------------------------
+
+def _same(a, b):
+    return torch.equal(a.codes, b.codes) and torch.equal(a.scales, b.scales) and torch.equal(a.unit, b.unit)
+
+
+@pytest.mark.parametrize("rows,cols,kind", [(16, 16, "normal"), (48, 80, "outliers"), (128, 64, "normal"), (144, 1536, "student"),
+                                            (2048, 2048, "outliers"), (1040, 3584, "student"), (4096, 272, "normal")])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("layout", [cabi.SF_ROWMAJOR, cabi.SF_MMA])
+def test_one_pass_gives_both_orientations_bit_for_bit(rows, cols, kind, dtype, layout):
+    x = synthetic(rows, cols, kind, seed=rows + 3 * cols, dtype=dtype).to(DEV)
+    torch.empty(1 << 22, device=DEV, dtype=torch.uint8).fill_(0xA5)       # stale bytes where the outputs will land
+    q, qt = ops.nvfp4_quantize_dual(x, sf_layout=layout)
+    assert q.shape == (rows, cols) and qt.shape == (cols, rows)
+    assert _same(q, ops.nvfp4_quantize(x, sf_layout=layout))
+    assert _same(qt, ops.nvfp4_quantize(x, transpose=True, sf_layout=layout))
+    if layout == cabi.SF_ROWMAJOR:                                         # and both against the oracle
+        assert_packed_equal(q, x.float().cpu().numpy(), layout, what="dual, row-major")
+        assert_packed_equal(qt, x.float().t().contiguous().cpu().numpy(), layout, what="dual, transposed")
+    mean = ops.col_mean(x)
+    q, qt = ops.nvfp4_quantize_dual(x, mean=mean, sf_layout=layout)
+    assert _same(q, ops.nvfp4_quantize(x, mean=mean, sf_layout=layout))
+    assert _same(qt, ops.nvfp4_quantize(x, transpose=True, mean=mean, sf_layout=layout))
+    assert q.row_vec is mean or torch.equal(q.row_vec, mean)
+    assert torch.equal(qt.col_vec, mean)
+
+
+def test_one_pass_takes_a_strided_view_and_rejects_ragged_token_counts():
+    wide = synthetic(256, 1024, "normal", seed=4, dtype=torch.bfloat16).to(DEV)
+    view = wide[:, 256:768]
+    q, qt = ops.nvfp4_quantize_dual(view, sf_layout=cabi.SF_ROWMAJOR)
+    assert _same(q, ops.nvfp4_quantize(view.contiguous(), sf_layout=cabi.SF_ROWMAJOR))
+    assert _same(qt, ops.nvfp4_quantize(view.contiguous(), transpose=True, sf_layout=cabi.SF_ROWMAJOR))
+    with pytest.raises(ValueError, match="does not divide"):
+        ops.nvfp4_quantize_dual(torch.zeros(24, 32, device=DEV))
+
+
+def test_one_pass_stochastic_keeps_the_scales_and_draws_two_independent_streams():
+    x = synthetic(512, 512, "normal", seed=8, dtype=torch.bfloat16).to(DEV)
+    q, qt = ops.nvfp4_quantize_dual(x, stochastic=True, seed=3, offset=9, sf_layout=cabi.SF_ROWMAJOR)
+    qr, qtr = ops.nvfp4_quantize_dual(x, sf_layout=cabi.SF_ROWMAJOR)
+    assert torch.equal(q.scales, qr.scales) and torch.equal(q.unit, qr.unit)
+    assert torch.equal(qt.scales, qtr.scales) and torch.equal(qt.unit, qtr.unit)
+    # same seed and offset: the same bits again; the two orientations do not share theirs
+    q2, qt2 = ops.nvfp4_quantize_dual(x, stochastic=True, seed=3, offset=9, sf_layout=cabi.SF_ROWMAJOR)
+    assert torch.equal(q.codes, q2.codes) and torch.equal(qt.codes, qt2.codes)
+    sym = synthetic(512, 512, "normal", seed=9, dtype=torch.bfloat16)
+    sym = (sym + sym.t()).to(DEV)                                          # x = x^T: both outputs quantize the same matrix
+    a, b = ops.nvfp4_quantize_dual(sym, stochastic=True, seed=3, offset=9, sf_layout=cabi.SF_ROWMAJOR)
+    assert torch.equal(a.scales, b.scales) and not torch.equal(a.codes, b.codes)
+    # both dequantize to x without bias
+    for part, ref in ((q, x.float()), (qt, x.float().t())):
+        assert (part.dequantize(torch.float32) - ref).mean().abs().item() < 5e-3

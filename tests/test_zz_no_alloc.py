@@ -12,10 +12,12 @@ every other test.
 """
 import ctypes as C
 
+import numpy as np
 import pytest
 import torch
 
 from fp4_post_b200 import cabi, ops
+from oracle import nvfp4_oracle as O
 
 
 @pytest.fixture(scope="module", autouse=True)
@@ -49,6 +51,29 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point():
         assert torch.equal(unit, want.unit)
         assert torch.equal(codes, want.codes)
         assert torch.equal(scales, want.scales)
+    # and against the CPU oracle itself, not only against the sibling entry point
+    codes, scales, unit = _static_quantize(second, cabi.SF_ROWMAJOR)
+    ocodes, oscales, ounit, _ = O.quantize(second.cpu().numpy())
+    assert np.float32(unit.item()) == ounit
+    assert np.array_equal(codes.cpu().numpy(), ocodes) and np.array_equal(scales.cpu().numpy(), oscales.reshape(-1))
+
+
+@pytest.mark.gpu
+def test_a_tensor_of_exactly_the_limit_fills_the_whole_scratch():
+    # METIS_STATIC_MAX_ELEMENTS elements: the last block maximum lands in the last word of the array
+    rows, cols = cabi.STATIC_MAX_ELEMENTS // 4096, 4096
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(rows, cols, device="cuda", generator=g).to(torch.bfloat16)
+    x[-1, -16:] = 300.0                                       # the largest block is the very last one
+    codes, scales, unit = _static_quantize(x, cabi.SF_ROWMAJOR)
+    want = ops.nvfp4_quantize(x, sf_layout=cabi.SF_ROWMAJOR)
+    torch.cuda.synchronize()
+    assert torch.equal(unit, want.unit) and torch.equal(codes, want.codes) and torch.equal(scales, want.scales)
+    tail = x[-8:].float().cpu().numpy()
+    ocodes, oscales, ounit, _ = O.quantize(tail)              # these rows hold the largest block: same unit as the whole
+    assert np.float32(unit.item()) == ounit
+    assert np.array_equal(codes[-8:].cpu().numpy(), ocodes)
+    assert np.array_equal(scales.view(rows, cols // 16)[-8:].cpu().numpy(), oscales)
 
 
 def test_a_tensor_beyond_the_limit_is_rejected_before_anything_runs(built_library):
