@@ -235,8 +235,9 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus):
-    return {"workload": f"one Metis NVFP4 linear layer fwd+bwd, M={M_TOKENS} tokens per GPU, K={HIDDEN_K}, N={HIDDEN_N}, "
+def workload_config(n_gpus, n_layers=1):
+    what = "one Metis NVFP4 linear layer" if n_layers == 1 else f"{n_layers} stacked Metis NVFP4 linear layers"
+    return {"workload": f"{what} fwd+bwd, M={M_TOKENS} tokens per GPU, K={HIDDEN_K}, N={HIDDEN_N}, "
                         f"rank {RANK}, bf16, mean mode, RTN forward / stochastic-rounding backward",
             "tokens_per_gpu": M_TOKENS, "in_features": HIDDEN_K, "out_features": HIDDEN_N, "rank": RANK,
             "parallelism": f"dp{n_gpus} (tokens sharded, weights replicated" + (", NCCL all-reduce of weight grads)" if n_gpus > 1 else ")"),
@@ -465,6 +466,9 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
+    ap.add_argument("--layers", type=int, default=1,
+                    help="stack this many Metis layers (the headline is 1): with several GPUs the gradient all-reduce "
+                         "of layer k then runs beside the backward of layer k-1")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
@@ -520,12 +524,17 @@ def main():
     margs = MetisArgs(forward_svd_rank=RANK, activation_lowrank_svd=RANK, backward_lowrank_svd=RANK,
                       cache_quantized_weight=False)
     margs.device = dev
-    layer = BitLinear(HIDDEN_K, HIDDEN_N, args=margs, bias=False, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
-    with torch.no_grad():
-        layer.warmup_linear.weight.copy_(torch.randn(HIDDEN_N, HIDDEN_K, device=dev) / HIDDEN_K ** 0.5)
-    layer.layer_name = "bench.layer"
-    layer.split()                                  # exact SVD once, outside the timed region
-    params = [p for p in layer.parameters()]
+    n_layers = max(1, args.layers)
+    layers = []
+    for i in range(n_layers):
+        lyr = BitLinear(HIDDEN_K, HIDDEN_N, args=margs, bias=False, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+        with torch.no_grad():
+            lyr.warmup_linear.weight.copy_(torch.randn(HIDDEN_N, HIDDEN_K, device=dev) / HIDDEN_K ** 0.5)
+        lyr.layer_name = f"bench.layer{i}"
+        lyr.split()                                # exact SVD once, outside the timed region
+        layers.append(lyr)
+    layer = layers[0]
+    params = [p for lyr in layers for p in lyr.parameters()]
 
     g = torch.Generator(device="cpu").manual_seed(1 + rank)
     x_host = torch.randn(1, M_TOKENS, HIDDEN_K, generator=g).to(torch.bfloat16)
@@ -534,13 +543,15 @@ def main():
     x_host, g_host = x_host.pin_memory(), g_host.pin_memory()
     x_dev = x_host.to(dev).requires_grad_(True)
     g_dev = g_host.to(dev)
-    flops = layer_flops(M_TOKENS, HIDDEN_N, HIDDEN_K, RANK)
+    flops = n_layers * layer_flops(M_TOKENS, HIDDEN_N, HIDDEN_K, RANK)
 
     def step(x, grad):
         for p in params:
             p.grad = None
         x.grad = None
-        y = layer(x)
+        y = x
+        for lyr in layers:
+            y = lyr(y)
         y.backward(grad)
         return y
 
@@ -593,9 +604,10 @@ def main():
         # the same step with the opt-in packed-weight cache (weights that do not change between steps:
         # evaluation, rollout, frozen layers): their four quantizations leave the step
         def set_weight_cache(on):
-            for m in (layer.warmup_linear, layer.vlinear):
-                m.cache_quantized_weight = on
-                m._quantized_weight_cache = None
+            for lyr in layers:
+                for m in (lyr.warmup_linear, lyr.vlinear):
+                    m.cache_quantized_weight = on
+                    m._quantized_weight_cache = None
         set_weight_cache(True)
         for _ in range(2):
             step(x_dev, g_dev)
@@ -604,6 +616,17 @@ def main():
         cached()
         ms_cached = timed(cached, max(3, args.steps // 2))
         set_weight_cache(False)
+        # N > 1: the same step without the gradient all-reduce; the difference is what the collective costs the step
+        ms_local = None
+        if world > 1:
+            GradientReducer.detach()
+            for _ in range(2):
+                step(x_dev, g_dev)
+            local_graph = GraphedStep(lambda: step(x_dev, g_dev), warmup=1, pool=graphed.pool())
+            graphs.append(local_graph)
+            local_graph()
+            ms_local = timed(local_graph, max(3, args.steps // 2))
+            GradientReducer(overlap_sms=OVERLAP_SMS).attach()
         # and in the mode whose gradients meet the 1e-3 bar against the reference's own (the reference's
         # wiring: native quantizers, dequantized operands, torch.matmul), issued from Python
         ms_dense = None
@@ -706,6 +729,7 @@ def main():
                "kind": kind, "sample": f"{tokens} of {M_TOKENS} tokens, same N, K, r, fp32, 2 timed steps after 1 warm-up",
                "config1": cpu_c1_lines(kind, threads)}
 
+    grad_bytes = sum(p.numel() * p.element_size() for p in params)
     if rank == 0:
         fp4_peak = 4.0 * peaks["bf16_tflops"]
         achieved = gemm_flops / ms_gemm / 1e9
@@ -713,7 +737,7 @@ def main():
             "metric": METRIC, "value": world * flops / ms_step / 1e9, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate) + bf16 rank-r",
-            "data": "synthetic", "config": workload_config(world),
+            "data": "synthetic", "config": workload_config(world, n_layers),
             "e2e": {"value": world * flops / ms_e2e / 1e9, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": x_host.numel() * 2 + g_host.numel() * 2, "d2h_bytes_per_step": 8,
                     "ms_per_step": ms_e2e},
@@ -723,6 +747,10 @@ def main():
                                    "tests/test_layer_gpu.py)",
                           "dense_ms_per_step": ms_dense,
                           "dense": "reference wiring (fake-quantized operands, torch.matmul): gradients within 1e-3 of the reference's"},
+            "allreduce": None if ms_local is None else {
+                "ms_per_step_without": ms_local, "exposed_ms": ms_step - ms_local, "bytes_per_step": grad_bytes,
+                "bus_gbs_if_fully_exposed": 2 * (world - 1) / world * grad_bytes / max(ms_step - ms_local, 1e-6) / 1e6,
+                "dtype": "gradients travel in the parameters' dtype (bf16)"},
             "gpu_launches": launches, "launch_mode": "one CUDA graph per step" + (" (NCCL all-reduce of the weight gradients captured inside)" if world > 1 else ""), "ms_per_step_eager": ms_eager,
             "clocks": clock_summary,
             "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_pair_kernel (CTA pairs, 256x256 tiles) forward residual GEMM + fused rank-128 product",

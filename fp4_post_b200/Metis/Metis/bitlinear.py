@@ -52,6 +52,7 @@ class PackedOperand:
         self._dense = {}
         self.mean_event = None         # recorded when the column mean exists (before the quantization that uses it)
         self.fresh = True              # produced by kernels of the current call (cleared by a weight-cache hit)
+        self.ready_event = None        # quantized on the second stream: what the current stream waits for before its first use
 
     @property
     def dtype(self):
@@ -75,8 +76,8 @@ class PackedOperand:
         return self._dense[dtype]
 
 
-def _packed_matmul(a, b, rank1=(), lowrank=None, c=None, out_dtype=torch.bfloat16):
-    return ops.nvfp4_gemm(a, b, rank1=rank1, lowrank=lowrank, c=c, out_dtype=out_dtype)
+def _packed_matmul(a, b, rank1=(), lowrank=None, c=None, out_dtype=torch.bfloat16, sm_limit=0):
+    return ops.nvfp4_gemm(a, b, rank1=rank1, lowrank=lowrank, c=c, out_dtype=out_dtype, sm_limit=sm_limit)
 
 
 def _backward_can_pack(shared) -> bool:
@@ -529,7 +530,7 @@ def _row_sums(q):
     return cached
 
 
-def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, side=None, mean_row=None):
+def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, side=None, mean_row=None, sm_limit=0):
     """dX = D^ @ W^ on the FP4 GEMM (bitlinear.py:508): contraction over N, so A = Q(D) [M, N] and
     B = W quantized along N ([K, N], transposed quantizer), plus the row vector mu_D @ W^.
     `side` = (T, U, row_vec) adds a bf16 rank-r product T @ U^T (in this product's accumulator
@@ -545,7 +546,7 @@ def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, sid
         if extra is not None:
             row = extra if row is None else row + extra
     rank1 = [(None, row)] if row is not None else []
-    return _packed_matmul(da.q, w_t, rank1=rank1, lowrank=lowrank, c=addend, out_dtype=out_dtype)
+    return _packed_matmul(da.q, w_t, rank1=rank1, lowrank=lowrank, c=addend, out_dtype=out_dtype, sm_limit=sm_limit)
 
 
 def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int, out_dtype=torch.float32):
@@ -682,8 +683,10 @@ class MetisFusedFunction(torch.autograd.Function):
         if xa.mean is not None:
             # mu_x V^T and mu_x R^T need the mean only: on the second stream they run beside the
             # quantization of x instead of after it
-            # (only with weights from the cache: fresh ones are still being quantized on this stream)
-            overlap = MetisFusedFunction.concurrent_branches and not vq.fresh and not rq.fresh
+            # (weights from the cache, or quantized on the second stream itself: fresh ones made on this
+            # stream are still being quantized here)
+            beside = vq.ready_event is not None and rq.ready_event is not None
+            overlap = MetisFusedFunction.concurrent_branches and (beside or (not vq.fresh and not rq.fresh))
             with _beside(xa.mean_event if overlap else None, xa.mean.device) as join:
                 row_v = ops.nvfp4_gemv(vq.q, xa.mean)
                 # the product with V needs only this one: the pass over the (much larger) residual
@@ -700,6 +703,10 @@ class MetisFusedFunction(torch.autograd.Function):
             rank1_r.append((None, row_r))
         if bias is not None:
             rank1_r.append((None, bias.float()))
+        for op in (vq, rq):
+            if op.ready_event is not None:             # quantized on the second stream: order this stream after it, once
+                torch.cuda.current_stream(xa.q.device).wait_event(op.ready_event)
+                op.ready_event = None
         yv = _packed_matmul(xa.q, vq.q, rank1=rank1_v, out_dtype=act)                 # [M, r]
         # torch.mul(self.s, y), in the units the side product accumulates in: 1/(unit_x * unit_R)
         if act == torch.bfloat16:
@@ -800,7 +807,6 @@ class MetisFusedFunction(torch.autograd.Function):
             reducer.start_small()
         # with a gradient all-reduce in flight the input-gradient GEMM leaves it some SMs
         sm_limit = reducer.gemm_sm_limit(g.device) if reducer is not None else 0
-        saved_limit = ops.set_gemm_sm_limit(sm_limit) if sm_limit else 0
         if fuse_dx:
             # dX of both branches in ONE launch: D^v @ V^ enters the residual product as a bf16
             # rank-r side product.  e2m1 x e4m3 is exact in bf16; the ratio of the two products'
@@ -809,12 +815,10 @@ class MetisFusedFunction(torch.autograd.Function):
             u_side, extra = side
             ratio = (dv.q.unit * v_t.unit) / (dg.q.unit * r_t.unit)
             t_acc = ops.nvfp4_dequantize(dv.q, torch.bfloat16, add_mean=False, unit=ratio)
-            gx = _packed_dx(dg, rq, act, side=(t_acc, u_side, extra), mean_row=mean_row)
+            gx = _packed_dx(dg, rq, act, side=(t_acc, u_side, extra), mean_row=mean_row, sm_limit=sm_limit)
         else:
-            gx_v = _packed_dx(dv, vq, act)
-            gx = _packed_dx(dg, rq, act, addend=gx_v, mean_row=mean_row)          # summed in the epilogue
-        if sm_limit:
-            ops.set_gemm_sm_limit(saved_limit)
+            gx_v = _packed_dx(dv, vq, act, sm_limit=sm_limit)
+            gx = _packed_dx(dg, rq, act, addend=gx_v, mean_row=mean_row, sm_limit=sm_limit)          # summed in the epilogue
         grad_x = gx.reshape(xa.shape)
         if reducer is not None:
             reducer.flush()
@@ -944,6 +948,7 @@ class BitLinear(nn.Module):
         share_activation = (isinstance(self.vlinear, LinearLowbit) and isinstance(self.warmup_linear, LinearLowbit)
                             and self.args.forward_svd_rank > 0)
         if share_activation:
+            self._quantize_weights_beside(x)
             shared = self._get_shared_quantized_input(x)
             if isinstance(shared, PackedOperand):
                 fused = self._forward_packed(x, shared)
@@ -969,13 +974,46 @@ class BitLinear(nn.Module):
                 y = y + self.warmup_linear(x)
         return y
 
+    def _quantize_weights_beside(self, x):
+        """With the weight cache off (the reference's default) every forward quantizes V and R again.
+        That work does not depend on x: it is issued on the device's second stream, where it runs
+        beside the column mean and the quantization of the activation instead of after them.  The
+        operands remember the event the current stream has to wait for before it reads them."""
+        F = LinearLowbitFunction
+        self._prefetched = None
+        v, w = self.vlinear, self.warmup_linear
+        if not (MetisFusedFunction.concurrent_branches and x.is_cuda and v.weight.is_cuda
+                and F._use_packed(v.weight, F.q_forward_weight) and not F.enable_nv_recipe):
+            return
+        if v.cache_quantized_weight and w.cache_quantized_weight and v._quantized_weight_cache is not None \
+                and w._quantized_weight_cache is not None:
+            return                                        # (probably) cache hits: nothing to overlap
+        main, aux = torch.cuda.current_stream(x.device), _aux_stream(x.device)
+        aux.wait_stream(main)
+        with torch.cuda.stream(aux):
+            vq = v._get_quantized_weight(v.weight.to(v.compute_dtype))
+            rq = w._get_quantized_weight(w.weight.to(w.compute_dtype))
+            done = torch.cuda.Event()
+            done.record(aux)
+        for op in (vq, rq):
+            if isinstance(op, PackedOperand) and op.fresh:
+                op.ready_event = done
+                for q in (op.q, op._qt):
+                    if q is not None:
+                        q.codes.record_stream(main)      # one allocation holds codes, scales and unit
+        self._prefetched = (vq, rq)
+
     def _forward_packed(self, x, shared: PackedOperand):
         """Packed mode of the shared-activation branch: both weights as PackedOperand, one fused
         autograd node.  Also serves rollout (no merged bf16 weight is needed: the FP4 weights are
         a quarter of its bytes).  Returns None when a shape does not fit the FP4 GEMM."""
         v, w = self.vlinear, self.warmup_linear
-        vq = v._get_quantized_weight(v.weight.to(v.compute_dtype))
-        rq = w._get_quantized_weight(w.weight.to(w.compute_dtype))
+        if getattr(self, "_prefetched", None) is not None:
+            vq, rq = self._prefetched
+            self._prefetched = None
+        else:
+            vq = v._get_quantized_weight(v.weight.to(v.compute_dtype))
+            rq = w._get_quantized_weight(w.weight.to(w.compute_dtype))
         if not (isinstance(vq, PackedOperand) and isinstance(rq, PackedOperand)):
             return None
         M, K = shared.q.shape

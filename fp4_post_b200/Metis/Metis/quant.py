@@ -287,6 +287,17 @@ class _NativeNVFP4(BlockQuantFunc):
     def _native_input(cls, x: torch.Tensor) -> torch.Tensor:
         return x if x.dtype in (torch.bfloat16, torch.float32) else x.float()
 
+    @classmethod
+    def philox_key(cls) -> int:
+        """Philox key of the stochastic calls being issued now: the class seed and the random lane in the
+        low word, the data-parallel rank in the high word, so that ranks that quantize the same element
+        index with the same call number draw independent bits (the reference's ranks each have their own
+        torch generator stream)."""
+        rank = 0
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            rank = torch.distributed.get_rank()
+        return ((cls._seed + _NativeNVFP4._lane) & 0xFFFFFFFF) | (rank << 32)
+
     _counters = {}          # (device, lane) -> int64 [1]: the Philox offset of the next stochastic call
     _lane = 0               # random lane of the calls being issued now (see random_lane)
 
@@ -309,7 +320,7 @@ class _NativeNVFP4(BlockQuantFunc):
         transpose).  `mean` (fp32 [cols]) is subtracted first and recorded on the result."""
         cls._check(x)
         return ops.nvfp4_quantize(cls._native_input(x), transpose=transpose, stochastic=cls.stochastic,
-                                  seed=cls._seed + _NativeNVFP4._lane, sf_layout=sf_layout, mean=mean,
+                                  seed=cls.philox_key(), sf_layout=sf_layout, mean=mean,
                                   offset_counter=cls._offset_counter(x.device) if cls.stochastic else None)
 
     @classmethod
@@ -319,7 +330,7 @@ class _NativeNVFP4(BlockQuantFunc):
         step needs of every operand (the products of the backward contract over the other dimension)."""
         cls._check(x)
         return ops.nvfp4_quantize_dual(cls._native_input(x), stochastic=cls.stochastic,
-                                       seed=cls._seed + _NativeNVFP4._lane, sf_layout=sf_layout, mean=mean,
+                                       seed=cls.philox_key(), sf_layout=sf_layout, mean=mean,
                                        offset_counter=cls._offset_counter(x.device) if cls.stochastic else None)
 
     @classmethod

@@ -27,7 +27,7 @@ EXPORTS = (
     "metis_nvfp4_quantize_workspace_bytes", "metis_nvfp4_quantize", "metis_rmsnorm_nvfp4_quantize",
     "metis_nvfp4_dequantize", "metis_col_mean_workspace_bytes", "metis_col_mean", "metis_nvfp4_gemv",
     "metis_nvfp4_gemm", "metis_nvfp4_quantize_static", "metis_nvfp4_gemm_workspace_bytes",
-    "metis_lowrank_scale", "metis_set_gemm_sm_limit",
+    "metis_lowrank_scale",
     "metis_nvfp4_quantize_dual_workspace_bytes", "metis_nvfp4_quantize_dual",
     "metis_bf16_panel_gemm_workspace_bytes", "metis_bf16_panel_gemm",
     "metis_lowrank_dts_workspace_bytes", "metis_lowrank_dts", "metis_lowrank_du_workspace_bytes", "metis_lowrank_du",
@@ -50,6 +50,7 @@ class GemmArgs(C.Structure):
         ("d_dtype", C.c_int32), ("reserved", C.c_int32),
         ("status", C.c_void_p), ("stream", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+        ("sm_limit", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 
@@ -99,8 +100,6 @@ def lib() -> C.CDLL:
     L.metis_nvfp4_gemv.restype = i32
     L.metis_nvfp4_gemm.argtypes = [C.POINTER(GemmArgs)]
     L.metis_nvfp4_gemm.restype = i32
-    L.metis_set_gemm_sm_limit.argtypes = [i32]
-    L.metis_set_gemm_sm_limit.restype = i32
     L.metis_lowrank_scale.argtypes = [vp, i64, i64, i64, vp, i32, vp, vp, vp, vp]
     L.metis_lowrank_scale.restype = i32
     for name in ("metis_bf16_panel_gemm_workspace_bytes", "metis_lowrank_dts_workspace_bytes", "metis_lowrank_du_workspace_bytes"):

@@ -20,13 +20,10 @@ int32_t fail(int32_t code, const char* fmt, ...) {
 
 extern "C" const char* metis_last_error_string(void) { return metis::g_last_error; }
 
-static std::atomic<int32_t> g_gemm_sm_limit{0};
-
 namespace metis {
-// SMs the persistent GEMM kernels may take on the current device
-int gemm_sm_budget() {
+// SMs a launch of the persistent GEMM kernels may take on the current device: all, or the caller's limit
+int gemm_sm_budget(int32_t limit) {
   const int n = device_sm_count();
-  const int32_t limit = g_gemm_sm_limit.load(std::memory_order_relaxed);
   return (limit > 0 && limit < n) ? (int)limit : n;
 }
 // METIS_LAUNCH_OVERLAP in the environment: a mask of the LaunchClass bits that get programmatic-serialization launches
@@ -38,10 +35,6 @@ bool launch_overlap_enabled(int launch_class) {
   return (mask & launch_class) != 0;
 }
 }  // namespace metis
-
-extern "C" int32_t metis_set_gemm_sm_limit(int32_t sms) {
-  return g_gemm_sm_limit.exchange(sms < 0 ? 0 : sms, std::memory_order_relaxed);
-}
 
 extern "C" int32_t metis_query(int32_t* abi_version, int32_t* compiled_sm, int32_t* device_sm_count) {
   if (abi_version) *abi_version = METIS_NVFP4_ABI_VERSION;

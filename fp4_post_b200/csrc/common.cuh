@@ -45,7 +45,7 @@ int32_t check_quant_outputs(int64_t R, int64_t C, int32_t sf_layout, const void*
                             const void* scales, const void* unit, const void* workspace,
                             int64_t workspace_bytes);
 int device_sm_count();
-int gemm_sm_budget();          // device_sm_count() capped by metis_set_gemm_sm_limit
+int gemm_sm_budget(int32_t limit);   // device_sm_count(), capped by a positive per-call limit
 
 // ---- overlapped launches ------------------------------------------------------------------------
 // Every kernel of the library is launched with programmatic stream serialization: its CTAs may become

@@ -411,7 +411,7 @@ static int32_t launch_gemm(const metis_gemm_args* a, const CUtensorMap& ma, cons
   // per device and cheap, so it is simply repeated on every launch
   METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
   const int64_t work = ceil_div(a->M, kBM) * ceil_div(a->N, BN) * p.splits;
-  int64_t grid = gemm_sm_budget();
+  int64_t grid = gemm_sm_budget(a->sm_limit);
   if (grid > work) grid = work;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
   METIS_CUDA_OK(launch_overlapped(kLaunchGemm, kern, dim3((unsigned)grid), dim3(kGemmThreads), Cfg::kSmemBytes, st, ma, mb, mt, mu, p));
@@ -459,6 +459,7 @@ extern "C" int32_t metis_nvfp4_gemm(const metis_gemm_args* a) {
   }
   if ((a->cvec0 && !a->rvec0) || (a->cvec1 && !a->rvec1)) return fail(METIS_ERR_BAD_ARGUMENT, "a cvec needs its rvec");
   if (a->reserved & ~kDebugMask) return fail(METIS_ERR_BAD_ARGUMENT, "reserved must be 0");
+  if (a->sm_limit < 0 || a->reserved2 != 0) return fail(METIS_ERR_BAD_ARGUMENT, "sm_limit must not be negative and reserved2 must be 0");
 
   const int sms = device_sm_count();
   const int bn = tile_width(a->M, a->N, sms);

@@ -377,7 +377,7 @@ static int32_t launch_pair_t(const metis_gemm_args* a, const CUtensorMap* maps, 
   auto kern = nvfp4_gemm_pair_kernel<TD>;
   METIS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes));
   const int64_t tiles = ceil_div(a->M, 2 * kBM) * ceil_div(a->N, PairCfg::BN);
-  int64_t pairs = gemm_sm_budget() / 2;
+  int64_t pairs = gemm_sm_budget(a->sm_limit) / 2;
   if (pairs > tiles) pairs = tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);

@@ -270,12 +270,6 @@ def nvfp4_gemv(q: NVFP4Tensor, v: Optional[torch.Tensor] = None) -> torch.Tensor
     return out
 
 
-def set_gemm_sm_limit(sms: int) -> int:
-    """Cap the SMs the persistent GEMM kernels occupy (0: all); returns the previous cap.  Leaves room
-    for a collective's kernel that should run beside a GEMM."""
-    return int(cabi.lib().metis_set_gemm_sm_limit(int(sms)))
-
-
 def lowrank_scale(yv: torch.Tensor, s: torch.Tensor, unit_a: torch.Tensor, unit_b: torch.Tensor) -> torch.Tensor:
     """bf16( (yv * s).float() / (unit_a * unit_b) ) for bf16 yv [M, r]: torch.mul(self.s, y) of the
     low-rank branch, in the accumulator units of the GEMM whose side product it feeds (one kernel)."""
@@ -299,12 +293,13 @@ def lowrank_scale(yv: torch.Tensor, s: torch.Tensor, unit_a: torch.Tensor, unit_
 def nvfp4_gemm(a: NVFP4Tensor, b: NVFP4Tensor, *, lowrank=None, rank1=(), c: Optional[torch.Tensor] = None,
                out_dtype: torch.dtype = torch.bfloat16, alpha: float = 1.0,
                status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-               _debug: int = 0) -> torch.Tensor:
+               sm_limit: int = 0, _debug: int = 0) -> torch.Tensor:
     """D = alpha*ua*ub * (A @ B^T + T @ U^T) + sum_i cvec_i (x) rvec_i (+ c), see metis_nvfp4_gemm.
 
     a: [M, K], b: [N, K] (both METIS_SF_MMA).  lowrank = (T [M, r] bf16, U [N, r] bf16), already in
     accumulator units.  rank1 = up to two (cvec or None, rvec) pairs of fp32 vectors.
-    Only the packed parts of a and b enter the product; their mean vectors do not."""
+    Only the packed parts of a and b enter the product; their mean vectors do not.
+    sm_limit > 0 caps the SMs this launch occupies (room for a collective's kernel beside it)."""
     M, K = a.shape
     N, K2 = b.shape
     if K != K2:
@@ -352,6 +347,7 @@ def nvfp4_gemm(a: NVFP4Tensor, b: NVFP4Tensor, *, lowrank=None, rank1=(), c: Opt
         args.d, args.ldd = out.data_ptr(), out.stride(0)
         args.d_dtype = _DTYPES[out_dtype]
         args.reserved = int(_debug)
+        args.sm_limit = int(sm_limit)
         args.status = _ptr(status)
         args.stream = _stream()
         ws_bytes = cabi.lib().metis_nvfp4_gemm_workspace_bytes(M, N, K) if M <= 128 else 0

@@ -47,7 +47,7 @@
 extern "C" {
 #endif
 
-#define METIS_NVFP4_ABI_VERSION 1
+#define METIS_NVFP4_ABI_VERSION 2
 
 /* element types of dense operands */
 #define METIS_DTYPE_BF16 0
@@ -80,12 +80,6 @@ extern "C" {
 /* ABI version, compiled arch (100 for sm_100a), SM count of the current device (0 if no
  * device).  Any pointer may be NULL.  Replaces nothing in the reference. */
 int32_t metis_query(int32_t* abi_version, int32_t* compiled_sm, int32_t* device_sm_count);
-
-/* Upper bound on the SMs the persistent GEMM kernels occupy (0, the default: all of them).
- * A data-parallel step that overlaps a collective with a GEMM leaves the collective's kernel
- * some SMs this way.  Process-wide; returns the previous value.  Replaces nothing in the
- * reference. */
-int32_t metis_set_gemm_sm_limit(int32_t sms);
 
 /* Thread-local text for the last non-zero status returned to this thread. */
 const char* metis_last_error_string(void);
@@ -279,6 +273,11 @@ typedef struct metis_gemm_args {
   void* stream;
   void* workspace;          /* optional scratch, 16-byte aligned: metis_nvfp4_gemm_workspace_bytes */
   int64_t workspace_bytes;
+  int32_t sm_limit;         /* upper bound on the SMs this launch's persistent CTAs occupy; 0: all of them.  A
+                               data-parallel step that runs a collective beside this product leaves the
+                               collective's kernel its SMs this way.  Per call: launches on other streams and
+                               threads are not affected. */
+  int32_t reserved2;        /* 0 */
 } metis_gemm_args;
 
 int32_t metis_nvfp4_gemm(const metis_gemm_args* args);

@@ -34,7 +34,7 @@ def test_symbol_is_exported(L, name):
 def test_query_reports_abi_and_arch(L):
     abi, sm, n = C.c_int32(), C.c_int32(), C.c_int32(-1)
     assert L.metis_query(C.byref(abi), C.byref(sm), C.byref(n)) == 0
-    assert abi.value == 1 and sm.value == 100 and n.value >= 0
+    assert abi.value == 2 and sm.value == 100 and n.value >= 0      # version 2: per-call sm_limit in metis_gemm_args
 
 
 def test_size_helpers(L):
@@ -47,13 +47,17 @@ def test_size_helpers(L):
     assert L.metis_col_mean_workspace_bytes(1000, 64) == 8 * 64 * 4
 
 
-def test_gemm_sm_limit_is_a_process_wide_setting_that_returns_the_previous_value(L):
-    assert L.metis_set_gemm_sm_limit(116) == 0
-    assert L.metis_set_gemm_sm_limit(-5) == 116          # negative: no cap
-    assert L.metis_set_gemm_sm_limit(0) == 0
-    # split-K scratch: only for a single row block of A with few column tiles and a long K
-    assert L.metis_nvfp4_gemm_workspace_bytes(4096, 4096, 4096) == 0
-    assert L.metis_nvfp4_gemm_workspace_bytes(16, 64, 64) == 0
+def test_gemm_rejects_a_negative_sm_limit(L):
+    from fp4_post_b200 import cabi
+    buf = (C.c_uint8 * 1024)()
+    p = C.addressof(buf)
+    p += (-p) % 256
+    a = cabi.GemmArgs()
+    a.M, a.N, a.K = 256, 256, 256
+    for f in ("a_codes", "a_scales", "a_unit", "b_codes", "b_scales", "b_unit", "d"):
+        setattr(a, f, p)
+    a.ldd, a.d_dtype, a.alpha, a.sm_limit = 256, cabi.DTYPE_BF16, 1.0, -3
+    assert L.metis_nvfp4_gemm(C.byref(a)) == -1 and b"sm_limit" in L.metis_last_error_string()
 
 
 def test_quantize_rejects_bad_arguments_without_a_device(L):

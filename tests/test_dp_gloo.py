@@ -92,8 +92,15 @@ def _reducer_worker(rank, world, port, out):
             red.ready(t)
         red.ready(None)                                           # an absent gradient (no bias) is skipped
         red.flush()
+        # every rank draws its stochastic-rounding bits from its own Philox key
+        from fp4_post_b200.Metis.Metis.quant import Cast2NVFp4e2m1Block, random_lane
+        keys = torch.tensor([Cast2NVFp4e2m1Block.philox_key()], dtype=torch.int64)
+        with random_lane(1):
+            keys = torch.cat([keys, torch.tensor([Cast2NVFp4e2m1Block.philox_key()], dtype=torch.int64)])
+        gathered = [torch.zeros_like(keys) for _ in range(world)]
+        dist.all_gather(gathered, keys)
         if rank == 0:
-            out.put((big.clone(), [t.clone() for t in small], red.bytes_reduced))
+            out.put((big.clone(), [t.clone() for t in small], red.bytes_reduced, torch.stack(gathered)))
     finally:
         dist.destroy_process_group()
 
@@ -105,10 +112,11 @@ def test_gradient_reducer_sums_large_tensors_in_place_and_small_ones_in_one_buck
     procs = [ctx.Process(target=_reducer_worker, args=(r, 2, port, out)) for r in range(2)]
     for p in procs:
         p.start()
-    big, small, nbytes = out.get(timeout=120)
+    big, small, nbytes, keys = out.get(timeout=120)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
+    assert keys.unique().numel() == 4                 # 2 ranks x 2 random lanes: four different Philox keys
     assert torch.equal(big, torch.full((64, 64), 3.0))
     assert torch.equal(small[0], torch.full((5,), 3.0)) and torch.equal(small[1], torch.full((3, 2), 30.0))
     assert nbytes == (64 * 64 + 5 + 6) * 4
