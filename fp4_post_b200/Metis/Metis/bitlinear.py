@@ -549,7 +549,7 @@ def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, sid
     return _packed_matmul(da.q, w_t, rank1=rank1, lowrank=lowrank, c=addend, out_dtype=out_dtype, sm_limit=sm_limit)
 
 
-def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int, out_dtype=torch.float32):
+def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int, out_dtype=torch.float32, sm_limit=0):
     """dW = D^T @ x^ on the FP4 GEMM (bitlinear.py:502-505), fp32 unless told otherwise: contraction over tokens, so
     A = Q(D)^T [N, M] and B = Q(x)^T [K, M], both from the transposed quantizer, plus the two
     rank-1 terms of  dW = Qd^T Qx + (Qd^T 1) mu_x^T + mu_D (Qx^T 1 + M mu_x)^T."""
@@ -564,7 +564,7 @@ def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int, out_dtype=torch.flo
         if mu_x is not None:
             tail = tail + float(M) * mu_x
         rank1.append((mu_d, tail))
-    return _packed_matmul(d_t, x_t, rank1=rank1, out_dtype=out_dtype)
+    return _packed_matmul(d_t, x_t, rank1=rank1, out_dtype=out_dtype, sm_limit=sm_limit)
 
 
 def _grad_dtype(param: torch.Tensor):
@@ -720,7 +720,8 @@ class MetisFusedFunction(torch.autograd.Function):
         ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
         ctx.has_bias = bias is not None
         ctx.dims = (M, N, K)
-        ctx.v_weight, ctx.r_weight = v_weight, r_weight        # for their dtypes only
+        ctx.v_weight, ctx.r_weight = v_weight, r_weight        # for their dtypes, and for a reducer that fills .grad itself
+        ctx.s_param, ctx.u_param = s, u_weight
         ctx.save_for_backward(yv, s, u_weight)
         return y.reshape(*xa.shape[:-1], N).to(xa.dtype)
 
@@ -738,6 +739,8 @@ class MetisFusedFunction(torch.autograd.Function):
         centred = F._backward_centred()
         quantizer = F.q_backward_outputgrad
         reducer = GRADIENT_REDUCER
+        # a collective of a layer further up may still be running: leave its kernel some SMs
+        busy_limit = reducer.gemm_sm_limit(g.device) if reducer is not None and reducer.pending() else 0
 
         fuse_dx = MetisFusedFunction.fuse_dx_side_product and act == torch.bfloat16 and r <= 256
 
@@ -766,13 +769,16 @@ class MetisFusedFunction(torch.autograd.Function):
                 v_t = vq.transposed()
                 u_side = ops.nvfp4_dequantize(v_t, torch.bfloat16, add_mean=False, unit=_one(v_t.unit))
                 side = (u_side, ops.nvfp4_gemv(v_t, dv.mean) if dv.mean is not None else None)
-            return grad_u, grad_s, dv, _packed_dw(dv, xa, M, _grad_dtype(v_weight)), side
+            return grad_u, grad_s, dv, _packed_dw(dv, xa, M, _grad_dtype(v_weight), sm_limit=busy_limit), side
 
         def residual_weight_gradient(dg):
             # warmup_linear (the residual): quantized backward with grad_output = g
-            grad_r = _packed_dw(dg, xa, M, _grad_dtype(r_weight))
+            grad_r = _packed_dw(dg, xa, M, _grad_dtype(r_weight), sm_limit=busy_limit)
             if reducer is not None:
-                reducer.ready(grad_r)       # the big all-reduce starts here and runs beside the dX product
+                if reducer.across_layers:
+                    reducer.adopt(r_weight, grad_r)
+                else:
+                    reducer.ready(grad_r)   # the big all-reduce starts here and runs beside the dX product
             return grad_r
 
         mean_row = None
@@ -802,8 +808,13 @@ class MetisFusedFunction(torch.autograd.Function):
             grad_r = residual_weight_gradient(dg)
         if reducer is not None:
             # the small gradients are final too: their bucket goes out before the input-gradient GEMM
-            for t in (grad_v, grad_s, grad_u, grad_bias):
-                reducer.ready(t)
+            if reducer.across_layers:
+                for prm, t in ((v_weight, grad_v), (ctx.s_param, grad_s), (ctx.u_param, grad_u)):
+                    reducer.adopt(prm, t)
+                reducer.ready(grad_bias)
+            else:
+                for t in (grad_v, grad_s, grad_u, grad_bias):
+                    reducer.ready(t)
             reducer.start_small()
         # with a gradient all-reduce in flight the input-gradient GEMM leaves it some SMs
         sm_limit = reducer.gemm_sm_limit(g.device) if reducer is not None else 0
@@ -820,6 +831,10 @@ class MetisFusedFunction(torch.autograd.Function):
             gx_v = _packed_dx(dv, vq, act, sm_limit=sm_limit)
             gx = _packed_dx(dg, rq, act, addend=gx_v, mean_row=mean_row, sm_limit=sm_limit)          # summed in the epilogue
         grad_x = gx.reshape(xa.shape)
+        if reducer is not None and reducer.across_layers and reducer.active():
+            # the gradients sit in .grad already; the wait for their collectives moves to the end of the pass
+            reducer.finish_at_end_of_backward()
+            return grad_x, None, None, None, None, None, None, None, grad_bias
         if reducer is not None:
             reducer.flush()
         return grad_x, None, grad_v, None, grad_s, grad_u, grad_r, None, grad_bias

@@ -36,13 +36,50 @@ class GradientReducer:
     autograd never sees a gradient that is still being reduced."""
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, average: bool = False, small_bytes: int = 8 << 20,
-                 overlap_sms: int = 0):
+                 overlap_sms: int = 0, across_layers: bool = False):
         self.group, self.average, self.small_bytes = group, average, small_bytes
-        self.overlap_sms = overlap_sms        # SMs the input-gradient GEMM leaves to the collective that runs beside it
+        self.overlap_sms = overlap_sms        # SMs the GEMMs leave to a collective that runs beside them
+        # across_layers: the fused backward stores the weight gradients in .grad itself (autograd gets None for
+        # them, so nothing copies a tensor whose all-reduce is still in flight) and the wait moves to the end
+        # of the whole backward pass: the collective of layer k then runs beside the backward of layer k-1
+        self.across_layers = across_layers
         self._work, self._small, self._buckets, self.bytes_reduced = [], [], [], 0
+        self._deferred = False
+
+    def pending(self) -> bool:
+        """A collective started by this reducer may still be running."""
+        return bool(self._work or self._buckets)
+
+    def adopt(self, param: torch.nn.Parameter, grad: Optional[torch.Tensor]) -> None:
+        """across_layers mode: `grad` becomes (or is added to) param.grad and its all-reduce starts (large) or is
+        remembered for the bucket (small).  The caller returns None to autograd for this parameter."""
+        if grad is None:
+            return
+        grad = grad.to(param.dtype) if grad.dtype != param.dtype else grad
+        if param.grad is None:
+            param.grad = grad
+            self.ready(grad)
+        else:                                  # gradient accumulation: reduce the new part, then add
+            self.ready(grad)
+            self._accumulate = getattr(self, "_accumulate", [])
+            self._accumulate.append((param, grad))
+
+    def finish_at_end_of_backward(self) -> None:
+        """Ask the autograd engine to call flush() when the backward pass that is running has finished."""
+        if self._deferred or not self.active():
+            return
+        self._deferred = True
+
+        def done():
+            self._deferred = False
+            self.flush()
+            for param, grad in getattr(self, "_accumulate", []):
+                param.grad.add_(grad)
+            self._accumulate = []
+        torch.autograd.Variable._execution_engine.queue_callback(done)
 
     def gemm_sm_limit(self, device) -> int:
-        """SM budget of the GEMM that overlaps the big all-reduce (0: no cap).  The persistent GEMM
+        """SM budget of a GEMM that overlaps an all-reduce (0: no cap).  The persistent GEMM
         kernels otherwise hold every SM and the collective's kernel would wait for them to finish."""
         if self.overlap_sms <= 0 or not self.active():
             return 0

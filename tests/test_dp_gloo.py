@@ -137,3 +137,60 @@ def test_sharding_covers_the_batch_once_and_allreduce_is_a_noop_without_a_group(
     parts = [shard_tokens(x, r, 3) for r in range(3)]
     assert torch.equal(torch.cat(parts), x) and [p.shape[0] for p in parts] == [2, 2, 3]
     assert allreduce_gradients([torch.nn.Parameter(torch.zeros(2))]) == 0
+
+
+class _Adopting(torch.autograd.Function):
+    """y = x * w whose backward hands w's gradient to the reducer instead of to autograd (what the fused
+    Metis backward does with GradientReducer(across_layers=True))."""
+
+    @staticmethod
+    def forward(ctx, x, w, reducer):
+        ctx.save_for_backward(x, w)
+        ctx.w_param, ctx.reducer = w, reducer
+        return x * w
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        ctx.reducer.adopt(ctx.w_param, (gy * x).sum(0))
+        ctx.reducer.finish_at_end_of_backward()
+        return gy * w, None, None
+
+
+def _across_layers_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fp4_post_b200.dp import GradientReducer
+        red = GradientReducer(small_bytes=64, across_layers=True)
+        w1 = torch.nn.Parameter(torch.full((32,), 2.0))          # 128 bytes: its own collective
+        w2 = torch.nn.Parameter(torch.full((4,), 3.0))           # 16 bytes: the flat bucket
+        x = torch.full((3, 32), float(rank + 1), requires_grad=True)
+        h = _Adopting.apply(x, w1, red)                           # two "layers": both collectives are waited for once,
+        y = _Adopting.apply(h[:, :4], w2, red)                    # after the whole backward pass
+        assert not red.pending()
+        y.sum().backward()
+        assert not red.pending() and x.grad is not None
+        if rank == 0:
+            out.put((w1.grad.clone(), w2.grad.clone()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reducer_across_layers_fills_grad_itself_and_waits_once_at_the_end_of_backward():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_across_layers_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    g1, g2 = out.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    # rank r: x = r + 1; dw2 = sum over 3 rows of h = 3 * 2 (r+1) -> summed over ranks 6 * (1 + 2) = 18
+    assert torch.equal(g2, torch.full((4,), 18.0))
+    # dw1 = sum over rows of gy1 * x with gy1 = w2 on the first 4 columns (0 elsewhere): 3 * 3 * (r+1) -> 27
+    want = torch.zeros(32)
+    want[:4] = 27.0
+    assert torch.equal(g1, want)
