@@ -414,6 +414,131 @@ def run_gemm_yardstick(args):
         print(json.dumps(line), flush=True)
 
 
+def run_decoder_step(args):
+    """`--only c4` / `--only c5_update`: one training step (forward, next-token loss, backward) of a Qwen2-style
+    decoder with random weights whose seven projections per block are Metis rank-r NVFP4 layers, on synthetic
+    token ids; data-parallel over the ranks of the job (tokens sharded, NCCL all-reduce of every gradient).
+    c4: 1.5B shape, rank 64, batch 8 x 1024 per job.  c5_update: 7B shape, rank 128, 2 x 768 per GPU (a slice of
+    the policy update of the rollout configuration).  One JSON line: tokens/s, the Metis layers' algorithmic
+    TFLOP/s over the whole step time, and the share of device time spent in this library's kernels.
+    The rank-r factors come from a randomized SVD instead of the exact one (196 exact SVDs take minutes):
+    same shapes, same work per step."""
+    import torch
+    import torch.distributed as dist
+    import fp4_post_b200
+    from fp4_post_b200 import cabi, ops
+    from fp4_post_b200.decoder import QWEN2_1P5B, QWEN2_7B, Decoder
+    from fp4_post_b200.dp import GradientReducer, allreduce_gradients
+    from fp4_post_b200.graphs import GraphedStep
+    from fp4_post_b200.grpo.grpo import MetisArgs, replace_linear_with_metis
+    from fp4_post_b200.Metis.Metis.bitlinear import BitLinear
+
+    cabi.lib()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("NCCL_MAX_CTAS", str(OVERLAP_SMS))
+        os.environ.setdefault("METIS_LAUNCH_OVERLAP", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    if args.only == "c4":
+        cfg, r, batch, seq = QWEN2_1P5B, 64, max(1, 8 // world), 1024
+    else:
+        cfg, r, batch, seq = QWEN2_7B, 128, 2, 768
+    if args.layers > 1 or args.layers_set:
+        cfg = type(cfg)(**{**cfg.__dict__, "layers": args.layers})          # a shallower stack for quick runs
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = Decoder(cfg, fuse_norms=not args.no_fused_norm).to(torch.bfloat16)
+    margs = MetisArgs(forward_svd_rank=r, activation_lowrank_svd=r, backward_lowrank_svd=r)
+    margs.device = dev
+    exact_svd = torch.linalg.svd
+
+    def quick_svd(w, full_matrices=False):
+        # randomized range finder, then the exact SVD of the small projected matrix
+        omega = torch.randn(w.shape[1], r + 8, device=w.device, dtype=w.dtype)
+        q, _ = torch.linalg.qr(w @ omega)
+        ub, sv, vh = exact_svd(q.T @ w, full_matrices=False)
+        return q @ ub, sv, vh
+    torch.linalg.svd = quick_svd
+    try:
+        replace_linear_with_metis(model, dtype=torch.bfloat16, metis_args=margs, compute_dtype=torch.bfloat16)
+    finally:
+        torch.linalg.svd = exact_svd
+    params = list(model.parameters())
+    metis_params = {id(p) for m in model.modules() if isinstance(m, BitLinear) for p in m.parameters()}
+    other = [p for p in params if id(p) not in metis_params]
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    ids = torch.randint(0, cfg.vocab, (batch, seq), device=dev, generator=g)
+    if world > 1:
+        GradientReducer(overlap_sms=OVERLAP_SMS, across_layers=True).attach()
+
+    def step():
+        for p in params:
+            p.grad = None
+        loss = model.loss(ids)
+        loss.backward()
+        if world > 1:
+            allreduce_gradients(other)              # norms, embedding, lm_head: what the fused backward does not see
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        step()
+    barrier()
+    mode = "eager"
+    runner = step
+    if not args.no_graph:
+        try:
+            runner = GraphedStep(step, warmup=1)
+            runner()
+            mode = "one CUDA graph per step"
+        except Exception as exc:                    # capture is an optimisation: say why it was not taken
+            mode = f"eager (capture failed: {type(exc).__name__}: {str(exc)[:120]})"
+            runner = step
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        runner()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    # share of device time in this library's kernels: one profiled eager step
+    share = None
+    if rank == 0:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        ours = sum(e.device_time_total for e in prof.key_averages() if e.key.startswith(("void metis::", "metis::")))
+        total = sum(e.device_time_total for e in prof.key_averages())
+        share = ours / max(total, 1e-9)
+    if rank == 0:
+        tokens = world * batch * seq
+        lin = 3 * cfg.linear_flops_per_token(r) * tokens
+        print(json.dumps({"only": args.only, "n_gpus": world, "tokens_per_step": tokens, "batch_per_gpu": batch, "seq_len": seq,
+                          "layers": cfg.layers, "hidden": cfg.hidden, "rank": r, "ms_per_step": ms,
+                          "tokens_per_s": tokens / ms * 1e3, "metis_linear_tflops": lin / ms / 1e9,
+                          "share_of_device_time_in_library_kernels": share, "launch_mode": mode,
+                          "fused_norms": not args.no_fused_norm, "data": "synthetic token ids, random weights"}), flush=True)
+    if world > 1:
+        if isinstance(runner, GraphedStep):
+            runner.release()
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
+
+
 def run_single_kernel(args):
     """`--only K`: a few launches of one kernel on [rows, cols] bf16 (GEMM: M = rows, K = cols, N = n),
     timed with CUDA events.  Small enough to sit under an ncu capture."""
@@ -464,16 +589,21 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer", "c4", "c5_update"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--layers", type=int, default=1,
                     help="stack this many Metis layers (the headline is 1): with several GPUs the gradient all-reduce "
                          "of layer k then runs beside the backward of layer k-1")
+    ap.add_argument("--no-graph", action="store_true", help="decoder steps: issue from Python instead of one CUDA graph")
+    ap.add_argument("--no-fused-norm", action="store_true", help="decoder steps: plain RMSNorm modules instead of the fused norm -> quantizer entry")
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--rank", type=int, default=128)
     args = ap.parse_args()
+    args.layers_set = "--layers" in sys.argv
+    if args.only in ("c4", "c5_update"):
+        return run_decoder_step(args)
     if args.impl == "reference":
         return run_reference_arm(args)
     if args.only == "gemm_sweep":

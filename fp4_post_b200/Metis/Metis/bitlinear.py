@@ -309,16 +309,18 @@ class LinearLowbitFunction(torch.autograd.Function):
                 and not F.tp_simulate and tensor.shape[-1] % 16 == 0)
 
     @staticmethod
-    def _pack_centred(tensor, quantizer, centred: bool, mean_cache=None, cache_key="default", both=False):
+    def _pack_centred(tensor, quantizer, centred: bool, mean_cache=None, cache_key="default", both=False,
+                      fresh_mean=None):
         """NVFP4 of `tensor` ([..., C] viewed as rows), optionally after subtracting the column
         mean (rolling at decode).  The native counterpart of svd_quant(metis_mode="mean").
         `both`: the transposed quantization (needed by the backward products) comes out of the same
-        pass over the tensor, where both dimensions are multiples of 16."""
+        pass over the tensor, where both dimensions are multiples of 16.  `fresh_mean`: the column
+        mean of `tensor` when its producer computed it already (the fused RMSNorm does)."""
         flat = tensor.reshape(-1, tensor.shape[-1])
         mean = None
         if centred:
             seq_len = tensor.shape[1] if tensor.dim() == 3 else tensor.shape[0]
-            fresh = ops.col_mean(flat)
+            fresh = ops.col_mean(flat) if fresh_mean is None else fresh_mean
             rows = flat.shape[0]
             if seq_len == 1 and mean_cache is not None and cache_key in mean_cache:
                 old, count = mean_cache[cache_key]

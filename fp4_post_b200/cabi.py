@@ -29,6 +29,7 @@ EXPORTS = (
     "metis_nvfp4_gemm", "metis_nvfp4_quantize_static", "metis_nvfp4_gemm_workspace_bytes",
     "metis_lowrank_scale",
     "metis_nvfp4_quantize_dual_workspace_bytes", "metis_nvfp4_quantize_dual",
+    "metis_rmsnorm_mean_workspace_bytes", "metis_rmsnorm_mean",
     "metis_bf16_panel_gemm_workspace_bytes", "metis_bf16_panel_gemm",
     "metis_lowrank_dts_workspace_bytes", "metis_lowrank_dts", "metis_lowrank_du_workspace_bytes", "metis_lowrank_du",
 )
@@ -90,6 +91,10 @@ def lib() -> C.CDLL:
     L.metis_nvfp4_quantize_static.restype = i32
     L.metis_rmsnorm_nvfp4_quantize.argtypes = [vp, i32, i64, i64, i64, vp, i32, f32, i32, vp, vp, vp, vp, vp, i64, vp]
     L.metis_rmsnorm_nvfp4_quantize.restype = i32
+    L.metis_rmsnorm_mean_workspace_bytes.argtypes = [i64, i64]
+    L.metis_rmsnorm_mean_workspace_bytes.restype = i64
+    L.metis_rmsnorm_mean.argtypes = [vp, i32, i64, i64, i64, vp, i32, f32, vp, vp, vp, vp, i64, vp]
+    L.metis_rmsnorm_mean.restype = i32
     L.metis_nvfp4_dequantize.argtypes = [vp, vp, vp, i32, i64, i64, vp, vp, i32, i64, vp]
     L.metis_nvfp4_dequantize.restype = i32
     L.metis_col_mean_workspace_bytes.argtypes = [i64, i64]

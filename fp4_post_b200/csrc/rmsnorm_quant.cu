@@ -418,6 +418,155 @@ static int32_t dispatch_chunks(const TX* x, int64_t rows, int64_t cols, int64_t 
   return METIS_OK;
 }
 
+// ---- RMSNorm with the column sums of its output (the mean-centred path) ------------------------------------
+// The mean-centred quantizer (bitlinear.py:326-332) needs the column mean of the NORMALISED activation before
+// it can quantize anything, so normalisation and quantization cannot share one pass.  This kernel is the first
+// of the two: it reads x once, writes y = norm(x) * gamma (the reference's roundings, llama.py:23-31), the
+// reciprocal RMS of every row (what a backward pass needs) and, per resident row slot, the sums of the y it
+// produced for every column; col_mean_finish_kernel adds those in a fixed order.  The quantizer then reads y
+// once for both orientations.  Same thread layout as rmsnorm_quantize_kernel: a thread keeps its column blocks
+// for all the rows it sees, so the sums stay in registers.
+template <typename TX, typename TG, int kBlocks>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_colsum_kernel(const TX* __restrict__ x, int rows, int blocks_per_row, int64_t ld, const TG* __restrict__ gamma,
+                      float eps, void* __restrict__ norm_out, float* __restrict__ rstd_out, float* __restrict__ partial) {
+  grid_dependency_wait();
+  constexpr bool kProductBf16 = (sizeof(TX) == 2) && (sizeof(TG) == 2);
+  __shared__ float s_red[kNormThreads / 32];
+  __shared__ float s_rs[kNormThreads / 32];
+  const int bx = blockDim.x, by = blockDim.y;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int tid = ty * bx + tx;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int seg = bx < 32 ? bx : 32;
+  const int warps_per_row = bx >> 5;
+  const float n_cols = (float)(blocks_per_row * 16);
+  float csum[kBlocks][16];
+#pragma unroll
+  for (int j = 0; j < kBlocks; ++j)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) csum[j][i] = 0.0f;
+
+  RawBlock<TX> raw[kBlocks];
+  auto fetch = [&](int r_first) {
+    const int r = r_first + ty;
+#pragma unroll
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (r < rows && bc < blocks_per_row) raw[j].load(x + (int64_t)r * ld + (int64_t)bc * 16);
+    }
+  };
+  fetch(blockIdx.x * by);
+  for (int r0 = blockIdx.x * by; r0 < rows; r0 += gridDim.x * by) {
+    const int r = r0 + ty;
+    const bool row_live = r < rows;
+    float v[kBlocks][16];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (row_live && bc < blocks_per_row) {
+        raw[j].unpack(v[j]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ss = __fmaf_rn(v[j][i], v[j][i], ss);
+      }
+    }
+    fetch(r0 + gridDim.x * by);
+    for (int o = seg >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    float rs;
+    if (warps_per_row > 1) {
+      if (lane == 0) s_red[warp] = ss;
+      __syncthreads();
+      if (tx == 0) {
+        float tot = 0.0f;
+        for (int w = 0; w < warps_per_row; ++w) tot += s_red[ty * warps_per_row + w];
+        s_rs[ty] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, n_cols), eps)));
+      }
+      __syncthreads();
+      rs = s_rs[ty];
+    } else {
+      rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, n_cols), eps)));
+    }
+    if (row_live && tx == 0 && rstd_out) rstd_out[r] = rs;
+#pragma unroll
+    for (int j = 0; j < kBlocks; ++j) {
+      const int bc = tx + j * bx;
+      if (!(row_live && bc < blocks_per_row)) continue;
+      float y[16];
+      norm_block<TX, TG>(v[j], rs, gamma + (int64_t)bc * 16, y);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) csum[j][i] += y[i];
+      const int64_t b = (int64_t)r * blocks_per_row + bc;
+      if (kProductBf16) {
+        __nv_bfloat162 o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);   // exact: already bf16 values
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(norm_out) + b * 16);
+        dst[0] = reinterpret_cast<uint4*>(o)[0];
+        dst[1] = reinterpret_cast<uint4*>(o)[1];
+      } else {
+        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(norm_out) + b * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
+      }
+    }
+  }
+  // this row slot's sums: partial[slot][cols], slot = blockIdx.x * by + ty
+  float* dst = partial + ((int64_t)blockIdx.x * by + ty) * (int64_t)blocks_per_row * 16;
+#pragma unroll
+  for (int j = 0; j < kBlocks; ++j) {
+    const int bc = tx + j * bx;
+    if (bc >= blocks_per_row) continue;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      reinterpret_cast<float4*>(dst + (int64_t)bc * 16)[i] = make_float4(csum[j][4 * i], csum[j][4 * i + 1], csum[j][4 * i + 2], csum[j][4 * i + 3]);
+  }
+}
+
+__global__ void rmsnorm_mean_finish_kernel(const float* __restrict__ partial, int64_t slots, int64_t rows, int64_t cols,
+                                           float* __restrict__ mean) {
+  grid_dependency_wait();
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float sum = 0.0f;
+  for (int64_t s = 0; s < slots; ++s) sum += partial[s * cols + c];        // fixed order
+  mean[c] = __fdiv_rn(sum, (float)rows);
+}
+
+struct NormShape { int bx, by, per_thread; };
+static NormShape norm_shape(int bpr) {
+  int bx = 1;
+  if (bpr >= 32) {
+    bx = ((bpr + 31) / 32) * 32;
+    if (bx > kNormThreads) bx = kNormThreads;
+  } else {
+    while (bx < bpr) bx <<= 1;
+  }
+  return {bx, kNormThreads / bx, (bpr + bx - 1) / bx};
+}
+// row slots (CTAs x rows in flight per CTA) the kernel above runs with: two CTAs per SM
+static int64_t colsum_ctas(int64_t rows, int by) {
+  int64_t blocks = (int64_t)device_sm_count() * 2;
+  const int64_t need = ceil_div(rows, by);
+  return blocks > need ? need : blocks;
+}
+
+template <typename TX, typename TG>
+static int32_t launch_colsum(const TX* x, int64_t rows, int64_t cols, int64_t ld, const TG* gamma, float eps, void* norm_out,
+                             float* rstd, float* partial, cudaStream_t st) {
+  const int bpr = (int)(cols >> 4);
+  const NormShape sh = norm_shape(bpr);
+  const dim3 g((unsigned)colsum_ctas(rows, sh.by)), b((unsigned)sh.bx, (unsigned)sh.by);
+#define METIS_COLSUM(KB) METIS_CUDA_OK(launch_overlapped(kLaunchStream, rmsnorm_colsum_kernel<TX, TG, KB>, g, b, 0, st, x, (int)rows, bpr, ld, gamma, eps, norm_out, rstd, partial))
+  if (sh.per_thread <= 1) METIS_COLSUM(1);
+  else if (sh.per_thread <= 2) METIS_COLSUM(2);
+  else if (sh.per_thread <= 3) METIS_COLSUM(3);
+  else if (sh.per_thread <= 5) METIS_COLSUM(5);
+  else return fail(METIS_ERR_TOO_LARGE, "rmsnorm rows longer than %d elements are not supported here", 5 * kNormThreads * 16);
+#undef METIS_COLSUM
+  return METIS_OK;
+}
+
 }  // namespace metis
 
 using namespace metis;
@@ -464,4 +613,41 @@ extern "C" int32_t metis_rmsnorm_nvfp4_quantize(const void* x, int32_t x_dtype, 
   if (rc) return rc;
   METIS_CUDA_OK(cudaGetLastError());
   return launch_finalize(ws, rows, cols, sf_layout, scales, unit, st);
+}
+
+
+extern "C" int64_t metis_rmsnorm_mean_workspace_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0 || cols % 16 != 0) return 0;
+  const NormShape sh = norm_shape((int)(cols >> 4));
+  return colsum_ctas(rows, sh.by) * sh.by * cols * (int64_t)sizeof(float);
+}
+
+extern "C" int32_t metis_rmsnorm_mean(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                                      const void* gamma, int32_t gamma_dtype, float eps, void* norm_out, float* rstd,
+                                      float* mean, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!x || !gamma || !norm_out || !mean || !workspace) return fail(METIS_ERR_BAD_ARGUMENT, "null pointer");
+  if ((x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) || (gamma_dtype != METIS_DTYPE_BF16 && gamma_dtype != METIS_DTYPE_F32))
+    return fail(METIS_ERR_BAD_ARGUMENT, "unknown dtype");
+  if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)rows, (long long)cols);
+  if (cols % 16 != 0) return fail(METIS_ERR_BAD_SHAPE, "NVFP4 block shape (1, 16) does not divide tensor shape (%lld, %lld)", (long long)rows, (long long)cols);
+  if (ld < cols || ld % 8 != 0 || !aligned16(x) || !aligned16(gamma) || !aligned16(norm_out) || !aligned16(workspace))
+    return fail(METIS_ERR_BAD_ALIGNMENT, "x, gamma, norm_out and workspace must be 16-byte aligned and ld a multiple of 8");
+  if (workspace_bytes < metis_rmsnorm_mean_workspace_bytes(rows, cols)) return fail(METIS_ERR_WORKSPACE, "workspace too small");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  float* partial = static_cast<float*>(workspace);
+  int32_t rc;
+  if (x_dtype == METIS_DTYPE_BF16 && gamma_dtype == METIS_DTYPE_BF16)
+    rc = launch_colsum(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, static_cast<const __nv_bfloat16*>(gamma), eps, norm_out, rstd, partial, st);
+  else if (x_dtype == METIS_DTYPE_BF16)
+    rc = launch_colsum(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, static_cast<const float*>(gamma), eps, norm_out, rstd, partial, st);
+  else if (gamma_dtype == METIS_DTYPE_BF16)
+    rc = launch_colsum(static_cast<const float*>(x), rows, cols, ld, static_cast<const __nv_bfloat16*>(gamma), eps, norm_out, rstd, partial, st);
+  else
+    rc = launch_colsum(static_cast<const float*>(x), rows, cols, ld, static_cast<const float*>(gamma), eps, norm_out, rstd, partial, st);
+  if (rc) return rc;
+  const NormShape sh = norm_shape((int)(cols >> 4));
+  const int64_t slots = colsum_ctas(rows, sh.by) * sh.by;
+  METIS_CUDA_OK(launch_overlapped(kLaunchShort, rmsnorm_mean_finish_kernel, dim3((unsigned)ceil_div(cols, 256)), dim3(256), 0, st,
+                                  (const float*)partial, slots, rows, cols, mean));
+  return METIS_OK;
 }

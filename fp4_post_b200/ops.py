@@ -236,6 +236,34 @@ def rmsnorm_nvfp4_quantize(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e
     return (q, norm.reshape(x.shape)) if return_norm else q
 
 
+def rmsnorm_mean(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, *, want_rstd: bool = True):
+    """RMSNorm of x viewed as [rows, cols] with the column mean of its output from the same pass:
+    (y shaped like x, mean fp32 [cols], rstd fp32 [rows] or None).  First pass of the mean-centred
+    activation path; nvfp4_quantize[_dual](y, mean=mean) is the second."""
+    _need_cuda(x, "x")
+    _need_cuda(gamma, "gamma")
+    x2 = _rows2d(x)
+    rows, cols = x2.shape
+    if cols % 16 != 0 or rows == 0:
+        raise ValueError(f"NVFP4 block shape (1, 16) does not divide tensor shape {(rows, cols)}")
+    gamma = gamma.contiguous()
+    assert gamma.numel() == cols
+    L = cabi.lib()
+    dev = x2.device
+    with _on_device(dev):
+        out_dtype = torch.bfloat16 if (x2.dtype == torch.bfloat16 and gamma.dtype == torch.bfloat16) else torch.float32
+        y = torch.empty((rows, cols), dtype=out_dtype, device=dev)
+        mean = torch.empty(cols, dtype=torch.float32, device=dev)
+        rstd = torch.empty(rows, dtype=torch.float32, device=dev) if want_rstd else None
+        ws = torch.empty(max(16, L.metis_rmsnorm_mean_workspace_bytes(rows, cols)), dtype=torch.uint8, device=dev)
+        rc = L.metis_rmsnorm_mean(x2.data_ptr(), _dtype_code(x2, "x"), rows, cols, x2.stride(0), gamma.data_ptr(),
+                                  _dtype_code(gamma, "gamma"), float(eps), y.data_ptr(), _ptr(rstd), mean.data_ptr(),
+                                  ws.data_ptr(), ws.numel(), _stream())
+    cabi.check(rc, "metis_rmsnorm_mean")
+    LAUNCHES["rmsnorm_quantize"] += 2
+    return y.reshape(x.shape), mean, rstd
+
+
 def nvfp4_dequantize(q: NVFP4Tensor, dtype: torch.dtype = torch.float32, add_mean: bool = True,
                      unit: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Dense [R, C] tensor of q.  `unit` (fp32 [1], device) replaces q's own unit, e.g. to express the

@@ -197,6 +197,21 @@ int32_t metis_rmsnorm_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t row
                                      void* stream);
 
 /*
+ * RMSNorm for the mean-centred quantizer: y = round_to_x_dtype(x * rsqrt(mean(x^2) + eps)) * gamma
+ * (src/Metis/models/llama.py:23-31) together with what the next steps need, from one read of x:
+ *   norm_out  y, [rows, cols] in the dtype of the product (bf16 when x and gamma are bf16, else fp32)
+ *   mean      fp32 [cols], the column mean of y (input_flat.mean(dim=0), bitlinear.py:326): the mean-centred
+ *             quantizer cannot start before it exists, so normalisation and quantization are two passes
+ *             here; metis_nvfp4_quantize[_dual](y, col_mean = mean) is the second and reads y once
+ *   rstd      optional fp32 [rows], rsqrt(mean(x^2) + eps) of every row, for the backward of the norm
+ * Deterministic summation order.  workspace: metis_rmsnorm_mean_workspace_bytes(rows, cols).
+ */
+int64_t metis_rmsnorm_mean_workspace_bytes(int64_t rows, int64_t cols);
+int32_t metis_rmsnorm_mean(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
+                           const void* gamma, int32_t gamma_dtype, float eps, void* norm_out, float* rstd,
+                           float* mean, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * codes/scales/unit -> dense [R, C] (ld elements per row), bf16 or fp32:
  * out = e2m1(code) * (e4m3(scale) * unit), the last two steps of quant.py:19-35.
  * If add_row_vec (fp32 [C]) is given it is added to every row (me + QDQ(x - me),

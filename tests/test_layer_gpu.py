@@ -410,3 +410,61 @@ def test_rmsnorm_module_feeds_a_projection_group_without_requantizing():
         fused = proj(y)                      # picks the registered operand up by identity
         plain = proj(y.clone())              # quantizes the same values itself
     assert torch.equal(fused, plain)
+
+
+def test_rmsnorm_module_in_mean_mode_is_trainable_and_matches_the_unfused_chain():
+    # GRPO defaults: mean-centred activations, stochastic backward replaced by round to nearest here so that the
+    # two chains can be compared; the fused entry must give what norm -> BitLinear gives, with gradients
+    from Metis.models.llama import RMSNorm
+    torch.manual_seed(4)
+    args = metis_args(32, cache=True)                      # enable_activation_svd=True, metis_mode="mean"
+    group = {"name": "blk.qkv", "mean_cache": {}, "input_ref": None, "quantized_input": None}
+    proj = BitLinear(512, 256, args=args, bias=False, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+    proj.layer_name, proj.activation_group = "blk.q_proj", group
+    proj.split()
+    proj = proj.to(DEV)
+    norm = RMSNorm(512).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        norm.weight.copy_(1.0 + 0.1 * torch.randn(512, device=DEV))
+    x = (torch.randn(2, 64, 512, device=DEV) + torch.randn(1, 1, 512, device=DEV)).to(torch.bfloat16)
+    gout = torch.randn(2, 64, 256, device=DEV, dtype=torch.bfloat16)
+    res = {}
+    for fused in (True, False):
+        xin = x.clone().requires_grad_(True)
+        for p in list(proj.parameters()) + [norm.weight]:
+            p.grad = None
+        if fused:
+            packed, y = norm.forward_quantized(xin, return_norm=True, activation_group=group)
+            assert isinstance(packed, PackedOperand) and packed.mean is not None and packed._qt is not None
+            assert group["input_ref"]() is y and "blk.qkv.shared" in group["mean_cache"]
+        else:
+            group["input_ref"] = group["quantized_input"] = None
+            y = norm(xin)
+        out = proj(y)
+        out.backward(gout)
+        res[fused] = dict(y=out.detach().float().cpu().numpy(), dx=xin.grad.float().cpu().numpy(),
+                          dgamma=norm.weight.grad.float().cpu().numpy(), dR=proj.warmup_linear.weight.grad.float().cpu().numpy())
+    # same normalised values up to a last bf16 bit, same quantizer: outputs and gradients agree closely
+    assert rel_l2(res[True]["y"], res[False]["y"]) <= 2e-2
+    assert rel_l2(res[True]["dR"], res[False]["dR"]) <= 5e-2
+    assert rel_l2(res[True]["dx"], res[False]["dx"]) <= 5e-2
+    assert rel_l2(res[True]["dgamma"], res[False]["dgamma"]) <= 5e-2
+
+
+def test_rmsnorm_module_keeps_the_rolling_decode_mean_of_its_group():
+    from Metis.models.llama import RMSNorm
+    torch.manual_seed(6)
+    metis_args(32, cache=True)                             # configures the class attributes (mean mode)
+    F.enable_activation_svd, F.metis_mode, F.compute_dtype = True, "mean", torch.bfloat16
+    F.q_forward_input = Cast2NVFp4e2m1BlockNOSR
+    group = {"name": "g", "mean_cache": {}, "input_ref": None, "quantized_input": None}
+    norm = RMSNorm(256).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        p0, y0 = norm.forward_quantized(torch.randn(4, 16, 256, device=DEV, dtype=torch.bfloat16), return_norm=True, activation_group=group)
+        me0, n0 = group["mean_cache"]["g.shared"]
+        p1, y1 = norm.forward_quantized(torch.randn(4, 1, 256, device=DEV, dtype=torch.bfloat16), return_norm=True, activation_group=group)
+        me1, n1 = group["mean_cache"]["g.shared"]
+    assert n0 == 64 and n1 == 68
+    want = (me0.float() * 64 + y1.float().reshape(-1, 256).mean(0) * 4) / 68
+    assert torch.allclose(me1.reshape(-1), want.reshape(-1), rtol=1e-5, atol=1e-6)
+    assert torch.allclose(p1.mean.reshape(-1), me1.reshape(-1))

@@ -103,3 +103,31 @@ def test_without_the_normalised_output_the_codes_are_the_same():
     q1 = ops.rmsnorm_nvfp4_quantize(x, gamma, 1e-6)
     q2, _ = ops.rmsnorm_nvfp4_quantize(x, gamma, 1e-6, return_norm=True)
     assert torch.equal(q1.codes, q2.codes) and torch.equal(q1.scales, q2.scales) and torch.equal(q1.unit, q2.unit)
+
+
+# ---- the mean-centred / trainable path: normalise + column mean in one pass, then the quantizer -------------------
+
+@pytest.mark.parametrize("rows,cols", [(48, 1536), (256, 3584), (1024, 4096), (40, 8960), (2048, 256)])
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+def test_norm_with_column_mean(rows, cols, gdtype):
+    x = synthetic(rows, cols, "student", seed=cols + rows, dtype=torch.bfloat16).to(DEV)
+    g = torch.Generator().manual_seed(cols + 1)
+    gamma = (1.0 + 0.1 * torch.randn(cols, generator=g)).to(gdtype).to(DEV)
+    y, mean, rstd = ops.rmsnorm_mean(x, gamma, 1e-6)
+    # the same normalised values as the fused quantizer writes, bit for bit (one arithmetic, two kernels)
+    _, y_fused = ops.rmsnorm_nvfp4_quantize(x, gamma, 1e-6, return_norm=True)
+    assert y.dtype == y_fused.dtype and torch.equal(y, y_fused)
+    # against the CPU chain: a reciprocal RMS that differs in its last bit moves the normalised value by one
+    # bf16 ulp, and the product with gamma by up to two
+    want = reference_norm(x.cpu(), gamma.cpu(), 1e-6).float()
+    assert bool(((y.float().cpu() - want).abs() <= want.abs().clamp(min=1e-30) * 2.0 ** -6).all())
+    assert float((y.float().cpu() == want).float().mean()) > 0.995
+    # mean of the kernel's own output, fp32 sums in a fixed order
+    assert torch.allclose(mean, y.float().mean(dim=0), rtol=1e-5, atol=1e-6)
+    m2 = ops.rmsnorm_mean(x, gamma, 1e-6)[1]
+    assert torch.equal(mean, m2)                                   # deterministic
+    want_rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
+    assert torch.allclose(rstd, want_rstd, rtol=1e-6, atol=0)
+    # second pass: the quantizer on y with that mean, against the oracle
+    q = ops.nvfp4_quantize(y, mean=mean, sf_layout=cabi.SF_ROWMAJOR)
+    assert_packed_equal(q, y.float().cpu().numpy(), cabi.SF_ROWMAJOR, mean=mean.cpu().numpy(), what="norm + mean -> quant")
