@@ -43,11 +43,12 @@ class PackedOperand:
              dX / dW can be produced on demand) and `quantizer` the class that did it.
     """
 
-    def __init__(self, q, source, quantizer, shape):
+    def __init__(self, q, source, quantizer, shape, rotate=None):
         self.q = q
         self.source = source
         self.quantizer = quantizer
         self.shape = tuple(shape)      # shape of the tensor this stands for, e.g. [B, T, K]
+        self.rotate = rotate           # sign mask of the Hadamard rotation of the transposed quantization, or None
         self._qt = None
         self._dense = {}
         self.mean_event = None         # recorded when the column mean exists (before the quantization that uses it)
@@ -65,7 +66,8 @@ class PackedOperand:
     def transposed(self):
         """Quantization of the transpose (blocks along the rows of the source), cached."""
         if self._qt is None:
-            self._qt = self.quantizer.quantize_packed(self.source, transpose=True, mean=self.q.row_vec)
+            self._qt = self.quantizer.quantize_packed(self.source, transpose=True, mean=self.q.row_vec,
+                                                      hadamard_signs=self.rotate)
         return self._qt
 
     def dense(self, dtype):
@@ -150,6 +152,21 @@ class LinearLowbitFunction(torch.autograd.Function):
 
     # "packed": real FP4 operands on the tensor-core GEMM; "dense": dequantize + torch.matmul
     gemm_mode = "packed"
+    # Packed mode only: rotate both operands of the weight-gradient product by the signed 16 x 16 Hadamard
+    # matrix along the tokens before they are quantized (the NVIDIA baseline's treatment of the Wgrad
+    # operands, bitlinear.py:395-405, folded into the transposed quantizer; the rotations cancel in the
+    # product).  The forward-weight rotation of `enable_nv_recipe` (bitlinear.py:578-585) has no packed form
+    # (the activation is quantized unrotated) and stays on the dense torch path.
+    packed_wgrad_rht = False
+
+    @staticmethod
+    def _wgrad_rotation():
+        """Sign mask of the Wgrad rotation (bit i set: position i of a block of 16 is negated), or None."""
+        F = LinearLowbitFunction
+        if not F.packed_wgrad_rht:
+            return None
+        signs = F._get_hadamard_sign(16, "cpu", torch.float32)
+        return sum(1 << i for i in range(16) if signs[i] < 0)
 
     # ---- random Hadamard transform of the NV baseline (kept in torch; bitlinear.py:75-211) ----------
     @staticmethod
@@ -335,11 +352,12 @@ class LinearLowbitFunction(torch.autograd.Function):
         if mean is not None and flat.is_cuda:
             mean_event = torch.cuda.Event()
             mean_event.record()             # work that needs only the mean may overlap the quantization
+        rotate = LinearLowbitFunction._wgrad_rotation()
         if both and _dual_ok(flat):
-            q, qt = quantizer.quantize_packed_dual(flat, mean=mean)
+            q, qt = quantizer.quantize_packed_dual(flat, mean=mean, hadamard_signs=rotate)
         else:
             q, qt = quantizer.quantize_packed(flat, mean=mean), None
-        packed = PackedOperand(q, flat, quantizer, tensor.shape)
+        packed = PackedOperand(q, flat, quantizer, tensor.shape, rotate=rotate)
         packed._qt = qt
         packed.mean_event = mean_event
         return packed
@@ -522,12 +540,18 @@ def _one(like: torch.Tensor) -> torch.Tensor:
     return t
 
 
-def _row_sums(q):
-    """Row sums of the quantized matrix, computed once per tensor (the activation's are needed by
-    both weight-gradient products of a fused layer)."""
+def _row_sums(q, rotate=None):
+    """Sums over the tokens of the matrix a transposed quantization stands for, computed once per tensor (the
+    activation's are needed by both weight-gradient products of a fused layer).  Of a rotated quantization
+    (blocks b stored as y = H (s . b)): 1^T b = ((H s) / 16)^T y, a weighted row sum with period 16."""
     cached = getattr(q, "_row_sums", None)
     if cached is None:
-        cached = ops.nvfp4_gemv(q)
+        weights = None
+        if rotate is not None:
+            sgn = torch.tensor([-1.0 if (rotate >> i) & 1 else 1.0 for i in range(16)])
+            h = LinearLowbitFunction._get_hadamard(16, "cpu", torch.float32)
+            weights = ((h @ sgn) / 16.0).repeat(q.shape[1] // 16).to(q.device)
+        cached = ops.nvfp4_gemv(q, weights)
         q._row_sums = cached
     return cached
 
@@ -557,16 +581,19 @@ def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int, out_dtype=torch.flo
     rank-1 terms of  dW = Qd^T Qx + (Qd^T 1) mu_x^T + mu_D (Qx^T 1 + M mu_x)^T."""
     d_t = da.transposed()                                   # [N, M], col_vec = mu_D
     x_t = xa.transposed()                                   # [K, M], col_vec = mu_x
+    if da.rotate != xa.rotate:
+        raise RuntimeError("the two operands of a weight-gradient product must be rotated alike")
     rank1 = []
     mu_x, mu_d = x_t.col_vec, d_t.col_vec
     if mu_x is not None:
-        rank1.append((_row_sums(d_t), mu_x))
+        rank1.append((_row_sums(d_t, da.rotate), mu_x))
     if mu_d is not None:
-        tail = _row_sums(x_t)
+        tail = _row_sums(x_t, xa.rotate)
         if mu_x is not None:
             tail = tail + float(M) * mu_x
         rank1.append((mu_d, tail))
-    return _packed_matmul(d_t, x_t, rank1=rank1, out_dtype=out_dtype, sm_limit=sm_limit)
+    # rotated operands: (H s)^T (H s) = 16 I
+    return ops.nvfp4_gemm(d_t, x_t, rank1=rank1, out_dtype=out_dtype, sm_limit=sm_limit, alpha=1.0 / 16 if da.rotate is not None else 1.0)
 
 
 def _grad_dtype(param: torch.Tensor):
@@ -790,7 +817,7 @@ class MetisFusedFunction(torch.autograd.Function):
             # GEMM.  Both branches contract over the transposed activation: made once, before the fork.
             x_t = xa.transposed()
             if centred:
-                _row_sums(x_t)              # cached on x_t and read by both branches
+                _row_sums(x_t, xa.rotate)   # cached on x_t and read by both branches
             main, aux = torch.cuda.current_stream(), _aux_stream(g.device)
             aux.wait_stream(main)
             dg = F._pack_centred(g, quantizer, centred, both=True)

@@ -315,23 +315,26 @@ class _NativeNVFP4(BlockQuantFunc):
     @classmethod
     @torch.no_grad()
     def quantize_packed(cls, x: torch.Tensor, *, transpose: bool = False, mean: torch.Tensor | None = None,
-                        sf_layout: int = cabi.SF_MMA) -> ops.NVFP4Tensor:
+                        sf_layout: int = cabi.SF_MMA, hadamard_signs: int | None = None) -> ops.NVFP4Tensor:
         """Real FP4: packed codes + E4M3 scales + unit of x viewed as [rows, cols] (or of its
         transpose).  `mean` (fp32 [cols]) is subtracted first and recorded on the result."""
         cls._check(x)
         return ops.nvfp4_quantize(cls._native_input(x), transpose=transpose, stochastic=cls.stochastic,
                                   seed=cls.philox_key(), sf_layout=sf_layout, mean=mean,
-                                  offset_counter=cls._offset_counter(x.device) if cls.stochastic else None)
+                                  offset_counter=cls._offset_counter(x.device) if cls.stochastic else None,
+                                  hadamard_signs=hadamard_signs if transpose else None)
 
     @classmethod
     @torch.no_grad()
-    def quantize_packed_dual(cls, x: torch.Tensor, *, mean: torch.Tensor | None = None, sf_layout: int = cabi.SF_MMA):
+    def quantize_packed_dual(cls, x: torch.Tensor, *, mean: torch.Tensor | None = None, sf_layout: int = cabi.SF_MMA,
+                             hadamard_signs: int | None = None):
         """(quantize_packed(x), quantize_packed(x, transpose=True)) from one pass over x: what a training
         step needs of every operand (the products of the backward contract over the other dimension)."""
         cls._check(x)
         return ops.nvfp4_quantize_dual(cls._native_input(x), stochastic=cls.stochastic,
                                        seed=cls.philox_key(), sf_layout=sf_layout, mean=mean,
-                                       offset_counter=cls._offset_counter(x.device) if cls.stochastic else None)
+                                       offset_counter=cls._offset_counter(x.device) if cls.stochastic else None,
+                                       hadamard_signs=hadamard_signs)
 
     @classmethod
     @torch.no_grad()

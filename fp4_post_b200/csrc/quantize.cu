@@ -118,7 +118,27 @@ struct TileOutputs {
   uint8_t* codes_t;  float* amax_t;  unsigned int* gmax_t;        // Qt [cols, rows]
   uint8_t* codes_r;  float* amax_r;  unsigned int* gmax_r;        // Q  [rows, cols] (dual mode)
   unsigned int* error;
+  uint32_t hadamard;         // bit 16: rotate every 16-row block of Qt first; bits [0, 16): the sign of each row
 };
+
+// y = H (s . v) for one block of 16 values: the signs flip as the mask says, then the 16-point Walsh-Hadamard
+// butterfly in natural (Sylvester) order, fp32 additions in this fixed order (bitlinear.py:75-211: the random
+// Hadamard transform of the NVIDIA baseline, x -> (x . signs) H per tile of 16, H unnormalised).
+__device__ __forceinline__ void hadamard16(float (&v)[16], uint32_t sign_mask) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(__float_as_uint(v[i]) ^ (((sign_mask >> i) & 1u) << 31));
+#pragma unroll
+  for (int h = 1; h < 16; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if ((i & h) == 0) {
+        const float a = v[i], b = v[i + h];
+        v[i] = __fadd_rn(a, b);
+        v[i + h] = __fsub_rn(a, b);
+      }
+    }
+  }
+}
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
@@ -223,6 +243,7 @@ quantize_tile_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, in
       float amax[TC::kColsPerWord];
 #pragma unroll
       for (int c = 0; c < TC::kColsPerWord; ++c) {
+        if (out.hadamard) hadamard16(v[c], out.hadamard & 0xFFFFu);           // uniform over the grid
         const int64_t out_row = col0 + lane * TC::kColsPerWord + c;           // row of Qt = column of x
         const float a = abs_max16(v[c]);
         const float s = block_scale_from_amax(a);
@@ -742,7 +763,10 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   if (ctr) offset = 0;
   if ((flags & METIS_Q_OFFSET_ON_DEVICE) && (!sr || !ctr || (reinterpret_cast<uintptr_t>(ctr) & 7u)))
     return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_OFFSET_ON_DEVICE needs METIS_Q_STOCHASTIC and an 8-byte aligned device address in offset");
-  if (flags & ~(METIS_Q_TRANSPOSE | METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x", flags);
+  if (flags & ~(METIS_Q_TRANSPOSE | METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x", flags);
+  if ((flags & METIS_Q_HADAMARD) && !transpose) return fail(METIS_ERR_UNSUPPORTED, "METIS_Q_HADAMARD rotates the blocks of the transposed quantization: it needs METIS_Q_TRANSPOSE");
+  if ((flags & METIS_Q_SIGN_MASK) && !(flags & METIS_Q_HADAMARD)) return fail(METIS_ERR_BAD_ARGUMENT, "sign bits without METIS_Q_HADAMARD");
+  const uint32_t rht = (flags & METIS_Q_HADAMARD) ? ((1u << 16) | (flags >> 16)) : 0u;
   if (!x) return fail(METIS_ERR_BAD_ARGUMENT, "x is null");
   if (x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown x_dtype %d", x_dtype);
   if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)rows, (long long)cols);
@@ -770,7 +794,7 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   // flight per CTA, where the register-fed kernel waits on its loads.  Same arithmetic, same bytes.
   const bool rows_by_tiles = !transpose && rows * cols >= kTileRowsMinElements && (ld * esz) % 16 == 0;
   if (rows_by_tiles) {
-    const TileOutputs out = {nullptr, nullptr, nullptr, codes, ws.amax, ws.gmax, ws.gmax + 1};
+    const TileOutputs out = {nullptr, nullptr, nullptr, codes, ws.amax, ws.gmax, ws.gmax + 1, 0u};
     const int32_t rc = x_dtype == METIS_DTYPE_BF16
         ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
         : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
@@ -783,7 +807,7 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
       launch_rows(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr,
                   reinterpret_cast<uint32_t*>(codes), ws, st);
   } else {
-    const TileOutputs out = {codes, ws.amax, ws.gmax, nullptr, nullptr, nullptr, ws.gmax + 1};
+    const TileOutputs out = {codes, ws.amax, ws.gmax, nullptr, nullptr, nullptr, ws.gmax + 1, rht};
     const int32_t rc = x_dtype == METIS_DTYPE_BF16
         ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
         : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
@@ -808,7 +832,9 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
   if (ctr) offset = 0;
   if ((flags & METIS_Q_OFFSET_ON_DEVICE) && (!sr || !ctr || (reinterpret_cast<uintptr_t>(ctr) & 7u)))
     return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_OFFSET_ON_DEVICE needs METIS_Q_STOCHASTIC and an 8-byte aligned device address in offset");
-  if (flags & ~(METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x (the dual quantizer always writes both orientations)", flags);
+  if (flags & ~(METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x (the dual quantizer always writes both orientations)", flags);
+  if ((flags & METIS_Q_SIGN_MASK) && !(flags & METIS_Q_HADAMARD)) return fail(METIS_ERR_BAD_ARGUMENT, "sign bits without METIS_Q_HADAMARD");
+  const uint32_t rht = (flags & METIS_Q_HADAMARD) ? ((1u << 16) | (flags >> 16)) : 0u;      // the transposed output only
   if (!x) return fail(METIS_ERR_BAD_ARGUMENT, "x is null");
   if (x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown x_dtype %d", x_dtype);
   if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)rows, (long long)cols);
@@ -832,7 +858,7 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
   float* amax_r = reinterpret_cast<float*>(static_cast<char*>(workspace) + kHeaderBytes);
   float* amax_t = amax_r + rows * (cols / 16);
   METIS_CUDA_OK(cudaMemsetAsync(head, 0, 3 * sizeof(unsigned int), st));
-  const TileOutputs out = {codes_t, amax_t, head + 2, codes, amax_r, head, head + 1};
+  const TileOutputs out = {codes_t, amax_t, head + 2, codes, amax_r, head, head + 1, rht};
   const int32_t rc = x_dtype == METIS_DTYPE_BF16
       ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
       : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);

@@ -119,10 +119,21 @@ def col_mean(x: torch.Tensor) -> torch.Tensor:
     return mean
 
 
+def _hadamard_flags(sign_mask: Optional[int]) -> int:
+    """Flag bits that make the transposed quantizer rotate its blocks: sign_mask has bit i set where position
+    i of every block of 16 is negated before the Hadamard butterfly; None: no rotation."""
+    if sign_mask is None:
+        return 0
+    if not 0 <= sign_mask < 1 << 16:
+        raise ValueError("sign_mask holds one bit per position of a block of 16")
+    return cabi.Q_HADAMARD | (sign_mask << 16)
+
+
 def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool = False, seed: int = 0,
                    offset: int = 0, sf_layout: int = cabi.SF_MMA,
                    mean: Optional[torch.Tensor] = None,
-                   offset_counter: Optional[torch.Tensor] = None) -> NVFP4Tensor:
+                   offset_counter: Optional[torch.Tensor] = None,
+                   hadamard_signs: Optional[int] = None) -> NVFP4Tensor:
     """Quantize x (viewed as [rows, cols]) or, with transpose=True, its transpose.
 
     `mean` (fp32 [cols]) is subtracted from every row of x first.  Stochastic rounding draws
@@ -135,7 +146,7 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
     if Cc % 16 != 0 or R == 0:
         raise ValueError(f"NVFP4 block shape (1, 16) does not divide tensor shape {(R, Cc)}")
     L = cabi.lib()
-    flags = (cabi.Q_TRANSPOSE if transpose else 0) | (cabi.Q_STOCHASTIC if stochastic else 0)
+    flags = (cabi.Q_TRANSPOSE if transpose else 0) | (cabi.Q_STOCHASTIC if stochastic else 0) | _hadamard_flags(hadamard_signs)
     dev = x2.device
     if stochastic and offset_counter is not None:
         if offset_counter.dtype != torch.int64 or offset_counter.device != dev or offset_counter.numel() != 1:
@@ -166,7 +177,7 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
 
 def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int = 0, offset: int = 0,
                         sf_layout: int = cabi.SF_MMA, mean: Optional[torch.Tensor] = None,
-                        offset_counter: Optional[torch.Tensor] = None):
+                        offset_counter: Optional[torch.Tensor] = None, hadamard_signs: Optional[int] = None):
     """Both quantizations of x viewed as [rows, cols] from one pass over it: (Q of x, Q of x^T), each
     bit-identical to the separate call (round to nearest).  rows and cols must be multiples of 16."""
     _need_cuda(x, "x")
@@ -175,7 +186,7 @@ def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int 
     if rows % 16 != 0 or cols % 16 != 0 or rows == 0:
         raise ValueError(f"NVFP4 block shape (1, 16) does not divide both dimensions of tensor shape {(rows, cols)}")
     L = cabi.lib()
-    flags = cabi.Q_STOCHASTIC if stochastic else 0
+    flags = (cabi.Q_STOCHASTIC if stochastic else 0) | _hadamard_flags(hadamard_signs)      # rotation: the transposed output only
     dev = x2.device
     if stochastic and offset_counter is not None:
         if offset_counter.dtype != torch.int64 or offset_counter.device != dev or offset_counter.numel() != 1:

@@ -61,6 +61,10 @@ extern "C" {
 #define METIS_Q_TRANSPOSE   (1u << 0) /* quantize x^T: blocks run along the rows of x     */
 #define METIS_Q_STOCHASTIC  (1u << 1) /* stochastic rounding (Philox4x32-10, seed/offset) */
 #define METIS_Q_OFFSET_ON_DEVICE (1u << 2) /* offset = address of a device uint64 counter   */
+#define METIS_Q_HADAMARD    (1u << 3) /* rotate every 16-element block of the transposed output by the signed
+                                         Hadamard matrix before it is quantized; bits [16, 32) of the flags give
+                                         the sign of each of the 16 positions (bit set: minus)                  */
+#define METIS_Q_SIGN_MASK   0xFFFF0000u
 
 /* status codes (host return values are <= 0, device status words are >= 0) */
 #define METIS_OK                 0
@@ -120,6 +124,14 @@ int64_t metis_nvfp4_quantize_workspace_bytes(int64_t R, int64_t C);
  * stream draw fresh bits although their arguments are identical, which is what a captured
  * CUDA graph needs when it is replayed (the reference's torch.rand advances a device-side
  * Philox offset in the same situation).
+ *
+ * METIS_Q_HADAMARD (with METIS_Q_TRANSPOSE, or on the transposed output of the dual quantizer): the
+ * random Hadamard transform of the NVIDIA baseline (_apply_hadamard_blocks, bitlinear.py:125-211, used by
+ * _quantize_wgrad_operand, bitlinear.py:395-405) folded into the quantizer.  Every block of 16 values b
+ * (16 consecutive tokens of one channel, after the mean has been subtracted) becomes H (s . b), with H the
+ * unnormalised 16 x 16 Sylvester matrix and s the signs from the flag bits, in fp32, before amax, scale and
+ * codes are taken.  Two operands rotated alike along their contraction dimension give 16 times the plain
+ * product (H s is orthogonal up to that factor), so the weight-gradient GEMM runs with alpha = 1/16.
  *
  * Launches: large tensors take a zero-fill of the workspace header, one streaming pass and a scale
  * pass.  Round-to-nearest, untransposed tensors of at most 16384 blocks (rollout-sized

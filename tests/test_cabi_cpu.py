@@ -73,7 +73,9 @@ def test_quantize_rejects_bad_arguments_without_a_device(L):
     assert b"16" in L.metis_last_error_string()
     assert L.metis_nvfp4_quantize(None, 1, 4, 32, 32, None, 0, 0, 0, 0, p, p, p, p, 4096, None) == -1
     assert L.metis_nvfp4_quantize(p, 7, 4, 32, 32, None, 0, 0, 0, 0, p, p, p, p, 4096, None) == -1
-    assert L.metis_nvfp4_quantize(p, 1, 4, 32, 32, None, 8, 0, 0, 0, p, p, p, p, 4096, None) == -1   # unknown flag
+    assert L.metis_nvfp4_quantize(p, 1, 4, 32, 32, None, 16, 0, 0, 0, p, p, p, p, 4096, None) == -1   # unknown flag
+    assert L.metis_nvfp4_quantize(p, 1, 16, 32, 32, None, 8, 0, 0, 0, p, p, p, p, 4096, None) == -6   # the Hadamard rotation belongs to the transposed output
+    assert L.metis_nvfp4_quantize(p, 1, 16, 32, 32, None, 1 | (5 << 16), 0, 0, 0, p, p, p, p, 4096, None) == -1   # sign bits without the rotation
     assert L.metis_nvfp4_quantize(p, 1, 4, 32, 32, None, 0, 0, 0, 0, p, p, p, p, 16, None) == -4     # workspace
     assert L.metis_nvfp4_quantize(p + 4, 1, 4, 32, 32, None, 0, 0, 0, 0, p, p, p, p, 4096, None) == -3
     assert L.metis_nvfp4_quantize(p, 1, 0, 32, 32, None, 0, 0, 0, 0, p, p, p, p, 4096, None) == -2   # empty

@@ -468,3 +468,71 @@ def test_rmsnorm_module_keeps_the_rolling_decode_mean_of_its_group():
     want = (me0.float() * 64 + y1.float().reshape(-1, 256).mean(0) * 4) / 68
     assert torch.allclose(me1.reshape(-1), want.reshape(-1), rtol=1e-5, atol=1e-6)
     assert torch.allclose(p1.mean.reshape(-1), me1.reshape(-1))
+
+
+def test_packed_gradients_average_towards_the_dense_gradients_over_stochastic_draws(layer_golden):
+    # The packed backward quantizes W, D and x once more along the contraction dimension; D with stochastic
+    # rounding.  Its gradients are noisy versions of the dense (reference-wiring) ones: they point the same
+    # way, and the noise of the stochastic part averages out over draws.
+    g = layer_golden
+    x0 = torch.from_numpy(g["x"]).to(DEV)
+    gout = torch.from_numpy(g["grad_out"]).to(DEV)
+
+    def grads(mode, backward_q):
+        layer = build_layer(g, metis_args(int(g["rank"]), backward_q=backward_q, gemm_mode=mode), torch.float32)
+        x = x0.clone().requires_grad_(True)
+        layer(x).backward(gout)
+        return {k: v.double().cpu() for k, v in grads_of(layer, x).items()}
+
+    dense = grads("dense", "nvfp4e2m1bnosr")                         # deterministic reference wiring
+    draws = [grads("packed", "nvfp4e2m1b") for _ in range(24)]       # the device-side Philox counter moves on every call
+    for name in ("dx", "dR", "dV"):
+        single = draws[0][name]
+        mean = torch.stack([d[name] for d in draws]).mean(0)
+        cos = torch.nn.functional.cosine_similarity(single.flatten(), dense[name].flatten(), dim=0).item()
+        e1 = (single - dense[name]).norm().item() / dense[name].norm().item()
+        em = (mean - dense[name]).norm().item() / dense[name].norm().item()
+        print(f"{name}: cosine {cos:.4f}, rel-L2 of one draw {e1:.3f}, of the mean of 24 draws {em:.3f}")
+        # measured on B200: cosine 0.97-0.98; rel-L2 0.19-0.25 for one draw, 0.14-0.20 for the mean of 24 (what is
+        # left is the deterministic re-quantization of x and W along the other dimension)
+        assert cos > 0.95, name
+        assert em < 0.92 * e1, name                                  # the stochastic part of the error shrinks
+        assert not torch.equal(draws[0][name], draws[1][name])       # fresh bits every call
+
+
+def test_wgrad_rotation_keeps_the_weight_gradients_and_leaves_everything_else_alone():
+    # packed_wgrad_rht rotates both operands of dR and dV along the tokens (the NVIDIA baseline's Wgrad recipe):
+    # same gradients up to quantization noise, identical forward, dx, dU, ds
+    torch.manual_seed(9)
+    args = metis_args(32, cache=True)
+    layer = BitLinear(512, 384, args=args, bias=True, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+    layer.layer_name = "rht"
+    layer.split()
+    layer = layer.to(DEV)
+    x = (torch.randn(2, 256, 512, device=DEV) + 0.5 * torch.randn(1, 1, 512, device=DEV)).to(torch.bfloat16)
+    x[..., 7] *= 30                                            # an outlier channel: what the rotation is for
+    gout = torch.randn(2, 256, 384, device=DEV, dtype=torch.bfloat16)
+    res = {}
+    for rht in (False, True):
+        F.packed_wgrad_rht = rht
+        try:
+            xin = x.clone().requires_grad_(True)
+            for p in layer.parameters():
+                p.grad = None
+            y = layer(xin)
+            y.backward(gout)
+            res[rht] = dict(y=y.detach().clone(), **{k: v.clone() for k, v in grads_of(layer, xin).items()})
+        finally:
+            F.packed_wgrad_rht = False
+    for name in ("y", "dx", "dU", "ds", "dbias"):
+        assert torch.equal(res[True][name], res[False][name]), name
+    # float64 weight gradients of the unquantized chain as the yardstick
+    g2, x2 = gout.double().reshape(-1, 384), x.double().reshape(-1, 512)
+    exact_dR = g2.t() @ x2
+    for name in ("dR", "dV"):
+        a, b = res[True][name].double(), res[False][name].double()
+        assert not torch.equal(a, b)
+        assert (a - b).norm() / b.norm() < 0.3, name
+    e_plain = (res[False]["dR"].double() - exact_dR).norm() / exact_dR.norm()
+    e_rot = (res[True]["dR"].double() - exact_dR).norm() / exact_dR.norm()
+    assert e_rot < e_plain * 1.1

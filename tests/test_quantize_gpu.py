@@ -302,3 +302,62 @@ def test_one_pass_stochastic_keeps_the_scales_and_draws_two_independent_streams(
     # both dequantize to x without bias
     for part, ref in ((q, x.float()), (qt, x.float().t())):
         assert (part.dequantize(torch.float32) - ref).mean().abs().item() < 5e-3
+
+
+# ---- random Hadamard transform folded into the transposed quantizer ------------------------------------------------
+
+def _rotate_blocks_along_rows(x_f32: torch.Tensor, sign_mask: int) -> torch.Tensor:
+    """H (s . b) for every block b of 16 consecutive rows of each column, the butterfly in the kernel's order."""
+    R, C = x_f32.shape
+    v = x_f32.reshape(R // 16, 16, C).clone()
+    signs = torch.tensor([-1.0 if (sign_mask >> i) & 1 else 1.0 for i in range(16)], device=x_f32.device)
+    v = v * signs[None, :, None]
+    h = 1
+    while h < 16:
+        out = v.clone()
+        for i in range(16):
+            if (i & h) == 0:
+                out[:, i] = v[:, i] + v[:, i + h]
+                out[:, i + h] = v[:, i] - v[:, i + h]
+        v = out
+        h <<= 1
+    return v.reshape(R, C)
+
+
+@pytest.mark.parametrize("rows,cols,dtype", [(16, 16, torch.float32), (256, 64, torch.bfloat16), (2048, 1536, torch.bfloat16), (144, 272, torch.float32)])
+def test_rotated_transposed_quantization_is_the_quantization_of_the_rotated_tensor(rows, cols, dtype):
+    from fp4_post_b200.Metis.Metis.bitlinear import LinearLowbitFunction as F
+    x = synthetic(rows, cols, "outliers", seed=rows + cols, dtype=dtype).to(DEV)
+    signs = F._get_hadamard_sign(16, "cpu", torch.float32)
+    mask = sum(1 << i for i in range(16) if signs[i] < 0)
+    q = ops.nvfp4_quantize(x, transpose=True, hadamard_signs=mask, sf_layout=cabi.SF_ROWMAJOR)
+    rotated = _rotate_blocks_along_rows(x.float(), mask)
+    # the same matrix the reference's torch path builds: (tile . signs) @ H per tile of 16 along the tokens
+    want_ref = F._apply_hadamard_blocks(x.float().t().contiguous(), inverse=False).t()
+    assert torch.allclose(rotated, want_ref, rtol=1e-5, atol=1e-5)
+    assert_packed_equal(q, rotated.t().contiguous().cpu().numpy(), cabi.SF_ROWMAJOR, what="rotated transposed quantizer")
+    # with a mean: subtracted first, then rotated
+    mean = ops.col_mean(x)
+    q = ops.nvfp4_quantize(x, transpose=True, mean=mean, hadamard_signs=mask, sf_layout=cabi.SF_ROWMAJOR)
+    rotated = _rotate_blocks_along_rows(x.float() - mean, mask)
+    assert_packed_equal(q, rotated.t().contiguous().cpu().numpy(), cabi.SF_ROWMAJOR, what="rotated, mean-centred")
+    # the dual quantizer rotates its transposed output only
+    qd, qdt = ops.nvfp4_quantize_dual(x, mean=mean, hadamard_signs=mask, sf_layout=cabi.SF_ROWMAJOR)
+    assert _same(qdt, q) and _same(qd, ops.nvfp4_quantize(x, mean=mean, sf_layout=cabi.SF_ROWMAJOR))
+
+
+def test_two_operands_rotated_alike_give_sixteen_times_the_plain_product():
+    # (H s)^T (H s) = 16 I: the weight-gradient product of rotated operands, with alpha = 1/16, is the plain
+    # product up to the (different) quantization noise
+    M, N, K = 2048, 256, 384
+    d = synthetic(M, N, "normal", seed=1, dtype=torch.bfloat16).to(DEV)
+    x = synthetic(M, K, "outliers", seed=2, dtype=torch.bfloat16).to(DEV)
+    mask = 0b1010011100101101
+    plain = ops.nvfp4_gemm(ops.nvfp4_quantize(d, transpose=True), ops.nvfp4_quantize(x, transpose=True), out_dtype=torch.float32)
+    rot = ops.nvfp4_gemm(ops.nvfp4_quantize(d, transpose=True, hadamard_signs=mask), ops.nvfp4_quantize(x, transpose=True, hadamard_signs=mask),
+                         out_dtype=torch.float32, alpha=1.0 / 16)
+    exact = d.double().t() @ x.double()
+    e_plain = (plain.double() - exact).norm() / exact.norm()
+    e_rot = (rot.double() - exact).norm() / exact.norm()
+    assert e_plain < 0.2 and e_rot < 0.2
+    assert e_rot < e_plain * 1.1                                  # the rotation spreads the outlier channels: no worse
