@@ -191,3 +191,45 @@ void oracle_scales_to_mma_layout(const uint8_t* rowmajor, int64_t R, int64_t C, 
       out[((r >> 7) * tiles + (k >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (k & 3)] =
           rowmajor[r * nb + k];
 }
+
+/* ---- cross-check of the conversion-based rounding the CUDA kernels use --------------------------------
+ * The kernels take the code from a round-to-nearest-even conversion of v = x/s onto the e2m1 grid
+ * {0, .5, 1, 1.5, 2, 3, 4, 6}, where the reference (quant.py:26-31) rounds the folded index
+ * q - (relu(q-4)/2 + relu(q-8)/4), q = 2v, twice.  This walks every fp32 v whose bit pattern lies in
+ * [lo_bits, hi_bits] and counts where the reference's code differs from (a) the plain conversion and
+ * (b) the conversion applied to (v + t) - t with t = 2 on [2, 4), 4 on [4, 8), 0 or 2^-126 below 2
+ * (t = bits(v) & 0xC0800000), which drops the last bit of v the way the reference's addition does. */
+static inline uint32_t e2m1_round_nearest_even(float a) {
+  if (a >= 6.0f) return 7;
+  int lo = 0;
+  for (int i = 0; i < 8; ++i) if (kE2M1[i] <= a) lo = i;
+  const float dl = a - kE2M1[lo], dh = kE2M1[lo + 1] - a; /* exact: neighbours within a factor of two */
+  if (dl < dh) return (uint32_t)lo;
+  if (dl > dh) return (uint32_t)lo + 1;
+  return (uint32_t)((lo & 1) ? lo + 1 : lo);
+}
+
+void oracle_compare_conversion_rounding(uint32_t lo_bits, uint32_t hi_bits, uint64_t* plain_differs,
+                                        uint64_t* fixed_differs, uint32_t* first_plain_bits) {
+  uint64_t plain = 0, fixed = 0;
+  int n_first = 0;
+  for (uint32_t b = lo_bits;; ++b) {
+    float v;
+    memcpy(&v, &b, 4);
+    const float half_s = 0.5f;                       /* q = v / 0.5 = 2v exactly */
+    const uint32_t want = magnitude_code(v, half_s);
+    if (e2m1_round_nearest_even(v) != want) {
+      ++plain;
+      if (n_first < 8 && first_plain_bits) first_plain_bits[n_first++] = b;
+    }
+    const uint32_t tb = b & 0xC0800000u;
+    float t;
+    memcpy(&t, &tb, 4);
+    volatile float w = v + t;
+    const float v2 = w - t;
+    if (e2m1_round_nearest_even(v2) != want) ++fixed;
+    if (b == hi_bits) break;
+  }
+  *plain_differs = plain;
+  *fixed_differs = fixed;
+}

@@ -44,6 +44,8 @@ def lib() -> ctypes.CDLL:
         _lib.oracle_nvfp4_dequantize.restype = c.c_int
         _lib.oracle_scales_to_mma_layout.argtypes = [c.c_void_p, c.c_int64, c.c_int64, c.c_void_p]
         _lib.oracle_scales_to_mma_layout.restype = None
+        _lib.oracle_compare_conversion_rounding.argtypes = [c.c_uint32, c.c_uint32, c.c_void_p, c.c_void_p, c.c_void_p]
+        _lib.oracle_compare_conversion_rounding.restype = None
         _lib.oracle_f32_to_e4m3fn.argtypes = [c.c_float]
         _lib.oracle_f32_to_e4m3fn.restype = c.c_uint8
         _lib.oracle_e4m3fn_to_f32.argtypes = [c.c_uint8]
@@ -134,3 +136,15 @@ def gemm_reference(a_deq: np.ndarray, b_deq: np.ndarray, t=None, u=None, rvec=No
     if bias is not None:
         out += bias.astype(np.float64)[None, :]
     return out.astype(np.float32)
+
+
+def compare_conversion_rounding(lo: float, hi: float):
+    """For every fp32 v in [lo, hi] (both positive): how often the reference's twice-rounded code differs from a
+    round-to-nearest-even conversion of v onto the e2m1 grid, without and with the kernels' (v + t) - t step.
+    Returns (count without, count with, the first few v where the plain conversion differs)."""
+    lo_bits = int(np.float32(lo).view(np.uint32))
+    hi_bits = int(np.float32(hi).view(np.uint32))
+    plain, fixed = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    first = np.zeros(8, np.uint32)
+    lib().oracle_compare_conversion_rounding(lo_bits, hi_bits, ctypes.byref(plain), ctypes.byref(fixed), _ptr(first))
+    return plain.value, fixed.value, first[: min(plain.value, 8)].view(np.float32)

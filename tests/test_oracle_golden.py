@@ -91,3 +91,13 @@ def test_e4m3_helpers_agree():
     back = np.array([O.lib().oracle_f32_to_e4m3fn(float(v)) for v in a[finite]], dtype=np.uint8)
     # every finite byte survives a round trip (-0 keeps its sign)
     assert np.array_equal(back, finite)
+
+
+def test_conversion_rounding_equals_the_reference_after_the_second_rounding_step():
+    # every fp32 quotient from below the first tie (0.25) to past the largest code: 4.7e7 values
+    plain, fixed, where = O.compare_conversion_rounding(0.125, 6.5)
+    assert fixed == 0
+    # a single rounding differs from the reference's two at exactly the fp32 neighbours of three ties
+    assert plain == 3
+    assert list(where) == [np.nextafter(np.float32(2.5), np.float32(3)), np.nextafter(np.float32(3.5), np.float32(3)),
+                           np.nextafter(np.float32(5), np.float32(6))]
