@@ -49,6 +49,7 @@ class PackedOperand:
         self.quantizer = quantizer
         self.shape = tuple(shape)      # shape of the tensor this stands for, e.g. [B, T, K]
         self.rotate = rotate           # sign mask of the Hadamard rotation of the transposed quantization, or None
+        self._version = source._version    # what autograd's saved-tensor check would compare
         self._qt = None
         self._dense = {}
         self.mean_event = None         # recorded when the column mean exists (before the quantization that uses it)
@@ -66,6 +67,11 @@ class PackedOperand:
     def transposed(self):
         """Quantization of the transpose (blocks along the rows of the source), cached."""
         if self._qt is None:
+            if self.source._version != self._version:
+                # the same complaint autograd makes about a saved tensor: the backward would otherwise
+                # quantize values the forward never saw
+                raise RuntimeError("a tensor needed for the backward of a Metis layer was modified in place after "
+                                   f"the forward (version {self.source._version}, expected {self._version})")
             self._qt = self.quantizer.quantize_packed(self.source, transpose=True, mean=self.q.row_vec,
                                                       hadamard_signs=self.rotate)
         return self._qt
@@ -829,8 +835,14 @@ class MetisFusedFunction(torch.autograd.Function):
                     mean_row = ops.nvfp4_gemv(rq.transposed(), dg.mean)
             grad_r = residual_weight_gradient(dg)
             main.wait_stream(aux)
-            for t in (grad_u, grad_s, grad_v):
-                t.record_stream(main)       # allocated on the second stream, consumed by autograd on this one
+            # allocated on the second stream, read by kernels (or by autograd) on this one: the allocator must
+            # not hand their memory to the next second-stream allocation while this stream still uses it
+            handed_over = [grad_u, grad_s, grad_v, mean_row, dv.q.codes, dv._qt.codes if dv._qt is not None else None]
+            if side is not None:
+                handed_over += [side[0], side[1]]
+            for t in handed_over:
+                if t is not None:
+                    t.record_stream(main)
         else:
             grad_u, grad_s, dv, grad_v, side = low_rank_branch()
             dg = F._pack_centred(g, quantizer, centred, both=True)

@@ -27,13 +27,17 @@ constexpr int kDebugDropFirstSfa = 1;
 #ifdef METIS_TIMING_KNOBS
 constexpr int kDebugNoMma = 2;
 constexpr int kDebugNoLoad = 4;
+constexpr int kDebugNoEpilogue = 16;     // accumulator chunks are read and dropped
+constexpr int kDebugNoStore = 32;        // everything but the global stores of the epilogue
 #else
 constexpr int kDebugNoMma = 0;
 constexpr int kDebugNoLoad = 0;
+constexpr int kDebugNoEpilogue = 0;
+constexpr int kDebugNoStore = 0;
 #endif
 // run the single-CTA kernel where the CTA-pair kernel would be chosen (tests cover both)
 constexpr int kDebugSingleCta = 8;
-constexpr int kDebugMask = kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad | kDebugSingleCta;
+constexpr int kDebugMask = kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad | kDebugSingleCta | kDebugNoEpilogue | kDebugNoStore;
 
 template <int BN> struct GemmCfg {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
@@ -205,6 +209,7 @@ __device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uin
   const int lane = threadIdx.x & 31;
   const int64_t row = ctx.row0 + lane;
   if (ctx.row0 >= p.M || col0 >= p.N) return;          // warp-uniform
+  if (p.debug & kDebugNoEpilogue) return;
   const bool live = row < p.M;
   if (ctx.partial) {                                   // warp-uniform; ldp is a multiple of 32: the chunk fits
     if (live) {
@@ -246,7 +251,7 @@ __device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uin
       for (int i = 0; i < 4; ++i) {
         const int rl = 8 * i + (lane >> 2), j = lane & 3;
         const uint4 w = *reinterpret_cast<const uint4*>(ctx.staging + rl * 64 + ((j ^ ((rl >> 1) & 3)) << 4));
-        if (ctx.row0 + rl < p.M)
+        if (ctx.row0 + rl < p.M && !(p.debug & kDebugNoStore))
           *reinterpret_cast<uint4*>(static_cast<TD*>(p.d) + (ctx.row0 + rl) * p.ldd + col0 + j * 8) = w;
       }
       __syncwarp();

@@ -344,3 +344,26 @@ def test_random_lane_is_scoped_and_restored():
             assert Cast2NVFp4e2m1Block._lane == 1
         assert Cast2NVFp4e2m1Block._lane == 3
     assert Cast2NVFp4e2m1Block._lane == base
+
+
+def test_a_saved_operand_notices_an_in_place_change_before_it_quantizes_again():
+    from types import SimpleNamespace
+    from Metis.Metis.bitlinear import PackedOperand
+
+    class Recorder:
+        calls = 0
+
+        @classmethod
+        def quantize_packed(cls, x, **kw):
+            cls.calls += 1
+            return SimpleNamespace(row_vec=None, kw=kw)
+
+    x = torch.randn(32, 32)
+    op = PackedOperand(SimpleNamespace(row_vec=None), x, Recorder, x.shape)
+    x.add_(1.0)                                    # what autograd reports for a saved tensor
+    with pytest.raises(RuntimeError, match="modified in place"):
+        op.transposed()
+    assert Recorder.calls == 0
+    fresh = PackedOperand(SimpleNamespace(row_vec=None), x, Recorder, x.shape, rotate=5)
+    qt = fresh.transposed()
+    assert Recorder.calls == 1 and qt.kw["transpose"] and qt.kw["hadamard_signs"] == 5 and fresh.transposed() is qt
