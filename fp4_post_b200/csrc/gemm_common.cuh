@@ -29,15 +29,17 @@ constexpr int kDebugNoMma = 2;
 constexpr int kDebugNoLoad = 4;
 constexpr int kDebugNoEpilogue = 16;     // accumulator chunks are read and dropped
 constexpr int kDebugNoStore = 32;        // everything but the global stores of the epilogue
+constexpr int kDebugDirectStore = 64;    // bf16 chunks straight from registers (64 bytes per lane) instead of through shared memory
 #else
 constexpr int kDebugNoMma = 0;
 constexpr int kDebugNoLoad = 0;
 constexpr int kDebugNoEpilogue = 0;
 constexpr int kDebugNoStore = 0;
+constexpr int kDebugDirectStore = 0;
 #endif
 // run the single-CTA kernel where the CTA-pair kernel would be chosen (tests cover both)
 constexpr int kDebugSingleCta = 8;
-constexpr int kDebugMask = kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad | kDebugSingleCta | kDebugNoEpilogue | kDebugNoStore;
+constexpr int kDebugMask = kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad | kDebugSingleCta | kDebugNoEpilogue | kDebugNoStore | kDebugDirectStore;
 
 template <int BN> struct GemmCfg {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
@@ -238,6 +240,16 @@ __device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uin
 #pragma unroll
           for (int k = 0; k < 4; ++k) { v[8 * i + 2 * k] += bf16_lo(ww[k]); v[8 * i + 2 * k + 1] += bf16_hi(ww[k]); }
         }
+      }
+      if ((p.debug & kDebugDirectStore) && live) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          __nv_bfloat162 o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(v[8 * k + 2 * e], v[8 * k + 2 * e + 1]);
+          reinterpret_cast<uint4*>(static_cast<TD*>(p.d) + row * p.ldd + col0)[k] = *reinterpret_cast<uint4*>(o);
+        }
+        return;
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
