@@ -29,17 +29,23 @@ constexpr int kDebugNoMma = 2;
 constexpr int kDebugNoLoad = 4;
 constexpr int kDebugNoEpilogue = 16;     // accumulator chunks are read and dropped
 constexpr int kDebugNoStore = 32;        // everything but the global stores of the epilogue
-constexpr int kDebugDirectStore = 64;    // bf16 chunks straight from registers (64 bytes per lane) instead of through shared memory
+constexpr int kDebugLsuStore = 64;       // pair kernel: store D with ordinary store instructions instead of TMA
+constexpr int kDebugProfile = 128;       // pair kernel: CTA 0's issuer writes its cycle counts to status[2..6]
+constexpr int kDebugNoScaleCopy = 0x10000;   // pair kernel: the MMAs read whatever tensor memory holds as scales
+constexpr int kDebugGroupMask = 0xFF00;  // pair kernel: row tiles per band of the tile order (0 = the default)
 #else
 constexpr int kDebugNoMma = 0;
 constexpr int kDebugNoLoad = 0;
 constexpr int kDebugNoEpilogue = 0;
 constexpr int kDebugNoStore = 0;
-constexpr int kDebugDirectStore = 0;
+constexpr int kDebugLsuStore = 0;
+constexpr int kDebugProfile = 0;
+constexpr int kDebugNoScaleCopy = 0;
+constexpr int kDebugGroupMask = 0;
 #endif
 // run the single-CTA kernel where the CTA-pair kernel would be chosen (tests cover both)
 constexpr int kDebugSingleCta = 8;
-constexpr int kDebugMask = kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad | kDebugSingleCta | kDebugNoEpilogue | kDebugNoStore | kDebugDirectStore;
+constexpr int kDebugMask = kDebugDropFirstSfa | kDebugNoMma | kDebugNoLoad | kDebugSingleCta | kDebugNoEpilogue | kDebugNoStore | kDebugLsuStore | kDebugGroupMask | kDebugProfile | kDebugNoScaleCopy;
 
 template <int BN> struct GemmCfg {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
@@ -178,6 +184,8 @@ template <typename TD> struct EpilogueCtx {
   float g, c0, c1;
   float* partial = nullptr;   // split-K: raw fp32 partial sums [M, ldp] of this split go here instead of D
   int64_t ldp = 0;
+  const CUtensorMap* dmap = nullptr;   // D as [M, N] with 32-row x 64-byte boxes, 64-byte swizzle: stores go through the TMA unit
+  uint32_t flip = 0;                   //   and `staging` is then two buffers of 2 KiB used in turn
 };
 
 // v[i] += c * rvec[col0 + i] for the 32 columns of a chunk (128-bit loads when the chunk is whole
@@ -201,12 +209,46 @@ __device__ __forceinline__ void add_rank1(float (&v)[32], const float* __restric
   }
 }
 
+// The addend C for the 32 columns of a chunk (src = this lane's row of C at the chunk, or null).
+template <typename TD>
+__device__ __forceinline__ void add_c(float (&v)[32], const TD* __restrict__ src, int64_t col0, int64_t N, bool full_chunk) {
+  if (!src) return;
+  if (!full_chunk) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (col0 + i < N) {
+        if constexpr (sizeof(TD) == 2) v[i] += __bfloat162float(src[i]); else v[i] += src[i];
+      }
+    return;
+  }
+  if constexpr (sizeof(TD) == 2) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(src) + i);
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { v[8 * i + 2 * k] += bf16_lo(ww[k]); v[8 * i + 2 * k + 1] += bf16_hi(ww[k]); }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 w = __ldg(reinterpret_cast<const float4*>(src) + i);
+      v[4 * i] += w.x; v[4 * i + 1] += w.y; v[4 * i + 2] += w.z; v[4 * i + 3] += w.w;
+    }
+  }
+}
+
 // Lane l arrives with 32 consecutive columns of row row0 + l.  Stored straight from there, one
 // 16-byte store instruction would touch 32 different rows; instead the warp turns the chunk
-// through shared memory (64-byte rows, 16-byte pieces XOR-swizzled by the row so that neither side
-// has bank conflicts) and every store instruction writes 64 contiguous bytes of 8 rows.
+// through shared memory: 64-byte rows, 16-byte pieces XOR-swizzled by the row (the 64-byte swizzle
+// pattern of the tensor maps), so that neither side has bank conflicts.
+//   with a tensor map of D (ctx.dmap): lane 0 hands each 32 x 64-byte piece to the TMA unit, which
+//     clips it at the edges of D.  The warp owns two such buffers and waits, before it refills one,
+//     until the store issued from it two pieces ago has read it; the stores never pass through
+//     the load/store unit, which the operand feed of the tensor core needs
+//   without: every store instruction writes 64 contiguous bytes of 8 rows
 template <typename TD>
-__device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uint32_t (&r)[32], int64_t col0) {
+__device__ __forceinline__ void emit_chunk(EpilogueCtx<TD>& ctx, const uint32_t (&r)[32], int64_t col0) {
   const GemmParams& p = *ctx.p;
   const int lane = threadIdx.x & 31;
   const int64_t row = ctx.row0 + lane;
@@ -229,28 +271,40 @@ __device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uin
   add_rank1(v, p.rvec0, ctx.c0, col0, p.N, full_chunk);
   add_rank1(v, p.rvec1, ctx.c1, col0, p.N, full_chunk);
   const TD* src = (p.c && live) ? static_cast<const TD*>(p.c) + row * p.ldc + col0 : nullptr;
-  if (full_chunk) {
-    const int own_swz = (lane >> 1) & 3;
-    if constexpr (sizeof(TD) == 2) {
-      if (src) {
+  const int own_swz = (lane >> 1) & 3;
+  if (ctx.dmap) {                                      // warp-uniform
+    add_c<TD>(v, src, col0, p.N, full_chunk);
+    constexpr int kPieces = sizeof(TD) == 2 ? 1 : 2;   // 64-byte wide pieces per chunk
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 w = __ldg(reinterpret_cast<const uint4*>(src) + i);
-          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    for (int h = 0; h < kPieces; ++h) {
+      uint8_t* buf = ctx.staging + ctx.flip * 2048;
+      ctx.flip ^= 1u;
+      if (lane == 0) bulk_store_wait_read<1>();
+      __syncwarp();
 #pragma unroll
-          for (int k = 0; k < 4; ++k) { v[8 * i + 2 * k] += bf16_lo(ww[k]); v[8 * i + 2 * k + 1] += bf16_hi(ww[k]); }
-        }
-      }
-      if ((p.debug & kDebugDirectStore) && live) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < 4; ++k) {
+        uint4 w;
+        if constexpr (sizeof(TD) == 2) {
           __nv_bfloat162 o[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) o[e] = __floats2bfloat162_rn(v[8 * k + 2 * e], v[8 * k + 2 * e + 1]);
-          reinterpret_cast<uint4*>(static_cast<TD*>(p.d) + row * p.ldd + col0)[k] = *reinterpret_cast<uint4*>(o);
+          w = *reinterpret_cast<uint4*>(o);
+        } else {
+          w = make_uint4(__float_as_uint(v[16 * h + 4 * k]), __float_as_uint(v[16 * h + 4 * k + 1]),
+                         __float_as_uint(v[16 * h + 4 * k + 2]), __float_as_uint(v[16 * h + 4 * k + 3]));
         }
-        return;
+        *reinterpret_cast<uint4*>(buf + lane * 64 + ((k ^ own_swz) << 4)) = w;
       }
+      fence_async_shared();
+      __syncwarp();
+      if (lane == 0 && !(p.debug & kDebugNoStore))
+        tma_store_2d(ctx.dmap, smem_u32(buf), (int32_t)col0 + h * 16, (int32_t)ctx.row0);
+    }
+    return;
+  }
+  if (full_chunk) {
+    add_c<TD>(v, src, col0, p.N, true);
+    if constexpr (sizeof(TD) == 2) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         __nv_bfloat162 o[4];
@@ -268,13 +322,6 @@ __device__ __forceinline__ void emit_chunk(const EpilogueCtx<TD>& ctx, const uin
       }
       __syncwarp();
     } else {
-      if (src) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 w = __ldg(reinterpret_cast<const float4*>(src) + i);
-          v[4 * i] += w.x; v[4 * i + 1] += w.y; v[4 * i + 2] += w.z; v[4 * i + 3] += w.w;
-        }
-      }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {                     // 16 columns = 64 bytes per row at a time
 #pragma unroll

@@ -32,7 +32,7 @@ struct PairCfg {
   static constexpr int kSfaBytes = 4 * 512;               // scales of this CTA's rows of A
   static constexpr int kSfbBytes = 2 * 4 * 512;           // scales of all 256 rows of B
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 38 KiB
-  static constexpr int kStagingBytes = 8 * 2048;           // epilogue: 32 rows x 64 bytes for each of 8 warps
+  static constexpr int kStagingBytes = 8 * 4096;           // epilogue: two buffers of 32 rows x 64 bytes for each of 8 warps
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
   static constexpr int kThreads = 320;
 };
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(PairCfg::kThreads, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                        const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_u,
-                       const GemmParams p) {
+                       const __grid_constant__ CUtensorMap map_d, const GemmParams p) {
   using Cfg = PairCfg;
   constexpr int kStages = Cfg::kStages;
   constexpr int BN = Cfg::BN;
@@ -150,6 +150,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   const int64_t sf_tiles_k = sf_tiles_per_row(p.K);        // scale tiles per 128-row block
   const int64_t a_row_blocks = (p.M + 127) / 128;
   const int64_t b_row_blocks = (p.N + 127) / 128;
+  const int band = (p.debug & kDebugGroupMask) ? ((p.debug & kDebugGroupMask) >> 8) : 8;   // row tiles per band of the tile order
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -182,7 +183,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t full_leader = map_to_cta(full_local, 0);
     for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, 8, tm, tn);
+      tile_coords(tile, tiles_m, tiles_n, band, tm, tn);
       const int32_t m0 = (int32_t)(tm * 2 * kBM + cta * kBM);         // this CTA's rows of A
       const int32_t n0 = (int32_t)(tn * BN);
       const int32_t nb0 = n0 + (int32_t)cta * 128;                    // this CTA's rows of B
@@ -242,9 +243,21 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       uint32_t stage_lo = stage0_lo;
       uint32_t sf_buf = 0;
       const bool no_mma = (p.debug & kDebugNoMma) != 0;
+#ifdef METIS_TIMING_KNOBS
+      long long prof_full = 0, prof_release = 0, prof_t;
+      const long long prof_start = clock64();
+      const uint64_t prof_ns0 = global_ns();
+#define METIS_PROF_BEGIN() prof_t = clock64()
+#define METIS_PROF_END(acc) acc += clock64() - prof_t
+#else
+#define METIS_PROF_BEGIN()
+#define METIS_PROF_END(acc)
+#endif
       for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
         if (local_tile > 0) {
+          METIS_PROF_BEGIN();
           ok = __all_sync(0xffffffffu, mbar_wait_cluster(acc_release, (local_tile - 1u) & 1u, abort_flag));
+          METIS_PROF_END(prof_release);
           if (!ok) {
             if (lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_EPI);
             break;
@@ -254,7 +267,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const uint32_t d_tmem = tmem_base + (local_tile & 1u) * Cfg::kAccStride;
         for (int it = 0; it < iters; ++it) {
           const bool scaled = it < k_iters;
+          METIS_PROF_BEGIN();
           ok = __all_sync(0xffffffffu, mbar_wait_cluster(&full[stage], phase, abort_flag));
+          METIS_PROF_END(prof_full);
           if (!ok) {
             if (lane == 0) report(p.status, abort_flag, METIS_DEV_TIMEOUT_TMA);
             break;
@@ -275,9 +290,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
               // only the first three of a stage wait for nothing.
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                tc_copy_scales_pair(t_sfa + 4 * j, sf_lo + 32 * j);
-                tc_copy_scales_pair(t_sfb + 8 * j, sf_lo + 128 + 32 * j);
-                tc_copy_scales_pair(t_sfb + 8 * j + 4, sf_lo + 256 + 32 * j);
+                if (!(p.debug & kDebugNoScaleCopy)) {
+                  tc_copy_scales_pair(t_sfa + 4 * j, sf_lo + 32 * j);
+                  tc_copy_scales_pair(t_sfb + 8 * j, sf_lo + 128 + 32 * j);
+                  tc_copy_scales_pair(t_sfb + 8 * j + 4, sf_lo + 256 + 32 * j);
+                }
                 tc_mma_fp4_pair(d_tmem, a_lo + 2 * j, b_lo + 2 * j, kOperandDescHi, idesc_fp4(BN, 2 * kBM), t_sfa + 4 * j,
                                 t_sfb + 8 * j, (it > 0 || j > 0) ? 1u : 0u);
               }
@@ -296,6 +313,18 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           if (++stage == kStages) { stage = 0; phase ^= 1u; stage_lo = stage0_lo; }
         }
       }
+#ifdef METIS_TIMING_KNOBS
+      if ((p.debug & kDebugProfile) && p.status && blockIdx.x == 0 && lane == 0) {
+        // drain the tensor pipe so that the total covers the last tile's MMAs
+        tc_commit_pair(smem_u32(drain));
+        while (!mbar_try(drain, 0) && global_ns() - prof_ns0 < kWaitLimitNs) {}
+        p.status[2] = (int32_t)(clock64() - prof_start);
+        p.status[3] = (int32_t)(global_ns() - prof_ns0);
+        p.status[4] = (int32_t)prof_full;
+        p.status[5] = (int32_t)prof_release;
+        p.status[6] = (int32_t)local_tile;
+      }
+#endif
       if (!ok && issued && elect_one()) {
         // error path: let the tensor core finish what was issued before tensor memory is freed
         tc_commit_pair(smem_u32(drain));
@@ -313,11 +342,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     EpilogueCtx<TD> ctx;
     ctx.g = p.alpha * __ldg(p.a_unit) * __ldg(p.b_unit);
     ctx.p = &p;
-    ctx.staging = staging + (warp - 2) * 2048;
+    ctx.staging = staging + (warp - 2) * 4096;
+    ctx.dmap = (p.debug & kDebugLsuStore) ? nullptr : &map_d;
     uint32_t local_tile = 0;
     for (int64_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, 8, tm, tn);
+      tile_coords(tile, tiles_m, tiles_n, band, tm, tn);
       const int64_t row0 = tm * 2 * kBM + cta * kBM + q * 32;
       const int64_t row = row0 + lane;
       const int64_t n0 = tn * BN;
@@ -359,6 +389,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       emit_chunk<TD>(ctx, rb, n0 + ch[3] * 32);
       tc_fence_before();
     }
+    if (lane == 0) bulk_store_wait_all();                    // shared memory stays until the TMA unit has read it
   }
 
   tc_fence_before();
@@ -393,7 +424,7 @@ static int32_t launch_pair_t(const metis_gemm_args* a, const CUtensorMap* maps, 
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.numAttrs = launch_overlap_enabled(kLaunchGemm) ? 2 : 1;
-  METIS_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p));
+  METIS_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6], p));
   return METIS_OK;
 }
 
@@ -403,12 +434,17 @@ int32_t launch_gemm_pair(const metis_gemm_args* a, const CUtensorMap& ma, const 
                          const CUtensorMap& mt, const CUtensorMap& mu, const GemmParams& p) {
   // the scale arrays as [tiles, 512 bytes]: one box = the 4 tiles (2 KiB) of one stage and row block
   const int64_t sf_tiles_k = sf_tiles_per_row(a->K);
-  CUtensorMap maps[6] = {ma, mb, {}, {}, mt, mu};
+  CUtensorMap maps[7] = {ma, mb, {}, {}, mt, mu, {}};
   if (int32_t rc = make_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a->a_scales, 128, ceil_div(a->M, 128) * sf_tiles_k, 512,
-                            128, 4, "scales of A", false)) return rc;
+                            128, 4, "scales of A", 0)) return rc;
   if (int32_t rc = make_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a->b_scales, 128, ceil_div(a->N, 128) * sf_tiles_k, 512,
-                            128, 4, "scales of B", false)) return rc;
-  if (a->d_dtype == METIS_DTYPE_BF16) return launch_pair_t<__nv_bfloat16>(a, maps, p);
+                            128, 4, "scales of B", 0)) return rc;
+  // D in boxes of 32 rows x 64 bytes for the epilogue's TMA stores
+  if (a->d_dtype == METIS_DTYPE_BF16) {
+    if (int32_t rc = make_map(&maps[6], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->d, a->N, a->M, a->ldd * 2, 32, 32, "D", 64)) return rc;
+    return launch_pair_t<__nv_bfloat16>(a, maps, p);
+  }
+  if (int32_t rc = make_map(&maps[6], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a->d, a->N, a->M, a->ldd * 4, 16, 32, "D", 64)) return rc;
   return launch_pair_t<float>(a, maps, p);
 }
 

@@ -664,7 +664,7 @@ static int32_t launch_tile(const T* x, int64_t rows, int64_t cols, int64_t ld, c
   using TC = TileCfg<T>;
   CUtensorMap map;
   const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  if (int32_t rc = make_map(&map, dt, sizeof(T), x, cols, rows, ld * (int64_t)sizeof(T), TC::kCols, TC::kRows, "x", true))
+  if (int32_t rc = make_map(&map, dt, sizeof(T), x, cols, rows, ld * (int64_t)sizeof(T), TC::kCols, TC::kRows, "x", 128))
     return rc;
   const int64_t tiles = ceil_div(cols, TC::kCols) * ceil_div(rows, TC::kRows);
   int64_t grid = (int64_t)sm_count() * 3;          // three CTAs of ~63 KiB per SM

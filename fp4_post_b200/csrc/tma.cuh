@@ -77,6 +77,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   bulk_load_addr(smem_u32(dst), src, bytes, smem_u32(bar));
 }
+// TMA tile store shared -> global as one bulk group of the calling thread; elements of the box that lie
+// outside the tensor are not written.  x times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];\n\tcp.async.bulk.commit_group;"
+               ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+// the calling thread's bulk stores, all but the newest `kPending` groups, have read their shared memory
+template <int kPending> __device__ __forceinline__ void bulk_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+// all bulk stores of the calling thread are complete
+__device__ __forceinline__ void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// generic-proxy writes to shared memory made before this are visible to the bulk copies issued after it
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 #endif  // __CUDACC__
 
@@ -98,11 +112,11 @@ static inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D row-major tensor [rows, inner] with a row pitch in bytes; box = [box_rows, box_inner],
-// 128-byte swizzle (or none), out-of-range elements read as zero.
+// 2-D row-major tensor [rows, inner] with a row pitch in bytes; box = [box_rows, box_inner];
+// swizzle = 128 or 64 (bytes) or 0 for none; out-of-range elements read as zero and are not written.
 static inline int32_t make_map(CUtensorMap* map, CUtensorMapDataType dt, int64_t esz, const void* base, int64_t inner,
                         int64_t rows, int64_t pitch_bytes, int box_inner, int box_rows, const char* what,
-                        bool swizzle128 = true) {
+                        int swizzle = 128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(METIS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
@@ -110,8 +124,12 @@ static inline int32_t make_map(CUtensorMap* map, CUtensorMapDataType dt, int64_t
   const cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   (void)esz;
+  CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+#ifdef METIS_TIMING_KNOBS
+  if (const char* e = getenv("METIS_DEV_L2PROMO")) promo = (CUtensorMapL2promotion)atoi(e);
+#endif
   const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(METIS_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
   return METIS_OK;
 }
