@@ -559,7 +559,32 @@ def _row_sums(q, rotate=None):
             weights = ((h @ sgn) / 16.0).repeat(q.shape[1] // 16).to(q.device)
         cached = ops.nvfp4_gemv(q, weights)
         q._row_sums = cached
+    else:
+        done = getattr(q, "_row_sums_event", None)
+        if done is not None:                        # computed on the second stream (_row_sums_beside)
+            cur = torch.cuda.current_stream(cached.device)
+            cur.wait_event(done)
+            cached.record_stream(cur)
     return cached
+
+
+def _row_sums_beside(op: "PackedOperand"):
+    """The token sums of an activation's transposed quantization are needed by the backward pass only: issue
+    them on the second stream, after what the current stream has queued so far (the quantization), so that
+    they run in the shadow of the forward products instead of in front of the backward ones."""
+    x_t = op.transposed()
+    if getattr(x_t, "_row_sums", None) is not None:
+        return
+    dev = x_t.codes.device
+    main, aux = torch.cuda.current_stream(dev), _aux_stream(dev)
+    queued = torch.cuda.Event()
+    queued.record(main)
+    aux.wait_event(queued)
+    with torch.cuda.stream(aux):
+        _row_sums(x_t, op.rotate)
+        done = torch.cuda.Event()
+        done.record(aux)
+    x_t._row_sums_event = done
 
 
 def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, side=None, mean_row=None, sm_limit=0):
@@ -752,6 +777,9 @@ class MetisFusedFunction(torch.autograd.Function):
         if join_residual is not None:
             join_residual()
         y = _packed_matmul(xa.q, rq.q, rank1=rank1_r, lowrank=lowrank, out_dtype=act)
+        if (MetisFusedFunction.concurrent_branches and xa.q.codes.is_cuda and any(ctx.needs_input_grad)
+                and xa._qt is not None and LinearLowbitFunction._backward_centred()):
+            _row_sums_beside(xa)        # queued behind the product: it runs as that one drains, not in front of it
         ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
         ctx.has_bias = bias is not None
         ctx.dims = (M, N, K)
@@ -779,8 +807,13 @@ class MetisFusedFunction(torch.autograd.Function):
 
         fuse_dx = MetisFusedFunction.fuse_dx_side_product and act == torch.bfloat16 and r <= 256
 
-        def low_rank_branch():
+        def low_rank_branch(before_weight_gradient=None):
             # ulinear: plain linear on ts = s . yv; vlinear: quantized backward with grad_output = d_yv
+            v_t = u_side = None
+            if fuse_dx:
+                # operand of the bf16 side product of the fused dX launch; it needs nothing of this pass
+                v_t = vq.transposed()
+                u_side = ops.nvfp4_dequantize(v_t, torch.bfloat16, add_mean=False, unit=_one(v_t.unit))
             if act == torch.bfloat16 and g.is_cuda and r % 8 == 0 and N % 8 == 0 and MetisFusedFunction.native_lowrank_backward:
                 # autograd's bf16 ops on the tensor core, one pass over g per product and no transposed copy:
                 # dU = g^T ts, then d_ts = g U with d_yv = d_ts . s and ds = sum d_ts . yv in its finishing pass
@@ -800,10 +833,9 @@ class MetisFusedFunction(torch.autograd.Function):
             dv = F._pack_centred(d_yv, quantizer, centred, both=True)
             side = None
             if fuse_dx:
-                # operands of the bf16 side product of the fused dX launch that depend on this branch only
-                v_t = vq.transposed()
-                u_side = ops.nvfp4_dequantize(v_t, torch.bfloat16, add_mean=False, unit=_one(v_t.unit))
                 side = (u_side, ops.nvfp4_gemv(v_t, dv.mean) if dv.mean is not None else None)
+            if before_weight_gradient is not None:
+                before_weight_gradient(dv)
             return grad_u, grad_s, dv, _packed_dw(dv, xa, M, _grad_dtype(v_weight), sm_limit=busy_limit), side
 
         def residual_weight_gradient(dg):
@@ -816,28 +848,48 @@ class MetisFusedFunction(torch.autograd.Function):
                     reducer.ready(grad_r)   # the big all-reduce starts here and runs beside the dX product
             return grad_r
 
-        mean_row = None
-        if MetisFusedFunction.concurrent_branches and g.is_cuda:
+        def side_operand(dv, dg):
+            # D^v in the units the fused dX launch accumulates in.  e2m1 x e4m3 is exact in bf16; the ratio of the
+            # two products' units goes into T, rounded once to bf16 (the unfused dX_v would be rounded there too).
+            ratio = (dv.q.unit * vq.transposed().unit) / (dg.q.unit * rq.transposed().unit)
+            return ops.nvfp4_dequantize(dv.q, torch.bfloat16, add_mean=False, unit=ratio)
+
+        mean_row = t_acc = None
+        concurrent = MetisFusedFunction.concurrent_branches and g.is_cuda
+        if concurrent:
             # The low-rank branch is a dozen small kernels that leave most of the GPU idle; on a second
             # stream they run in the shadow of the residual branch's quantizers and weight-gradient
             # GEMM.  Both branches contract over the transposed activation: made once, before the fork.
             x_t = xa.transposed()
-            if centred:
+            if centred and getattr(x_t, "_row_sums", None) is None:
                 _row_sums(x_t, xa.rotate)   # cached on x_t and read by both branches
             main, aux = torch.cuda.current_stream(), _aux_stream(g.device)
             aux.wait_stream(main)
             dg = F._pack_centred(g, quantizer, centred, both=True)
-            with torch.cuda.stream(aux), random_lane(1):
-                grad_u, grad_s, dv, grad_v, side = low_rank_branch()
+            dg_done = torch.cuda.Event()
+            dg_done.record(main)
+            for_dx = {}
+
+            def input_gradient_operands(dv):
+                # What the input-gradient product needs from this stream goes out ahead of this branch's own
+                # weight gradient, which nothing on the other stream waits for until the very end.
                 if dg.mean is not None:
-                    # mu_D R^ for the input gradient needs the mean of g only
-                    aux.wait_event(dg.mean_event)
-                    mean_row = ops.nvfp4_gemv(rq.transposed(), dg.mean)
+                    aux.wait_event(dg.mean_event)          # mu_D R^ needs the mean of g only
+                    for_dx["mean_row"] = ops.nvfp4_gemv(rq.transposed(), dg.mean)
+                if fuse_dx:
+                    aux.wait_event(dg_done)                # the unit of Q(g)
+                    for_dx["t_acc"] = side_operand(dv, dg)
+                for_dx["ready"] = torch.cuda.Event()
+                for_dx["ready"].record(aux)
+
+            with torch.cuda.stream(aux), random_lane(1):
+                grad_u, grad_s, dv, grad_v, side = low_rank_branch(input_gradient_operands)
             grad_r = residual_weight_gradient(dg)
-            main.wait_stream(aux)
+            main.wait_event(for_dx["ready"])
+            mean_row, t_acc = for_dx.get("mean_row"), for_dx.get("t_acc")
             # allocated on the second stream, read by kernels (or by autograd) on this one: the allocator must
             # not hand their memory to the next second-stream allocation while this stream still uses it
-            handed_over = [grad_u, grad_s, grad_v, mean_row, dv.q.codes, dv._qt.codes if dv._qt is not None else None]
+            handed_over = [mean_row, t_acc, dv.q.codes, dv._qt.codes if dv._qt is not None else None]
             if side is not None:
                 handed_over += [side[0], side[1]]
             for t in handed_over:
@@ -847,8 +899,24 @@ class MetisFusedFunction(torch.autograd.Function):
             grad_u, grad_s, dv, grad_v, side = low_rank_branch()
             dg = F._pack_centred(g, quantizer, centred, both=True)
             grad_r = residual_weight_gradient(dg)
+        # with a gradient all-reduce in flight the input-gradient GEMM leaves it some SMs
+        sm_limit = reducer.gemm_sm_limit(g.device) if reducer is not None else 0
+        if fuse_dx:
+            # dX of both branches in ONE launch: D^v @ V^ enters the residual product as a bf16 rank-r side product
+            u_side, extra = side
+            if t_acc is None:
+                t_acc = side_operand(dv, dg)
+            gx = _packed_dx(dg, rq, act, side=(t_acc, u_side, extra), mean_row=mean_row, sm_limit=sm_limit)
+        else:
+            gx_v = _packed_dx(dv, vq, act, sm_limit=sm_limit)
+            gx = _packed_dx(dg, rq, act, addend=gx_v, mean_row=mean_row, sm_limit=sm_limit)          # summed in the epilogue
+        if concurrent:
+            main.wait_stream(aux)                           # the low-rank branch's own gradients
+            for t in (grad_u, grad_s, grad_v):
+                if t is not None:
+                    t.record_stream(main)
         if reducer is not None:
-            # the small gradients are final too: their bucket goes out before the input-gradient GEMM
+            # the small gradients are final too
             if reducer.across_layers:
                 for prm, t in ((v_weight, grad_v), (ctx.s_param, grad_s), (ctx.u_param, grad_u)):
                     reducer.adopt(prm, t)
@@ -857,20 +925,6 @@ class MetisFusedFunction(torch.autograd.Function):
                 for t in (grad_v, grad_s, grad_u, grad_bias):
                     reducer.ready(t)
             reducer.start_small()
-        # with a gradient all-reduce in flight the input-gradient GEMM leaves it some SMs
-        sm_limit = reducer.gemm_sm_limit(g.device) if reducer is not None else 0
-        if fuse_dx:
-            # dX of both branches in ONE launch: D^v @ V^ enters the residual product as a bf16
-            # rank-r side product.  e2m1 x e4m3 is exact in bf16; the ratio of the two products'
-            # units goes into T, rounded once to bf16 (the unfused dX_v would be rounded there too).
-            v_t, r_t = vq.transposed(), rq.transposed()
-            u_side, extra = side
-            ratio = (dv.q.unit * v_t.unit) / (dg.q.unit * r_t.unit)
-            t_acc = ops.nvfp4_dequantize(dv.q, torch.bfloat16, add_mean=False, unit=ratio)
-            gx = _packed_dx(dg, rq, act, side=(t_acc, u_side, extra), mean_row=mean_row, sm_limit=sm_limit)
-        else:
-            gx_v = _packed_dx(dv, vq, act, sm_limit=sm_limit)
-            gx = _packed_dx(dg, rq, act, addend=gx_v, mean_row=mean_row, sm_limit=sm_limit)          # summed in the epilogue
         grad_x = gx.reshape(xa.shape)
         if reducer is not None and reducer.across_layers and reducer.active():
             # the gradients sit in .grad already; the wait for their collectives moves to the end of the pass

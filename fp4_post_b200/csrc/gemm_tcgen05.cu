@@ -413,6 +413,7 @@ static int32_t launch_gemm(const metis_gemm_args* a, const CUtensorMap& ma, cons
   const int64_t work = ceil_div(a->M, kBM) * ceil_div(a->N, BN) * p.splits;
   int64_t grid = gemm_sm_budget(a->sm_limit);
   if (grid > work) grid = work;
+  grid = ceil_div(work, ceil_div(work, grid));        // the fewest CTAs that still finish in the same number of rounds
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
   METIS_CUDA_OK(launch_overlapped(kLaunchGemm, kern, dim3((unsigned)grid), dim3(kGemmThreads), Cfg::kSmemBytes, st, ma, mb, mt, mu, p));
   if (p.splits > 1) {

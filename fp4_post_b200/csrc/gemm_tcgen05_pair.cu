@@ -410,6 +410,9 @@ static int32_t launch_pair_t(const metis_gemm_args* a, const CUtensorMap* maps, 
   const int64_t tiles = ceil_div(a->M, 2 * kBM) * ceil_div(a->N, PairCfg::BN);
   int64_t pairs = gemm_sm_budget(a->sm_limit) / 2;
   if (pairs > tiles) pairs = tiles;
+  // the fewest pairs that still finish in the same number of rounds: 256 tiles take 4 rounds on 74 pairs
+  // and on 64, and the SMs left over are free for whatever runs beside this product
+  pairs = ceil_div(tiles, ceil_div(tiles, pairs));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
   cfg.blockDim = dim3(PairCfg::kThreads, 1, 1);
