@@ -360,7 +360,10 @@ class LinearLowbitFunction(torch.autograd.Function):
             mean_event.record()             # work that needs only the mean may overlap the quantization
         rotate = LinearLowbitFunction._wgrad_rotation()
         if both and _dual_ok(flat):
-            q, qt = quantizer.quantize_packed_dual(flat, mean=mean, hadamard_signs=rotate)
+            # a centred operand's weight-gradient product needs the token sums of the transposed quantization
+            q, qt = quantizer.quantize_packed_dual(flat, mean=mean, hadamard_signs=rotate, token_sums=mean is not None)
+            if getattr(qt, "token_sums", None) is not None:
+                qt._row_sums = qt.token_sums
         else:
             q, qt = quantizer.quantize_packed(flat, mean=mean), None
         packed = PackedOperand(q, flat, quantizer, tensor.shape, rotate=rotate)
@@ -496,11 +499,11 @@ _ONES = {}
 _AUX_STREAMS = {}
 
 
-def _aux_stream(device: torch.device) -> "torch.cuda.Stream":
-    """The second stream of `device` for work that may overlap the current stream's (one per device)."""
-    st = _AUX_STREAMS.get(device)
+def _aux_stream(device: torch.device, index: int = 0) -> "torch.cuda.Stream":
+    """The second (index 0) or third stream of `device` for work that may overlap the current stream's."""
+    st = _AUX_STREAMS.get((device, index))
     if st is None:
-        st = _AUX_STREAMS[device] = torch.cuda.Stream(device=device)
+        st = _AUX_STREAMS[(device, index)] = torch.cuda.Stream(device=device)
     return st
 
 
@@ -870,12 +873,19 @@ class MetisFusedFunction(torch.autograd.Function):
             dg_done.record(main)
             for_dx = {}
 
+            if dg.mean is not None:
+                # mu_D R^ for the input gradient needs the mean of g only: a pass over the residual weight that
+                # belongs to neither chain, so it gets a stream of its own and runs wherever there is room
+                third = _aux_stream(g.device, 1)
+                third.wait_event(dg.mean_event)
+                with torch.cuda.stream(third):
+                    mean_row = ops.nvfp4_gemv(rq.transposed(), dg.mean)
+                    mean_row_done = torch.cuda.Event()
+                    mean_row_done.record(third)
+
             def input_gradient_operands(dv):
                 # What the input-gradient product needs from this stream goes out ahead of this branch's own
                 # weight gradient, which nothing on the other stream waits for until the very end.
-                if dg.mean is not None:
-                    aux.wait_event(dg.mean_event)          # mu_D R^ needs the mean of g only
-                    for_dx["mean_row"] = ops.nvfp4_gemv(rq.transposed(), dg.mean)
                 if fuse_dx:
                     aux.wait_event(dg_done)                # the unit of Q(g)
                     for_dx["t_acc"] = side_operand(dv, dg)
@@ -886,7 +896,9 @@ class MetisFusedFunction(torch.autograd.Function):
                 grad_u, grad_s, dv, grad_v, side = low_rank_branch(input_gradient_operands)
             grad_r = residual_weight_gradient(dg)
             main.wait_event(for_dx["ready"])
-            mean_row, t_acc = for_dx.get("mean_row"), for_dx.get("t_acc")
+            t_acc = for_dx.get("t_acc")
+            if mean_row is not None:
+                main.wait_event(mean_row_done)
             # allocated on the second stream, read by kernels (or by autograd) on this one: the allocator must
             # not hand their memory to the next second-stream allocation while this stream still uses it
             handed_over = [mean_row, t_acc, dv.q.codes, dv._qt.codes if dv._qt is not None else None]

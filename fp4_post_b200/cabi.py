@@ -85,7 +85,7 @@ def lib() -> C.CDLL:
     L.metis_nvfp4_quantize.restype = i32
     L.metis_nvfp4_quantize_dual_workspace_bytes.argtypes = [i64, i64]
     L.metis_nvfp4_quantize_dual_workspace_bytes.restype = i64
-    L.metis_nvfp4_quantize_dual.argtypes = [vp, i32, i64, i64, i64, vp, u32, u64, u64, i32, vp, vp, vp, vp, vp, vp, vp, i64, vp]
+    L.metis_nvfp4_quantize_dual.argtypes = [vp, i32, i64, i64, i64, vp, u32, u64, u64, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]
     L.metis_nvfp4_quantize_dual.restype = i32
     L.metis_nvfp4_quantize_static.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, vp, vp]
     L.metis_nvfp4_quantize_static.restype = i32

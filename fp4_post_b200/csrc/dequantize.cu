@@ -64,23 +64,6 @@ __device__ __forceinline__ int twice_e2m1(uint32_t nib) {
   return (nib & 8u) ? -mag : mag;
 }
 
-// Sum of the 16 signed codes of one block, in half units.  prmt looks four codes up at once in the
-// 8-entry magnitude table {0,1,2,3,4,6,8,12}; a selector nibble with bit 3 set yields the sign
-// replica of the table byte, i.e. zero, so the first look-up keeps the positive codes and the second
-// (sign bits flipped) the negative ones.  Byte sums stay below 256, one dp4a adds the four bytes.
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-  return d;
-}
-__device__ __forceinline__ int block_code_sum(uint2 w) {
-  constexpr uint32_t kLo = 0x03020100u, kHi = 0x0C080604u;
-  const uint32_t nx = w.x ^ 0x88888888u, ny = w.y ^ 0x88888888u;
-  const uint32_t pos = prmt(kLo, kHi, w.x) + prmt(kLo, kHi, w.x >> 16) + prmt(kLo, kHi, w.y) + prmt(kLo, kHi, w.y >> 16);
-  const uint32_t neg = prmt(kLo, kHi, nx) + prmt(kLo, kHi, nx >> 16) + prmt(kLo, kHi, ny) + prmt(kLo, kHi, ny >> 16);
-  return __dp4a(pos, 0x01010101u, 0u) - __dp4a(neg, 0x01010101u, 0u);
-}
-
 template <bool kHasV>
 __global__ void __launch_bounds__(256)
 gemv_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,

@@ -373,6 +373,10 @@ struct FinalizeJob {
   int32_t sf_layout;
   uint8_t* scales;  float* unit;
   int32_t bx;                 // threads along a row of groups (a power of two up to the CTA size)
+  // optional by-product: row_sums[r] = the sum of the quantized values of row r (unit included), from the
+  // codes the first pass wrote.  A weight-gradient product needs these sums of its operands when they
+  // were centred; here they cost one extra read of codes that are still in L2 instead of a pass of their own.
+  const uint2* codes;  float* row_sums;
 };
 struct FinalizeJobs { FinalizeJob job[2]; };
 
@@ -390,6 +394,7 @@ __device__ __forceinline__ uint32_t scale_bytes4(const float (&a)[4], int live, 
 // ty + by * gridDim.x, ...: no index divisions, and two rows are in flight per thread.
 __global__ void __launch_bounds__(kQuantThreads)
 finalize_scales_kernel(const FinalizeJob job0, const FinalizeJob job1, uint64_t* __restrict__ offset_ctr) {
+  __shared__ float2 s_sum[kQuantThreads / 32];
   grid_dependency_wait();
   const FinalizeJob& J = blockIdx.y == 0 ? job0 : job1;
   const int bx = J.bx, by = kQuantThreads / bx;
@@ -410,6 +415,7 @@ finalize_scales_kernel(const FinalizeJob job0, const FinalizeJob job1, uint64_t*
   const int64_t R_out = tiled ? ((R + 127) / 128) * 128 : R;
   const bool vec = (sf_cols & 3) == 0;
   const int64_t row_step = (int64_t)gridDim.x * by;
+  const bool sums = J.row_sums != nullptr;                       // the host asks for them only when vec holds
 
   auto load = [&](int64_t r, int g, float (&a)[4]) -> int {       // maxima of group g of row r; returns how many are real
     a[0] = a[1] = a[2] = a[3] = 0.0f;
@@ -435,14 +441,55 @@ finalize_scales_kernel(const FinalizeJob job0, const FinalizeJob job1, uint64_t*
       for (int j = 0; j < live; ++j) scales[r * sf_cols + k0 + j] = (uint8_t)(packed >> (8 * j));
     }
   };
-  for (int64_t r = (int64_t)blockIdx.x * by + ty; r < R_out; r += 2 * row_step) {
-    const int64_t r2 = r + row_step;
-    for (int g = tx; g < groups_per_row; g += bx) {
-      float a[4], b[4];
-      const int la = load(r, g, a);
-      const int lb = r2 < R_out ? load(r2, g, b) : 0;
-      store(r, g, scale_bytes4(a, la, unit), la);
-      if (r2 < R_out) store(r2, g, scale_bytes4(b, lb, unit), lb);
+  // sum of code values x scale of the 4 blocks of group g of row r, in half units of `unit`
+  auto group_sum = [&](int64_t r, int g, uint32_t packed) -> float {
+    const uint4* c = reinterpret_cast<const uint4*>(J.codes + r * sf_cols + (int64_t)g * 4);
+    const uint4 lo = c[0], hi = c[1];
+    float acc = (float)block_code_sum(make_uint2(lo.x, lo.y)) * e4m3_to_float(packed & 0xFFu);
+    acc = fmaf((float)block_code_sum(make_uint2(lo.z, lo.w)), e4m3_to_float((packed >> 8) & 0xFFu), acc);
+    acc = fmaf((float)block_code_sum(make_uint2(hi.x, hi.y)), e4m3_to_float((packed >> 16) & 0xFFu), acc);
+    return fmaf((float)block_code_sum(make_uint2(hi.z, hi.w)), e4m3_to_float(packed >> 24), acc);
+  };
+  // the row loop is uniform over the CTA (the reduction below meets at a barrier)
+  for (int64_t r0 = (int64_t)blockIdx.x * by; r0 < R_out; r0 += 2 * row_step) {
+    const int64_t r = r0 + ty, r2 = r + row_step;
+    float sum_a = 0.0f, sum_b = 0.0f;
+    if (r < R_out) {
+      for (int g = tx; g < groups_per_row; g += bx) {
+        float a[4], b[4];
+        const int la = load(r, g, a);
+        const int lb = r2 < R_out ? load(r2, g, b) : 0;
+        const uint32_t pa = scale_bytes4(a, la, unit);
+        store(r, g, pa, la);
+        if (sums && la) sum_a += group_sum(r, g, pa);
+        if (r2 < R_out) {
+          const uint32_t pb = scale_bytes4(b, lb, unit);
+          store(r2, g, pb, lb);
+          if (sums && lb) sum_b += group_sum(r2, g, pb);
+        }
+      }
+    }
+    if (sums) {
+      // fixed order: lanes of a row by butterfly, then the row's warps one after the other
+      for (int o = (bx < 32 ? bx : 32) >> 1; o > 0; o >>= 1) {
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, o);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, o);
+      }
+      if (bx > 32) {
+        const int warp = threadIdx.x >> 5, per_row = bx >> 5;
+        if ((threadIdx.x & 31) == 0) s_sum[warp] = make_float2(sum_a, sum_b);
+        __syncthreads();
+        if (tx == 0) {
+          sum_a = sum_b = 0.0f;
+          for (int w = 0; w < per_row; ++w) { sum_a += s_sum[ty * per_row + w].x; sum_b += s_sum[ty * per_row + w].y; }
+        }
+        __syncthreads();
+      }
+      if (tx == 0) {
+        const float half_unit = 0.5f * unit;
+        if (r < R) J.row_sums[r] = sum_a * half_unit;
+        if (r2 < R) J.row_sums[r2] = sum_b * half_unit;
+      }
     }
   }
 }
@@ -714,7 +761,7 @@ static int32_t launch_finalize_jobs(FinalizeJobs jobs, int njobs, cudaStream_t s
 int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t sf_layout,
                         uint8_t* scales, float* unit, cudaStream_t st, uint64_t* offset_ctr) {
   FinalizeJobs jobs = {};
-  jobs.job[0] = {ws.amax, ws.gmax, ws.gmax + 1, R, C / 16, sf_layout, scales, unit, 0};
+  jobs.job[0] = {ws.amax, ws.gmax, ws.gmax + 1, R, C / 16, sf_layout, scales, unit, 0, nullptr, nullptr};
   return launch_finalize_jobs(jobs, 1, st, offset_ctr);
 }
 
@@ -825,8 +872,8 @@ extern "C" int64_t metis_nvfp4_quantize_dual_workspace_bytes(int64_t rows, int64
 extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
                                              const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,
                                              int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,
-                                             uint8_t* codes_t, uint8_t* scales_t, float* unit_t, void* workspace,
-                                             int64_t workspace_bytes, void* stream) {
+                                             uint8_t* codes_t, uint8_t* scales_t, float* unit_t, float* token_sums_t,
+                                             void* workspace, int64_t workspace_bytes, void* stream) {
   const bool sr = flags & METIS_Q_STOCHASTIC;
   uint64_t* ctr = (sr && (flags & METIS_Q_OFFSET_ON_DEVICE)) ? reinterpret_cast<uint64_t*>(static_cast<uintptr_t>(offset)) : nullptr;
   if (ctr) offset = 0;
@@ -835,6 +882,8 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
   if (flags & ~(METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x (the dual quantizer always writes both orientations)", flags);
   if ((flags & METIS_Q_SIGN_MASK) && !(flags & METIS_Q_HADAMARD)) return fail(METIS_ERR_BAD_ARGUMENT, "sign bits without METIS_Q_HADAMARD");
   const uint32_t rht = (flags & METIS_Q_HADAMARD) ? ((1u << 16) | (flags >> 16)) : 0u;      // the transposed output only
+  if (token_sums_t && rht) return fail(METIS_ERR_BAD_ARGUMENT, "token_sums_t is not available with METIS_Q_HADAMARD (the rotated blocks need weighted sums)");
+  if (token_sums_t && rows % 64 != 0) return fail(METIS_ERR_BAD_SHAPE, "token_sums_t needs rows to be a multiple of 64");
   if (!x) return fail(METIS_ERR_BAD_ARGUMENT, "x is null");
   if (x_dtype != METIS_DTYPE_BF16 && x_dtype != METIS_DTYPE_F32) return fail(METIS_ERR_BAD_ARGUMENT, "unknown x_dtype %d", x_dtype);
   if (rows <= 0 || cols <= 0) return fail(METIS_ERR_BAD_SHAPE, "empty tensor [%lld, %lld]", (long long)rows, (long long)cols);
@@ -865,8 +914,9 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
   if (rc) return rc;
   METIS_CUDA_OK(cudaGetLastError());
   FinalizeJobs jobs = {};
-  jobs.job[0] = {amax_r, head, head + 1, rows, cols / 16, sf_layout, scales, unit, 0};
-  jobs.job[1] = {amax_t, head + 2, head + 1, cols, rows / 16, sf_layout, scales_t, unit_t, 0};
+  jobs.job[0] = {amax_r, head, head + 1, rows, cols / 16, sf_layout, scales, unit, 0, nullptr, nullptr};
+  jobs.job[1] = {amax_t, head + 2, head + 1, cols, rows / 16, sf_layout, scales_t, unit_t, 0,
+                 token_sums_t ? reinterpret_cast<const uint2*>(codes_t) : nullptr, token_sums_t};
   return launch_finalize_jobs(jobs, 2, st, ctr);
 }
 

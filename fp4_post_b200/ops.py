@@ -93,6 +93,7 @@ class NVFP4Tensor:
     sf_layout: int
     row_vec: Optional[torch.Tensor] = None
     col_vec: Optional[torch.Tensor] = None
+    token_sums: Optional[torch.Tensor] = None     # fp32 [R]: sums of the rows' quantized values, when the quantizer formed them
 
     @property
     def device(self):
@@ -177,9 +178,12 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
 
 def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int = 0, offset: int = 0,
                         sf_layout: int = cabi.SF_MMA, mean: Optional[torch.Tensor] = None,
-                        offset_counter: Optional[torch.Tensor] = None, hadamard_signs: Optional[int] = None):
+                        offset_counter: Optional[torch.Tensor] = None, hadamard_signs: Optional[int] = None,
+                        token_sums: bool = False):
     """Both quantizations of x viewed as [rows, cols] from one pass over it: (Q of x, Q of x^T), each
-    bit-identical to the separate call (round to nearest).  rows and cols must be multiples of 16."""
+    bit-identical to the separate call (round to nearest).  rows and cols must be multiples of 16.
+    With token_sums the second result carries `token_sums` (fp32 [cols]), the sums of its rows' quantized
+    values, formed by the scale pass (where the shape allows it: rows a multiple of 64, no rotation)."""
     _need_cuda(x, "x")
     x2 = _rows2d(x)
     rows, cols = x2.shape
@@ -201,10 +205,13 @@ def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int 
         codes, scales, unit = _packed_buffers(L, rows, cols, sf_layout, dev)
         codes_t, scales_t, unit_t = _packed_buffers(L, cols, rows, sf_layout, dev)
         ws = torch.empty(L.metis_nvfp4_quantize_dual_workspace_bytes(rows, cols), dtype=torch.uint8, device=dev)
+        sums = None
+        if token_sums and rows % 64 == 0 and hadamard_signs is None:
+            sums = torch.empty(cols, dtype=torch.float32, device=dev)
         rc = L.metis_nvfp4_quantize_dual(x2.data_ptr(), _dtype_code(x2, "x"), rows, cols, x2.stride(0), _ptr(mean),
                                          flags, seed & (2**64 - 1), offset & (2**64 - 1), sf_layout,
                                          codes.data_ptr(), scales.data_ptr(), unit.data_ptr(),
-                                         codes_t.data_ptr(), scales_t.data_ptr(), unit_t.data_ptr(),
+                                         codes_t.data_ptr(), scales_t.data_ptr(), unit_t.data_ptr(), _ptr(sums),
                                          ws.data_ptr(), ws.numel(), _stream())
     cabi.check(rc, "metis_nvfp4_quantize_dual")
     LAUNCHES["quantize"] += 2
@@ -213,6 +220,7 @@ def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int 
     if mean is not None:
         q.row_vec = mean
         qt.col_vec = mean
+    qt.token_sums = sums
     return q, qt
 
 

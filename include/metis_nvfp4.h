@@ -156,13 +156,18 @@ int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64
  * pass that finishes both outputs.
  *   codes    uint8 [rows, cols/2]   scales    metis_nvfp4_sf_bytes(rows, cols, sf_layout)   unit    fp32 [1]
  *   codes_t  uint8 [cols, rows/2]   scales_t  metis_nvfp4_sf_bytes(cols, rows, sf_layout)   unit_t  fp32 [1]
+ *   token_sums_t  optional fp32 [cols]: sum over the rows of x (the tokens) of the quantized values,
+ *              token_sums_t[k] = sum_m value(Qt[k, m]), what metis_nvfp4_gemv(Qt, v = NULL) returns up to the order
+ *              of the additions (fixed here too).  The weight-gradient product of centred operands needs these
+ *              sums (the rank-1 terms of bitlinear.py:502-505 written out); the scale pass forms them from
+ *              codes that are still in L2.  NULL = not wanted.  Needs rows % 64 == 0 and no METIS_Q_HADAMARD.
  *   workspace  metis_nvfp4_quantize_dual_workspace_bytes(rows, cols)
  */
 int64_t metis_nvfp4_quantize_dual_workspace_bytes(int64_t rows, int64_t cols);
 int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
                                   const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,
                                   int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,
-                                  uint8_t* codes_t, uint8_t* scales_t, float* unit_t,
+                                  uint8_t* codes_t, uint8_t* scales_t, float* unit_t, float* token_sums_t,
                                   void* workspace, int64_t workspace_bytes, void* stream);
 
 /*

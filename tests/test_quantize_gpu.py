@@ -361,3 +361,43 @@ def test_two_operands_rotated_alike_give_sixteen_times_the_plain_product():
     e_rot = (rot.double() - exact).norm() / exact.norm()
     assert e_plain < 0.2 and e_rot < 0.2
     assert e_rot < e_plain * 1.1                                  # the rotation spreads the outlier channels: no worse
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(64, 32), (128, 4096), (1024, 528), (16384, 128), (4096, 4096)])
+@pytest.mark.parametrize("stochastic", [False, True])
+def test_dual_quantizer_forms_the_token_sums_of_the_transposed_output(rows, cols, stochastic):
+    """token_sums_t[k] = sum over the tokens of the quantized values of column k: equal to the row sums the
+    gemv kernel forms from the same codes and scales (other order of the additions), and the same on every run."""
+    torch.manual_seed(rows + cols)
+    x = torch.randn(rows, cols, device=DEV, dtype=torch.bfloat16) * 3 + 0.5
+    mean = ops.col_mean(x)
+    for layout in (cabi.SF_ROWMAJOR, cabi.SF_MMA):
+        q, qt = ops.nvfp4_quantize_dual(x, mean=mean, stochastic=stochastic, seed=11, offset=4, sf_layout=layout, token_sums=True)
+        assert qt.token_sums is not None and qt.token_sums.shape == (cols,)
+        want = ops.nvfp4_gemv(qt, None)
+        dense = ops.nvfp4_dequantize(qt, torch.float32, add_mean=False).double().sum(dim=1)
+        scale = ops.nvfp4_dequantize(qt, torch.float32, add_mean=False).abs().double().sum(dim=1) + 1e-30
+        assert ((qt.token_sums.double() - dense).abs() / scale).max().item() < 1e-5
+        assert ((want.double() - dense).abs() / scale).max().item() < 1e-5
+        q2, qt2 = ops.nvfp4_quantize_dual(x, mean=mean, stochastic=stochastic, seed=11, offset=4, sf_layout=layout, token_sums=True)
+        assert torch.equal(qt.token_sums, qt2.token_sums)
+        # the outputs themselves are what they were without the by-product
+        q3, qt3 = ops.nvfp4_quantize_dual(x, mean=mean, stochastic=stochastic, seed=11, offset=4, sf_layout=layout)
+        assert qt3.token_sums is None
+        assert torch.equal(qt.codes, qt3.codes) and torch.equal(qt.scales, qt3.scales) and torch.equal(q.scales, q3.scales)
+
+
+@pytest.mark.gpu
+def test_token_sums_are_refused_where_the_scale_pass_cannot_form_them():
+    x = torch.randn(48, 64, device=DEV, dtype=torch.bfloat16)
+    q, qt = ops.nvfp4_quantize_dual(x, token_sums=True)          # rows not a multiple of 64: the host wrapper leaves them out
+    assert qt.token_sums is None
+    L = cabi.lib()
+    ws = torch.empty(L.metis_nvfp4_quantize_dual_workspace_bytes(48, 64), dtype=torch.uint8, device=DEV)
+    sums = torch.empty(64, dtype=torch.float32, device=DEV)
+    rc = L.metis_nvfp4_quantize_dual(x.data_ptr(), cabi.DTYPE_BF16, 48, 64, 64, None, 0, 0, 0, cabi.SF_ROWMAJOR,
+                                     q.codes.data_ptr(), q.scales.data_ptr(), q.unit.data_ptr(),
+                                     qt.codes.data_ptr(), qt.scales.data_ptr(), qt.unit.data_ptr(), sums.data_ptr(),
+                                     ws.data_ptr(), ws.numel(), None)
+    assert rc == -2          # METIS_ERR_BAD_SHAPE
