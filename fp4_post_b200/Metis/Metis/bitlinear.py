@@ -837,9 +837,16 @@ class MetisFusedFunction(torch.autograd.Function):
             side = None
             if fuse_dx:
                 side = (u_side, ops.nvfp4_gemv(v_t, dv.mean) if dv.mean is not None else None)
-            if before_weight_gradient is not None:
+            # Single process: the input-gradient product is the last big launch and nothing waits for this branch's
+            # own weight gradient, so its operands go first.  With a gradient reducer the small gradients' collective
+            # should start before that product, in whose shadow it runs: the weight gradient goes first.
+            early = before_weight_gradient is not None and reducer is None
+            if early:
                 before_weight_gradient(dv)
-            return grad_u, grad_s, dv, _packed_dw(dv, xa, M, _grad_dtype(v_weight), sm_limit=busy_limit), side
+            grad_v = _packed_dw(dv, xa, M, _grad_dtype(v_weight), sm_limit=busy_limit)
+            if before_weight_gradient is not None and not early:
+                before_weight_gradient(dv)
+            return grad_u, grad_s, dv, grad_v, side
 
         def residual_weight_gradient(dg):
             # warmup_linear (the residual): quantized backward with grad_output = g
@@ -911,6 +918,26 @@ class MetisFusedFunction(torch.autograd.Function):
             grad_u, grad_s, dv, grad_v, side = low_rank_branch()
             dg = F._pack_centred(g, quantizer, centred, both=True)
             grad_r = residual_weight_gradient(dg)
+
+        def small_gradients():
+            if concurrent:
+                main.wait_stream(aux)                           # the low-rank branch's own gradients
+                for t in (grad_u, grad_s, grad_v):
+                    if t is not None:
+                        t.record_stream(main)
+            if reducer is not None:
+                # the small gradients are final too: their bucket goes out before the input-gradient GEMM
+                if reducer.across_layers:
+                    for prm, t in ((v_weight, grad_v), (ctx.s_param, grad_s), (ctx.u_param, grad_u)):
+                        reducer.adopt(prm, t)
+                    reducer.ready(grad_bias)
+                else:
+                    for t in (grad_v, grad_s, grad_u, grad_bias):
+                        reducer.ready(t)
+                reducer.start_small()
+
+        if reducer is not None:
+            small_gradients()
         # with a gradient all-reduce in flight the input-gradient GEMM leaves it some SMs
         sm_limit = reducer.gemm_sm_limit(g.device) if reducer is not None else 0
         if fuse_dx:
@@ -922,21 +949,8 @@ class MetisFusedFunction(torch.autograd.Function):
         else:
             gx_v = _packed_dx(dv, vq, act, sm_limit=sm_limit)
             gx = _packed_dx(dg, rq, act, addend=gx_v, mean_row=mean_row, sm_limit=sm_limit)          # summed in the epilogue
-        if concurrent:
-            main.wait_stream(aux)                           # the low-rank branch's own gradients
-            for t in (grad_u, grad_s, grad_v):
-                if t is not None:
-                    t.record_stream(main)
-        if reducer is not None:
-            # the small gradients are final too
-            if reducer.across_layers:
-                for prm, t in ((v_weight, grad_v), (ctx.s_param, grad_s), (ctx.u_param, grad_u)):
-                    reducer.adopt(prm, t)
-                reducer.ready(grad_bias)
-            else:
-                for t in (grad_v, grad_s, grad_u, grad_bias):
-                    reducer.ready(t)
-            reducer.start_small()
+        if reducer is None:
+            small_gradients()
         grad_x = gx.reshape(xa.shape)
         if reducer is not None and reducer.across_layers and reducer.active():
             # the gradients sit in .grad already; the wait for their collectives moves to the end of the pass
