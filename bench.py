@@ -30,6 +30,9 @@ The JSON line also carries
 `--impl reference` times that CPU implementation as the whole job (rank 0 only).
 `--only gemm_yardstick` times the vendor library's block-scaled NVFP4 GEMM (torch._scaled_mm) at the
 benchmark's shapes: what a library kernel reaches on the same box and clocks (never on the product path).
+`--only gemm_sustained` runs both for seconds with clocks and power sampled; `--only gemm_accounting` (needs
+the timing-knobs build) says where a GEMM tile's cycles go; `--only step_timeline` lists the kernels of one
+graph replay of the step in start order.
 """
 from __future__ import annotations
 
@@ -414,6 +417,176 @@ def run_gemm_yardstick(args):
         print(json.dumps(line), flush=True)
 
 
+def _sustained(fn, name, index, seconds=2.5, burst=50):
+    """Runs `fn` back to back for `seconds` (bursts captured in a CUDA graph) with the GPU's clocks and power
+    sampled beside it; one dict with the time per call of a short burst and of the long run."""
+    import torch
+    from fp4_post_b200.graphs import GraphedStep
+
+    def many():
+        for _ in range(burst):
+            fn()
+    g = GraphedStep(many, warmup=1)
+    g()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); g(); e1.record()
+    torch.cuda.synchronize()
+    burst_ms = e0.elapsed_time(e1) / burst
+    reps = max(3, int(seconds * 1e3 / (burst_ms * burst)))
+    with ClockSampler(index) as clocks:
+        time.sleep(0.3)
+        clocks.rows.clear()                          # samples of the loaded GPU only
+        e0.record()
+        for _ in range(reps):
+            g()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / (reps * burst)
+    rows = clocks.rows[2:] if len(clocks.rows) > 6 else clocks.rows
+    power = [float(r[2]) for r in rows if r[2].replace(".", "", 1).isdigit()]
+    g.release()
+    time.sleep(1.0)
+    return {"variant": name, "burst_us": round(burst_ms * 1e3, 2), "sustained_us": round(ms * 1e3, 2),
+            "power_w_median": statistics.median(power) if power else None, "clocks": clocks.summary()}
+
+
+def run_gemm_sustained(args):
+    """`--only gemm_sustained`: the forward GEMM shape in a seconds-long loop, this library's kernel and the vendor
+    library's block-scaled NVFP4 GEMM (torch._scaled_mm) on the SAME codes and scales, with SM clock and board
+    power sampled during each loop.  Both run into the board's power limit; what differs is the clock they are
+    left with and the cycles they need."""
+    import torch
+    from fp4_post_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    M, N, K = args.rows, args.n, args.cols
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=dev, dtype=torch.bfloat16) / K ** 0.5
+    qa, qb = ops.nvfp4_quantize(a), ops.nvfp4_quantize(b)
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    lr = (torch.randn(M, args.rank, device=dev, dtype=torch.bfloat16), torch.randn(N, args.rank, device=dev, dtype=torch.bfloat16))
+    lines = [_sustained(lambda: ops.nvfp4_gemm(qa, qb, out=out), "this library, no side product", 0),
+             _sustained(lambda: ops.nvfp4_gemm(qa, qb, lowrank=lr, out=out), f"this library, rank-{args.rank} side product", 0)]
+    fp4 = getattr(torch, "float4_e2m1fn_x2", None)
+    if fp4 is not None:
+        try:
+            A, B = qa.codes.view(fp4), qb.codes.view(fp4)
+            sa, sb = qa.scales.view(torch.float8_e4m3fn), qb.scales.view(torch.float8_e4m3fn)
+            lines.append(_sustained(lambda: torch._scaled_mm(A, B.t(), sa, sb, out_dtype=torch.bfloat16),
+                                    "vendor library (torch._scaled_mm), same codes and scales, no side product", 0))
+        except Exception as exc:
+            lines.append({"variant": "vendor library", "unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"})
+    lines.append(_sustained(lambda: torch.matmul(a, b.t(), out=out), "torch.matmul bf16 (cuBLAS)", 0))
+    for line in lines:
+        line.update(only="gemm_sustained", M=M, N=N, K=K)
+        if "sustained_us" in line:
+            flops = 2 * M * N * (K + (args.rank if "rank-" in line["variant"] else 0))
+            line["tflops_burst"] = round(flops / line["burst_us"] / 1e6, 1)
+            line["tflops_sustained"] = round(flops / line["sustained_us"] / 1e6, 1)
+        print(json.dumps(line), flush=True)
+
+
+def run_gemm_accounting(args):
+    """`--only gemm_accounting`: where the cycles of a 256 x 256 tile of the CTA-pair GEMM go.  Needs the build
+    with the timing knobs (python -m fp4_post_b200.build --timing-knobs): parts of the kernel are switched off
+    one at a time and the issuing warp of CTA 0 counts its own cycles (clock64) and nanoseconds (globaltimer).
+    Two K per variant separate the cost per 256-element stage from the fixed cost per tile."""
+    import torch
+    from fp4_post_b200 import build as build_mod, cabi
+    if not build_mod.KNOBS_LIB.exists():
+        print(json.dumps({"only": "gemm_accounting", "unavailable": "build it first: python -m fp4_post_b200.build --timing-knobs"}))
+        return
+    cabi.LIB_PATH = build_mod.KNOBS_LIB
+    from fp4_post_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    M, N, rank = args.rows, args.n, 0
+    NO_MMA, NO_LOAD, NO_EPILOGUE, NO_STORE, PROFILE, NO_SCALE_COPY = 2, 4, 16, 32, 128, 0x10000
+    variants = (("everything", 0), ("no scale copies", NO_SCALE_COPY), ("no stores of D", NO_STORE), ("no epilogue arithmetic or stores", NO_EPILOGUE),
+                ("no loads", NO_LOAD), ("no loads, no scale copies", NO_LOAD | NO_SCALE_COPY),
+                ("MMAs only (no loads, scale copies, epilogue)", NO_LOAD | NO_SCALE_COPY | NO_EPILOGUE), ("loads only (no MMAs)", NO_MMA))
+    results = {}
+    for K in (4096, 8192):
+        qa = ops.nvfp4_quantize(torch.randn(M, K, device=dev, dtype=torch.bfloat16))
+        qb = ops.nvfp4_quantize(torch.randn(N, K, device=dev, dtype=torch.bfloat16) / K ** 0.5)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        st = torch.zeros(8, dtype=torch.int32, device=dev)
+        for name, bits in variants:
+            for _ in range(3):
+                ops.nvfp4_gemm(qa, qb, out=out, _debug=bits, status=st)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                ops.nvfp4_gemm(qa, qb, out=out, _debug=bits | PROFILE, status=st)
+            e1.record()
+            torch.cuda.synchronize()
+            w = st.tolist()
+            cyc, ns, tiles = w[2], w[3], max(w[6], 1)
+            results[(name, K)] = {"us_per_launch": round(e0.elapsed_time(e1) / args.steps * 1e3, 1), "sm_mhz_in_kernel": round(cyc / max(ns, 1) * 1e3),
+                                  "kcycles_per_tile": round(cyc / tiles / 1e3, 2), "tiles_of_cta0": tiles}
+    for name, _ in variants:
+        lo, hi = results[(name, 4096)], results[(name, 8192)]
+        per_stage = (hi["kcycles_per_tile"] - lo["kcycles_per_tile"]) * 1e3 / 16
+        print(json.dumps({"only": "gemm_accounting", "M": M, "N": N, "variant": name, "K4096": lo, "K8192": hi,
+                          "cycles_per_stage": round(per_stage), "fixed_kcycles_per_tile": round(lo["kcycles_per_tile"] - 16 * per_stage / 1e3, 2),
+                          "note": "a stage is 4 MMAs of 256x256x64 per CTA pair: 512 tensor-pipe cycles"}), flush=True)
+
+
+def run_step_timeline(args):
+    """`--only step_timeline`: start, duration and name of every kernel of ONE graph replay of the default training
+    step (torch profiler), in start order, and the time between the first start and the last end."""
+    import torch
+    from torch.profiler import profile, ProfilerActivity
+    from fp4_post_b200.graphs import GraphedStep
+    from fp4_post_b200.Metis.Metis.bitlinear import BitLinear
+    from fp4_post_b200.grpo.grpo import MetisArgs
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    M, K, N, R = args.rows, args.cols, args.n, args.rank
+    margs = MetisArgs(forward_svd_rank=R, activation_lowrank_svd=R, backward_lowrank_svd=R, cache_quantized_weight=False)
+    margs.device = dev
+    layer = BitLinear(K, N, args=margs, bias=False, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+    with torch.no_grad():
+        layer.warmup_linear.weight.copy_(torch.randn(N, K, device=dev) / K ** 0.5)
+    layer.layer_name = "p"
+    layer.split()
+    x = torch.randn(1, M, K, device=dev, dtype=torch.bfloat16).requires_grad_(True)
+    g = torch.randn(1, M, N, device=dev, dtype=torch.bfloat16)
+    params = list(layer.parameters())
+
+    def step():
+        for p in params:
+            p.grad = None
+        x.grad = None
+        y = layer(x)
+        y.backward(g)
+        return y
+    gs = GraphedStep(step, warmup=3)
+    for _ in range(5):
+        gs()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        gs()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"only": "step_timeline", "ms_per_step": e0.elapsed_time(e1) / args.steps}), flush=True)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        gs(); gs()
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type.name == "CUDA" and e.device_time > 0), key=lambda e: e.time_range.start)
+    ev = ev[len(ev) // 2:]                            # the second replay
+    t0 = ev[0].time_range.start
+    print(f"{'start us':>9} {'dur us':>8}  kernel")
+    for e in ev:
+        print(f"{e.time_range.start - t0:9.1f} {e.device_time:8.1f}  {e.name[:100]}")
+    print(f"span {max(e.time_range.end for e in ev) - t0:.1f} us, {len(ev)} kernels and memsets")
+    gs.release()
+
+
 def run_decoder_step(args):
     """`--only c4` / `--only c5_update`: one training step (forward, next-token loss, backward) of a Qwen2-style
     decoder with random weights whose seven projections per block are Metis rank-r NVFP4 layers, on synthetic
@@ -589,7 +762,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer", "c4", "c5_update"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "gemm_sustained", "gemm_accounting", "step_timeline", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer", "c4", "c5_update"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--layers", type=int, default=1,
                     help="stack this many Metis layers (the headline is 1): with several GPUs the gradient all-reduce "
@@ -610,6 +783,12 @@ def main():
         return run_gemm_sweep(args)
     if args.only == "gemm_yardstick":
         return run_gemm_yardstick(args)
+    if args.only == "gemm_sustained":
+        return run_gemm_sustained(args)
+    if args.only == "gemm_accounting":
+        return run_gemm_accounting(args)
+    if args.only == "step_timeline":
+        return run_step_timeline(args)
     if args.only == "rmsnorm_sweep":
         return run_rmsnorm_sweep(args)
     if args.only == "decode_layer":
