@@ -56,7 +56,7 @@ METRIC = "metis_nvfp4_linear_fwd_bwd_tflops"
 BYTES_PER_ELEM_BF16 = 2.5625          # 2 (bf16 in) + 0.5 (codes) + 1/16 (E4M3 scale)
 BYTES_PER_ELEM_DUAL_BF16 = 3.125      # one read, two packed outputs (row-major and transposed)
 # DRAM bytes (read + write) of one forward GEMM launch, from an ncu capture of the same kernel on
-# M = 8192 (31.6 MB read + 21.8 MB written) scaled by the rows processed; the profile summary
+# M = 8192 (31.6 MB read + 21.4 MB written) scaled by the rows processed; the profile summary
 # profiles/nvfp4_gemm_pair_8192x4096x4096_r128.md holds the capture and its command.
 GEMM_DRAM_BYTES_PER_LAUNCH = int(52.9e6 * M_TOKENS / 8192)      # 31.57 MB read + 21.36 MB written at M = 8192
 GEMM_DRAM_SOURCE = ("ncu dram__bytes_read.sum + dram__bytes_write.sum at M = 8192, scaled by M; below the algorithmic bytes "
