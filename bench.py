@@ -697,13 +697,16 @@ def run_decoder_step(args):
         ours = sum(e.device_time_total for e in prof.key_averages() if e.key.startswith(("void metis::", "metis::")))
         total = sum(e.device_time_total for e in prof.key_averages())
         share = ours / max(total, 1e-9)
+        top = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)[:14]
+        top_kernels = [{"kernel": e.key[:70], "launches": e.count, "ms": round(e.device_time_total / 1e3, 2)} for e in top]
     if rank == 0:
         tokens = world * batch * seq
         lin = 3 * cfg.linear_flops_per_token(r) * tokens
         print(json.dumps({"only": args.only, "n_gpus": world, "tokens_per_step": tokens, "batch_per_gpu": batch, "seq_len": seq,
                           "layers": cfg.layers, "hidden": cfg.hidden, "rank": r, "ms_per_step": ms,
                           "tokens_per_s": tokens / ms * 1e3, "metis_linear_tflops": lin / ms / 1e9,
-                          "share_of_device_time_in_library_kernels": share, "launch_mode": mode,
+                          "share_of_device_time_in_library_kernels": share, "device_ms_of_one_eager_step": round(total / 1e3, 1),
+                          "top_kernels_of_one_eager_step": top_kernels, "launch_mode": mode,
                           "fused_norms": not args.no_fused_norm, "data": "synthetic token ids, random weights"}), flush=True)
     if world > 1:
         if isinstance(runner, GraphedStep):

@@ -55,6 +55,10 @@ class PackedOperand:
         self.mean_event = None         # recorded when the column mean exists (before the quantization that uses it)
         self.fresh = True              # produced by kernels of the current call (cleared by a weight-cache hit)
         self.ready_event = None        # quantized on the second stream: what the current stream waits for before its first use
+        # Scale pass of one of the two outputs left to another stream (ops.nvfp4_quantize_dual(defer=...)): the
+        # event after which that output is complete.  Every consumer's stream waits for it.
+        self._q_event = None
+        self._qt_event = None
 
     @property
     def dtype(self):
@@ -74,7 +78,23 @@ class PackedOperand:
                                    f"the forward (version {self.source._version}, expected {self._version})")
             self._qt = self.quantizer.quantize_packed(self.source, transpose=True, mean=self.q.row_vec,
                                                       hadamard_signs=self.rotate)
+        if self._qt_event is not None:
+            torch.cuda.current_stream(self._qt.codes.device).wait_event(self._qt_event)
         return self._qt
+
+    def rowmajor(self):
+        """`q`, once its scale pass has run (see _q_event)."""
+        if self._q_event is not None:
+            torch.cuda.current_stream(self.q.codes.device).wait_event(self._q_event)
+        return self.q
+
+    def join_deferred(self):
+        """Order the current stream after every scale pass of this operand that was left to another stream.
+        Called where a forward or backward function ends, after its last launch: by then the pass is long
+        finished, and a stream capture that ends there sees the other stream joined."""
+        for ev in (self._q_event, self._qt_event):
+            if ev is not None:
+                torch.cuda.current_stream(self.q.codes.device).wait_event(ev)
 
     def dense(self, dtype):
         """The dequantized tensor the reference would have produced (mean added back)."""
@@ -164,6 +184,10 @@ class LinearLowbitFunction(torch.autograd.Function):
     # product).  The forward-weight rotation of `enable_nv_recipe` (bitlinear.py:578-585) has no packed form
     # (the activation is quantized unrotated) and stays on the dense torch path.
     packed_wgrad_rht = False
+    # Packed mode, CUDA: an operand that is quantized in both orientations hands the scale pass of the
+    # orientation its first consumer does not need to a third stream (the transposed one of a forward
+    # activation, the row-major one of an output gradient).  Results do not change.
+    defer_scale_pass = True
 
     @staticmethod
     def _wgrad_rotation():
@@ -333,12 +357,12 @@ class LinearLowbitFunction(torch.autograd.Function):
 
     @staticmethod
     def _pack_centred(tensor, quantizer, centred: bool, mean_cache=None, cache_key="default", both=False,
-                      fresh_mean=None):
+                      fresh_mean=None, defer=None):
         """NVFP4 of `tensor` ([..., C] viewed as rows), optionally after subtracting the column
         mean (rolling at decode).  The native counterpart of svd_quant(metis_mode="mean").
         `both`: the transposed quantization (needed by the backward products) comes out of the same
         pass over the tensor, where both dimensions are multiples of 16.  `fresh_mean`: the column
-        mean of `tensor` when its producer computed it already (the fused RMSNorm does)."""
+        mean of `tensor` when its producer computed it already (the fused RMSNorm does).  `defer`: see below."""
         flat = tensor.reshape(-1, tensor.shape[-1])
         mean = None
         if centred:
@@ -361,14 +385,36 @@ class LinearLowbitFunction(torch.autograd.Function):
         rotate = LinearLowbitFunction._wgrad_rotation()
         if both and _dual_ok(flat):
             # a centred operand's weight-gradient product needs the token sums of the transposed quantization
-            q, qt = quantizer.quantize_packed_dual(flat, mean=mean, hadamard_signs=rotate, token_sums=mean is not None)
+            # `defer`: the consumer that comes first needs one of the two outputs only; the scale pass of the other
+            # ("rowmajor" or "transposed") runs on the third stream, off this stream's critical path
+            defer = defer if flat.is_cuda else None
+            res = quantizer.quantize_packed_dual(flat, mean=mean, hadamard_signs=rotate, token_sums=mean is not None, defer=defer)
+            done = None
+            if defer is not None:
+                q, qt, finish = res
+                main, third = torch.cuda.current_stream(flat.device), _aux_stream(flat.device, 2)
+                issued = torch.cuda.Event()
+                issued.record(main)
+                third.wait_event(issued)
+                with torch.cuda.stream(third):
+                    finish()
+                    done = torch.cuda.Event()
+                    done.record(third)
+            else:
+                q, qt = res
             if getattr(qt, "token_sums", None) is not None:
                 qt._row_sums = qt.token_sums
+                if defer == "transposed":
+                    qt._row_sums_event = done
         else:
-            q, qt = quantizer.quantize_packed(flat, mean=mean), None
+            q, qt, defer, done = quantizer.quantize_packed(flat, mean=mean), None, None, None
         packed = PackedOperand(q, flat, quantizer, tensor.shape, rotate=rotate)
         packed._qt = qt
         packed.mean_event = mean_event
+        if defer == "transposed":
+            packed._qt_event = done
+        elif defer == "rowmajor":
+            packed._q_event = done
         return packed
 
     @staticmethod
@@ -394,7 +440,7 @@ class LinearLowbitFunction(torch.autograd.Function):
         if F._use_packed(input_, F.q_forward_input) and (not centred or F.metis_mode == "mean"):
             # with autograd recording, the weight-gradient product will want x quantized along the tokens
             return F._pack_centred(input_, F.q_forward_input, centred, mean_cache, cache_key,
-                                   both=torch.is_grad_enabled())
+                                   both=torch.is_grad_enabled(), defer="transposed" if F.defer_scale_pass else None)
         if centred:
             return F.svd_quant(input_, quant_func=F.q_forward_input, rank=F.activation_lowrank_svd,
                                niter=F.activation_lowrank_niter, broadcast_dim=F.activation_broadcast_dim,
@@ -436,7 +482,8 @@ class LinearLowbitFunction(torch.autograd.Function):
             if bias is not None:
                 rank1.append((None, bias.float()))
             out_dtype = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
-            y = _packed_matmul(xa.q, wq.q, rank1=rank1, out_dtype=out_dtype)
+            y = _packed_matmul(xa.rowmajor(), wq.q, rank1=rank1, out_dtype=out_dtype)
+            xa.join_deferred()
             return y.reshape(*xa.shape[:-1], wq.q.shape[0]).to(xa.dtype)
         # dense mode: the reference's wiring
         if isinstance(xa, PackedOperand):
@@ -500,7 +547,7 @@ _AUX_STREAMS = {}
 
 
 def _aux_stream(device: torch.device, index: int = 0) -> "torch.cuda.Stream":
-    """The second (index 0) or third stream of `device` for work that may overlap the current stream's."""
+    """The second (index 0), third or fourth stream of `device` for work that may overlap the current stream's."""
     st = _AUX_STREAMS.get((device, index))
     if st is None:
         st = _AUX_STREAMS[(device, index)] = torch.cuda.Stream(device=device)
@@ -606,7 +653,7 @@ def _packed_dx(da: PackedOperand, wq: PackedOperand, out_dtype, addend=None, sid
         if extra is not None:
             row = extra if row is None else row + extra
     rank1 = [(None, row)] if row is not None else []
-    return _packed_matmul(da.q, w_t, rank1=rank1, lowrank=lowrank, c=addend, out_dtype=out_dtype, sm_limit=sm_limit)
+    return _packed_matmul(da.rowmajor(), w_t, rank1=rank1, lowrank=lowrank, c=addend, out_dtype=out_dtype, sm_limit=sm_limit)
 
 
 def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int, out_dtype=torch.float32, sm_limit=0):
@@ -783,6 +830,7 @@ class MetisFusedFunction(torch.autograd.Function):
         if (MetisFusedFunction.concurrent_branches and xa.q.codes.is_cuda and any(ctx.needs_input_grad)
                 and xa._qt is not None and LinearLowbitFunction._backward_centred()):
             _row_sums_beside(xa)        # queued behind the product: it runs as that one drains, not in front of it
+        xa.join_deferred()              # a scale pass left to the third stream has long finished; this joins that stream
         ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
         ctx.has_bias = bias is not None
         ctx.dims = (M, N, K)
@@ -861,7 +909,7 @@ class MetisFusedFunction(torch.autograd.Function):
         def side_operand(dv, dg):
             # D^v in the units the fused dX launch accumulates in.  e2m1 x e4m3 is exact in bf16; the ratio of the
             # two products' units goes into T, rounded once to bf16 (the unfused dX_v would be rounded there too).
-            ratio = (dv.q.unit * vq.transposed().unit) / (dg.q.unit * rq.transposed().unit)
+            ratio = (dv.q.unit * vq.transposed().unit) / (dg.rowmajor().unit * rq.transposed().unit)
             return ops.nvfp4_dequantize(dv.q, torch.bfloat16, add_mean=False, unit=ratio)
 
         mean_row = t_acc = None
@@ -875,7 +923,8 @@ class MetisFusedFunction(torch.autograd.Function):
                 _row_sums(x_t, xa.rotate)   # cached on x_t and read by both branches
             main, aux = torch.cuda.current_stream(), _aux_stream(g.device)
             aux.wait_stream(main)
-            dg = F._pack_centred(g, quantizer, centred, both=True)
+            # the weight-gradient product comes first and reads the transposed output only
+            dg = F._pack_centred(g, quantizer, centred, both=True, defer="rowmajor" if F.defer_scale_pass else None)
             dg_done = torch.cuda.Event()
             dg_done.record(main)
             for_dx = {}

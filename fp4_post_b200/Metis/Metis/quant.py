@@ -327,15 +327,15 @@ class _NativeNVFP4(BlockQuantFunc):
     @classmethod
     @torch.no_grad()
     def quantize_packed_dual(cls, x: torch.Tensor, *, mean: torch.Tensor | None = None, sf_layout: int = cabi.SF_MMA,
-                             hadamard_signs: int | None = None, token_sums: bool = False):
+                             hadamard_signs: int | None = None, token_sums: bool = False, defer: str | None = None):
         """(quantize_packed(x), quantize_packed(x, transpose=True)) from one pass over x: what a training
         step needs of every operand (the products of the backward contract over the other dimension).
-        token_sums: see ops.nvfp4_quantize_dual."""
+        token_sums, defer: see ops.nvfp4_quantize_dual."""
         cls._check(x)
         return ops.nvfp4_quantize_dual(cls._native_input(x), stochastic=cls.stochastic,
                                        seed=cls.philox_key(), sf_layout=sf_layout, mean=mean,
                                        offset_counter=cls._offset_counter(x.device) if cls.stochastic else None,
-                                       hadamard_signs=hadamard_signs, token_sums=token_sums)
+                                       hadamard_signs=hadamard_signs, token_sums=token_sums, defer=defer)
 
     @classmethod
     @torch.no_grad()

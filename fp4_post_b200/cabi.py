@@ -13,6 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libmetis_nvfp4.so"
 DTYPE_BF16, DTYPE_F32 = 0, 1
 SF_ROWMAJOR, SF_MMA = 0, 1
 Q_TRANSPOSE, Q_STOCHASTIC, Q_OFFSET_ON_DEVICE, Q_HADAMARD = 1, 2, 4, 8
+Q_DEFER_ROWMAJOR, Q_DEFER_TRANSPOSED = 16, 32
 STATIC_MAX_ELEMENTS = 16 * 1024 * 1024
 
 STATUS_TEXT = {
@@ -28,7 +29,7 @@ EXPORTS = (
     "metis_nvfp4_dequantize", "metis_col_mean_workspace_bytes", "metis_col_mean", "metis_nvfp4_gemv",
     "metis_nvfp4_gemm", "metis_nvfp4_quantize_static", "metis_nvfp4_gemm_workspace_bytes",
     "metis_lowrank_scale",
-    "metis_nvfp4_quantize_dual_workspace_bytes", "metis_nvfp4_quantize_dual",
+    "metis_nvfp4_quantize_dual_workspace_bytes", "metis_nvfp4_quantize_dual", "metis_nvfp4_quantize_dual_finish",
     "metis_rmsnorm_mean_workspace_bytes", "metis_rmsnorm_mean",
     "metis_bf16_panel_gemm_workspace_bytes", "metis_bf16_panel_gemm",
     "metis_lowrank_dts_workspace_bytes", "metis_lowrank_dts", "metis_lowrank_du_workspace_bytes", "metis_lowrank_du",
@@ -87,6 +88,8 @@ def lib() -> C.CDLL:
     L.metis_nvfp4_quantize_dual_workspace_bytes.restype = i64
     L.metis_nvfp4_quantize_dual.argtypes = [vp, i32, i64, i64, i64, vp, u32, u64, u64, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, vp]
     L.metis_nvfp4_quantize_dual.restype = i32
+    L.metis_nvfp4_quantize_dual_finish.argtypes = [i64, i64, u32, i32, vp, vp, vp, vp, vp, vp, vp, i64, vp]
+    L.metis_nvfp4_quantize_dual_finish.restype = i32
     L.metis_nvfp4_quantize_static.argtypes = [vp, i32, i64, i64, i64, i32, vp, vp, vp, vp]
     L.metis_nvfp4_quantize_static.restype = i32
     L.metis_rmsnorm_nvfp4_quantize.argtypes = [vp, i32, i64, i64, i64, vp, i32, f32, i32, vp, vp, vp, vp, vp, i64, vp]

@@ -864,6 +864,23 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   return launch_finalize(ws, R, C, sf_layout, scales, unit, st, ctr);
 }
 
+// Scale pass of the dual quantizer's outputs (either or both) from the block maxima in its workspace.
+static int32_t finish_dual(int64_t rows, int64_t cols, int32_t sf_layout, uint8_t* scales, float* unit, const uint8_t* codes_t,
+                           uint8_t* scales_t, float* unit_t, float* token_sums_t, void* workspace, bool rowmajor,
+                           bool transposed, cudaStream_t st, uint64_t* ctr) {
+  unsigned int* head = static_cast<unsigned int*>(workspace);
+  float* amax_r = reinterpret_cast<float*>(static_cast<char*>(workspace) + kHeaderBytes);
+  float* amax_t = amax_r + rows * (cols / 16);
+  FinalizeJobs jobs = {};
+  int n = 0;
+  if (rowmajor) jobs.job[n++] = {amax_r, head, head + 1, rows, cols / 16, sf_layout, scales, unit, 0, nullptr, nullptr};
+  if (transposed)
+    jobs.job[n++] = {amax_t, head + 2, head + 1, cols, rows / 16, sf_layout, scales_t, unit_t, 0,
+                     token_sums_t ? reinterpret_cast<const uint2*>(codes_t) : nullptr, token_sums_t};
+  if (n == 0) return METIS_OK;
+  return launch_finalize_jobs(jobs, n, st, ctr);      // job 0 of the launch bumps the Philox offset counter, if there is one
+}
+
 extern "C" int64_t metis_nvfp4_quantize_dual_workspace_bytes(int64_t rows, int64_t cols) {
   if (rows <= 0 || cols <= 0) return kHeaderBytes;
   return kHeaderBytes + 2 * rows * ceil_div(cols, 16) * (int64_t)sizeof(float);
@@ -879,7 +896,8 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
   if (ctr) offset = 0;
   if ((flags & METIS_Q_OFFSET_ON_DEVICE) && (!sr || !ctr || (reinterpret_cast<uintptr_t>(ctr) & 7u)))
     return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_OFFSET_ON_DEVICE needs METIS_Q_STOCHASTIC and an 8-byte aligned device address in offset");
-  if (flags & ~(METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x (the dual quantizer always writes both orientations)", flags);
+  if (flags & ~(METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK | METIS_Q_DEFER_ROWMAJOR | METIS_Q_DEFER_TRANSPOSED)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x (the dual quantizer always writes both orientations)", flags);
+  if ((flags & METIS_Q_DEFER_ROWMAJOR) && (flags & METIS_Q_DEFER_TRANSPOSED)) return fail(METIS_ERR_BAD_ARGUMENT, "only one of the two scale passes can be deferred");
   if ((flags & METIS_Q_SIGN_MASK) && !(flags & METIS_Q_HADAMARD)) return fail(METIS_ERR_BAD_ARGUMENT, "sign bits without METIS_Q_HADAMARD");
   const uint32_t rht = (flags & METIS_Q_HADAMARD) ? ((1u << 16) | (flags >> 16)) : 0u;      // the transposed output only
   if (token_sums_t && rht) return fail(METIS_ERR_BAD_ARGUMENT, "token_sums_t is not available with METIS_Q_HADAMARD (the rotated blocks need weighted sums)");
@@ -913,11 +931,26 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
       : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
   if (rc) return rc;
   METIS_CUDA_OK(cudaGetLastError());
-  FinalizeJobs jobs = {};
-  jobs.job[0] = {amax_r, head, head + 1, rows, cols / 16, sf_layout, scales, unit, 0, nullptr, nullptr};
-  jobs.job[1] = {amax_t, head + 2, head + 1, cols, rows / 16, sf_layout, scales_t, unit_t, 0,
-                 token_sums_t ? reinterpret_cast<const uint2*>(codes_t) : nullptr, token_sums_t};
-  return launch_finalize_jobs(jobs, 2, st, ctr);
+  return finish_dual(rows, cols, sf_layout, scales, unit, codes_t, scales_t, unit_t, token_sums_t, workspace,
+                     !(flags & METIS_Q_DEFER_ROWMAJOR), !(flags & METIS_Q_DEFER_TRANSPOSED), st, ctr);
+}
+
+extern "C" int32_t metis_nvfp4_quantize_dual_finish(int64_t rows, int64_t cols, uint32_t deferred, int32_t sf_layout,
+                                                    uint8_t* scales, float* unit, const uint8_t* codes_t, uint8_t* scales_t,
+                                                    float* unit_t, float* token_sums_t, void* workspace,
+                                                    int64_t workspace_bytes, void* stream) {
+  const bool rowmajor = deferred == METIS_Q_DEFER_ROWMAJOR, transposed = deferred == METIS_Q_DEFER_TRANSPOSED;
+  if (!rowmajor && !transposed) return fail(METIS_ERR_BAD_ARGUMENT, "deferred must be METIS_Q_DEFER_ROWMAJOR or METIS_Q_DEFER_TRANSPOSED");
+  if (rows <= 0 || cols <= 0 || rows % 16 != 0 || cols % 16 != 0) return fail(METIS_ERR_BAD_SHAPE, "bad shape [%lld, %lld]", (long long)rows, (long long)cols);
+  if (sf_layout != METIS_SF_ROWMAJOR && sf_layout != METIS_SF_MMA) return fail(METIS_ERR_BAD_ARGUMENT, "unknown sf_layout %d", sf_layout);
+  if (!workspace || !aligned16(workspace) || workspace_bytes < metis_nvfp4_quantize_dual_workspace_bytes(rows, cols))
+    return fail(METIS_ERR_WORKSPACE, "the workspace of the quantizing call is needed");
+  if (rowmajor && (!scales || !unit || !aligned16(scales))) return fail(METIS_ERR_BAD_ARGUMENT, "scales and unit of the row-major output");
+  if (transposed && (!scales_t || !unit_t || !aligned16(scales_t) || (token_sums_t && !codes_t)))
+    return fail(METIS_ERR_BAD_ARGUMENT, "scales_t and unit_t of the transposed output (and codes_t for token_sums_t)");
+  if (token_sums_t && rows % 64 != 0) return fail(METIS_ERR_BAD_SHAPE, "token_sums_t needs rows to be a multiple of 64");
+  return finish_dual(rows, cols, sf_layout, scales, unit, codes_t, scales_t, unit_t, token_sums_t, workspace,
+                     rowmajor, transposed, reinterpret_cast<cudaStream_t>(stream), nullptr);
 }
 
 extern "C" int64_t metis_col_mean_workspace_bytes(int64_t rows, int64_t cols) {

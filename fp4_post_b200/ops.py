@@ -179,11 +179,14 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
 def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int = 0, offset: int = 0,
                         sf_layout: int = cabi.SF_MMA, mean: Optional[torch.Tensor] = None,
                         offset_counter: Optional[torch.Tensor] = None, hadamard_signs: Optional[int] = None,
-                        token_sums: bool = False):
+                        token_sums: bool = False, defer: Optional[str] = None):
     """Both quantizations of x viewed as [rows, cols] from one pass over it: (Q of x, Q of x^T), each
     bit-identical to the separate call (round to nearest).  rows and cols must be multiples of 16.
     With token_sums the second result carries `token_sums` (fp32 [cols]), the sums of its rows' quantized
-    values, formed by the scale pass (where the shape allows it: rows a multiple of 64, no rotation)."""
+    values, formed by the scale pass (where the shape allows it: rows a multiple of 64, no rotation).
+    defer = "rowmajor" or "transposed": the scale pass of that output (its scales, unit, token sums) is left
+    out; a third value is returned, a function that launches it on the stream that is current when it is
+    called (the caller orders that stream after this call and its consumers after that launch)."""
     _need_cuda(x, "x")
     x2 = _rows2d(x)
     rows, cols = x2.shape
@@ -191,6 +194,10 @@ def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int 
         raise ValueError(f"NVFP4 block shape (1, 16) does not divide both dimensions of tensor shape {(rows, cols)}")
     L = cabi.lib()
     flags = (cabi.Q_STOCHASTIC if stochastic else 0) | _hadamard_flags(hadamard_signs)      # rotation: the transposed output only
+    if defer not in (None, "rowmajor", "transposed"):
+        raise ValueError(f"defer must be 'rowmajor' or 'transposed', not {defer!r}")
+    deferred = {None: 0, "rowmajor": cabi.Q_DEFER_ROWMAJOR, "transposed": cabi.Q_DEFER_TRANSPOSED}[defer]
+    flags |= deferred
     dev = x2.device
     if stochastic and offset_counter is not None:
         if offset_counter.dtype != torch.int64 or offset_counter.device != dev or offset_counter.numel() != 1:
@@ -221,7 +228,22 @@ def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int 
         q.row_vec = mean
         qt.col_vec = mean
     qt.token_sums = sums
-    return q, qt
+    if defer is None:
+        return q, qt
+
+    def finish():
+        with _on_device(dev):
+            rc2 = L.metis_nvfp4_quantize_dual_finish(rows, cols, deferred, sf_layout, scales.data_ptr(), unit.data_ptr(),
+                                                     codes_t.data_ptr(), scales_t.data_ptr(), unit_t.data_ptr(), _ptr(sums),
+                                                     ws.data_ptr(), ws.numel(), _stream())
+        cabi.check(rc2, "metis_nvfp4_quantize_dual_finish")
+        # the buffers were allocated on the quantizing call's stream and are now also used on this one
+        cur = torch.cuda.current_stream(dev)
+        for t in (ws, scales, unit, codes_t, scales_t, unit_t, sums):
+            if t is not None:
+                t.record_stream(cur)
+        LAUNCHES["quantize"] += 1
+    return q, qt, finish
 
 
 def rmsnorm_nvfp4_quantize(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, *,

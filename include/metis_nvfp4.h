@@ -64,6 +64,8 @@ extern "C" {
 #define METIS_Q_HADAMARD    (1u << 3) /* rotate every 16-element block of the transposed output by the signed
                                          Hadamard matrix before it is quantized; bits [16, 32) of the flags give
                                          the sign of each of the 16 positions (bit set: minus)                  */
+#define METIS_Q_DEFER_ROWMAJOR   (1u << 4) /* dual quantizer: leave the scale pass of the row-major output to ..._dual_finish */
+#define METIS_Q_DEFER_TRANSPOSED (1u << 5) /* dual quantizer: leave the scale pass of the transposed output to ..._dual_finish */
 #define METIS_Q_SIGN_MASK   0xFFFF0000u
 
 /* status codes (host return values are <= 0, device status words are >= 0) */
@@ -162,8 +164,18 @@ int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64
  *              sums (the rank-1 terms of bitlinear.py:502-505 written out); the scale pass forms them from
  *              codes that are still in L2.  NULL = not wanted.  Needs rows % 64 == 0 and no METIS_Q_HADAMARD.
  *   workspace  metis_nvfp4_quantize_dual_workspace_bytes(rows, cols)
+ * With METIS_Q_DEFER_ROWMAJOR or METIS_Q_DEFER_TRANSPOSED (one of them) the call writes the codes of both outputs
+ * but runs the scale pass of the other output only; scales, unit (and token_sums_t) of the deferred output
+ * are written by metis_nvfp4_quantize_dual_finish, given the same shape, layout, pointers and workspace, on
+ * any stream that is ordered after this call.  A forward product needs the row-major output of its activation
+ * at once and the transposed one only in the backward pass; the weight-gradient product needs the transposed
+ * output of the output gradient first: the deferred half leaves the critical path.
  */
 int64_t metis_nvfp4_quantize_dual_workspace_bytes(int64_t rows, int64_t cols);
+int32_t metis_nvfp4_quantize_dual_finish(int64_t rows, int64_t cols, uint32_t deferred, int32_t sf_layout,
+                                         uint8_t* scales, float* unit, const uint8_t* codes_t, uint8_t* scales_t,
+                                         float* unit_t, float* token_sums_t, void* workspace,
+                                         int64_t workspace_bytes, void* stream);
 int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
                                   const float* col_mean, uint32_t flags, uint64_t seed, uint64_t offset,
                                   int32_t sf_layout, uint8_t* codes, uint8_t* scales, float* unit,

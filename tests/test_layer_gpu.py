@@ -536,3 +536,32 @@ def test_wgrad_rotation_keeps_the_weight_gradients_and_leaves_everything_else_al
     e_plain = (res[False]["dR"].double() - exact_dR).norm() / exact_dR.norm()
     e_rot = (res[True]["dR"].double() - exact_dR).norm() / exact_dR.norm()
     assert e_rot < e_plain * 1.1
+
+
+def test_deferred_scale_passes_leave_every_result_bit_for_bit():
+    """The scale pass of the orientation an operand's first consumer does not need runs on a third stream:
+    forward output and all gradients equal those of the undeferred order exactly (round to nearest everywhere)."""
+    torch.manual_seed(11)
+    dev = torch.device(DEV)
+    results = {}
+    for defer in (True, False):
+        torch.manual_seed(11)
+        margs = MetisArgs(forward_svd_rank=32, activation_lowrank_svd=32, backward_lowrank_svd=32)
+        margs.device = dev
+        margs.q_backward_input = margs.q_backward_weight = margs.q_backward_outputgrad = "nvfp4e2m1bnosr"
+        layer = BitLinear(512, 384, args=margs, bias=True, dtype=torch.bfloat16, compute_dtype=torch.bfloat16)
+        layer.layer_name = "defer"
+        layer.split()
+        LinearLowbitFunction.defer_scale_pass = defer
+        try:
+            x = (torch.randn(2, 256, 512, device=dev) + 0.25).to(torch.bfloat16).requires_grad_(True)
+            g = torch.randn(2, 256, 384, device=dev).to(torch.bfloat16)
+            y = layer(x)
+            y.backward(g)
+            torch.cuda.synchronize()
+        finally:
+            LinearLowbitFunction.defer_scale_pass = True
+        results[defer] = [y.detach().clone(), x.grad.clone()] + [p.grad.clone() for p in layer.parameters() if p.grad is not None]
+    assert len(results[True]) == len(results[False]) >= 6
+    for a, b in zip(results[True], results[False]):
+        assert torch.equal(a, b)

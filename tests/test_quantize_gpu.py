@@ -401,3 +401,30 @@ def test_token_sums_are_refused_where_the_scale_pass_cannot_form_them():
                                      qt.codes.data_ptr(), qt.scales.data_ptr(), qt.unit.data_ptr(), sums.data_ptr(),
                                      ws.data_ptr(), ws.numel(), None)
     assert rc == -2          # METIS_ERR_BAD_SHAPE
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("defer", ["rowmajor", "transposed"])
+@pytest.mark.parametrize("stochastic", [False, True])
+def test_deferred_scale_pass_writes_what_the_undeferred_call_writes(defer, stochastic):
+    torch.manual_seed(17)
+    x = torch.randn(1024, 768, device=DEV, dtype=torch.bfloat16) * 2 - 0.3
+    mean = ops.col_mean(x)
+    kw = dict(mean=mean, stochastic=stochastic, seed=5, offset=3, token_sums=True)
+    want_q, want_t = ops.nvfp4_quantize_dual(x, **kw)
+    q, qt, finish = ops.nvfp4_quantize_dual(x, defer=defer, **kw)
+    torch.cuda.synchronize()
+    # the half that was not deferred is complete, the codes of both are
+    done, late = (qt, q) if defer == "rowmajor" else (q, qt)
+    want_done, want_late = (want_t, want_q) if defer == "rowmajor" else (want_q, want_t)
+    assert torch.equal(done.codes, want_done.codes) and torch.equal(done.scales, want_done.scales) and torch.equal(done.unit, want_done.unit)
+    assert torch.equal(late.codes, want_late.codes)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        finish()
+    side.synchronize()
+    assert torch.equal(late.scales, want_late.scales) and torch.equal(late.unit, want_late.unit)
+    assert torch.equal(qt.token_sums, want_t.token_sums)
+    with pytest.raises(ValueError):
+        ops.nvfp4_quantize_dual(x, defer="both")
