@@ -565,3 +565,32 @@ def test_deferred_scale_passes_leave_every_result_bit_for_bit():
     assert len(results[True]) == len(results[False]) >= 6
     for a, b in zip(results[True], results[False]):
         assert torch.equal(a, b)
+
+
+def test_svd_activation_mode_runs_on_the_native_quantizers():
+    """metis_mode "svd" (bitlinear.py:243-309): x^ = Q(U) diag(s) Q(V) + Q(x - that), with the randomized SVD
+    from torch and every quantization on this library's kernels; the products stay dense (the reference's
+    wiring).  The factors come from random projections, so the check is what the mode is for: on an input
+    with a strong low-rank part the reconstruction beats plain quantization, and a layer trains in it."""
+    torch.manual_seed(5)
+    M, K, r = 512, 256, 16
+    low = torch.randn(M, r, device=DEV) @ torch.randn(r, K, device=DEV) * 4.0
+    x = (low + torch.randn(M, K, device=DEV) * 0.5).reshape(2, M // 2, K)
+    plain = Cast2NVFp4e2m1BlockNOSR.quantize_dequantize(x)
+    mixed = F.svd_quant(x, quant_func=Cast2NVFp4e2m1BlockNOSR, rank=r, niter=2, metis_mode="svd")
+    assert mixed.shape == x.shape and mixed.is_cuda
+    err_plain, err_mixed = rel_l2(plain.cpu().numpy(), x.cpu().numpy()), rel_l2(mixed.cpu().numpy(), x.cpu().numpy())
+    assert err_mixed < 0.6 * err_plain, (err_mixed, err_plain)
+
+    args = metis_args(16, metis_mode="svd")
+    layer = BitLinear(K, 192, args=args, bias=True, dtype=torch.float32, compute_dtype=torch.float32).to(DEV)
+    layer.layer_name = "svd.layer"
+    layer.split()
+    xin = x.clone().requires_grad_(True)
+    y = layer(xin)
+    y.backward(torch.randn_like(y))
+    want = xin.detach().reshape(-1, K) @ (layer.ulinear.weight @ torch.diag(layer.s) @ layer.vlinear.weight + layer.warmup_linear.weight).T \
+        + layer.warmup_linear.bias
+    assert rel_l2(y.detach().reshape(-1, 192).cpu().numpy(), want.detach().cpu().numpy()) < 0.15
+    assert xin.grad is not None and torch.isfinite(xin.grad).all()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in layer.parameters())
