@@ -81,6 +81,23 @@ def test_quantize_rejects_bad_arguments_without_a_device(L):
     assert L.metis_nvfp4_quantize(p, 1, 0, 32, 32, None, 0, 0, 0, 0, p, p, p, p, 4096, None) == -2   # empty
 
 
+def test_dual_quantizer_rejects_bad_arguments_without_a_device(L):
+    from fp4_post_b200 import cabi
+    buf = (C.c_uint8 * 65536)()
+    p = C.addressof(buf)
+    p += (-p) % 256
+    ws = L.metis_nvfp4_quantize_dual_workspace_bytes(64, 64)
+    dual = lambda flags, rows=64, sums=None: L.metis_nvfp4_quantize_dual(p, 0, rows, 64, 64, None, flags, 0, 0, 0, p, p, p, p, p, p, sums, p, ws, None)
+    assert dual(cabi.Q_DEFER_ROWMAJOR | cabi.Q_DEFER_TRANSPOSED) == -1           # only one of the two scale passes can be deferred
+    assert dual(64) == -1                                                      # unknown flag
+    assert dual(cabi.Q_HADAMARD, sums=p) == -1                                 # rotated blocks need weighted sums
+    assert dual(0, rows=48, sums=p) == -2                                      # token sums need rows % 64 == 0
+    finish = lambda which, rows=64, workspace=p: L.metis_nvfp4_quantize_dual_finish(rows, 64, which, 0, p, p, p, p, p, None, workspace, ws, None)
+    assert finish(0) == -1 and finish(cabi.Q_DEFER_ROWMAJOR | cabi.Q_DEFER_TRANSPOSED) == -1
+    assert finish(cabi.Q_DEFER_TRANSPOSED, rows=40) == -2
+    assert finish(cabi.Q_DEFER_ROWMAJOR, workspace=None) == -4
+
+
 def test_gemm_rejects_bad_arguments_without_a_device(L):
     from fp4_post_b200 import cabi
     buf = (C.c_uint8 * 1024)()
