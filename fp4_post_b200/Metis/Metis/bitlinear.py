@@ -671,7 +671,7 @@ def _packed_dw(da: PackedOperand, xa: PackedOperand, M: int, out_dtype=torch.flo
     if mu_d is not None:
         tail = _row_sums(x_t, xa.rotate)
         if mu_x is not None:
-            tail = tail + float(M) * mu_x
+            tail = torch.add(tail, mu_x, alpha=float(M))          # one kernel: Qx^T 1 + M mu_x
         rank1.append((mu_d, tail))
     # rotated operands: (H s)^T (H s) = 16 I
     return ops.nvfp4_gemm(d_t, x_t, rank1=rank1, out_dtype=out_dtype, sm_limit=sm_limit, alpha=1.0 / 16 if da.rotate is not None else 1.0)
