@@ -626,7 +626,18 @@ col_partial_sum_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int6
   const int64_t r_end = min(rows, r_begin + rows_per_split);
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (col < cols) {
-    for (int64_t r = r_begin + warp; r < r_end; r += kMeanThreads / 32) {
+    // four rows in flight per warp; the additions keep their order (row after row)
+    int64_t r = r_begin + warp;
+    for (; r + 3 * (kMeanThreads / 32) < r_end; r += 4 * (kMeanThreads / 32)) {
+      float v[4][8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) Load8<T>::load(x + (r + k * (kMeanThreads / 32)) * ld + col, v[k]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[k][i];
+    }
+    for (; r < r_end; r += kMeanThreads / 32) {
       float v[8];
       Load8<T>::load(x + r * ld + col, v);
 #pragma unroll
