@@ -269,6 +269,7 @@ class random_lane:
 class _NativeNVFP4(BlockQuantFunc):
     """Common part of the two NVFP4 quantizers: CUDA only, kernels behind the C ABI."""
     stochastic = False
+    sr_bits = 8          # random bits per element of the stochastic rounding: 8 (hardware) or 16 (software)
     _seed = 0x5EED
     _calls = 0
 
@@ -322,7 +323,7 @@ class _NativeNVFP4(BlockQuantFunc):
         return ops.nvfp4_quantize(cls._native_input(x), transpose=transpose, stochastic=cls.stochastic,
                                   seed=cls.philox_key(), sf_layout=sf_layout, mean=mean,
                                   offset_counter=cls._offset_counter(x.device) if cls.stochastic else None,
-                                  hadamard_signs=hadamard_signs if transpose else None)
+                                  hadamard_signs=hadamard_signs if transpose else None, sr_bits=cls.sr_bits)
 
     @classmethod
     @torch.no_grad()
@@ -335,7 +336,7 @@ class _NativeNVFP4(BlockQuantFunc):
         return ops.nvfp4_quantize_dual(cls._native_input(x), stochastic=cls.stochastic,
                                        seed=cls.philox_key(), sf_layout=sf_layout, mean=mean,
                                        offset_counter=cls._offset_counter(x.device) if cls.stochastic else None,
-                                       hadamard_signs=hadamard_signs, token_sums=token_sums, defer=defer)
+                                       hadamard_signs=hadamard_signs, token_sums=token_sums, defer=defer, sr_bits=cls.sr_bits)
 
     @classmethod
     @torch.no_grad()
@@ -401,7 +402,9 @@ class Cast2NVFp4e2m1BlockNOSR(_NativeNVFP4):
 
 
 class Cast2NVFp4e2m1Block(_NativeNVFP4):
-    """Stochastic-rounding NVFP4 (registry key 'nvfp4e2m1b'), the backward default."""
+    """Stochastic-rounding NVFP4 (registry key 'nvfp4e2m1b'), the backward default.  `sr_bits`: 8 uses the
+    hardware's stochastic e2m1 conversion (8 random bits per element: a value goes up with probability
+    floor(256 p) / 256, p its position between its neighbours); 16 the software form (2^-16 steps)."""
     stochastic = True
 
 

@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libmetis_nvfp4.so"
 DTYPE_BF16, DTYPE_F32 = 0, 1
 SF_ROWMAJOR, SF_MMA = 0, 1
 Q_TRANSPOSE, Q_STOCHASTIC, Q_OFFSET_ON_DEVICE, Q_HADAMARD = 1, 2, 4, 8
-Q_DEFER_ROWMAJOR, Q_DEFER_TRANSPOSED = 16, 32
+Q_DEFER_ROWMAJOR, Q_DEFER_TRANSPOSED, Q_SR16 = 16, 32, 64
 STATIC_MAX_ELEMENTS = 16 * 1024 * 1024
 
 STATUS_TEXT = {

@@ -293,6 +293,27 @@ __device__ __forceinline__ void quantize16_sr(const float (&x)[16], float s, uin
   }
 }
 
+// The same rounding by the hardware conversion cvt.rs.satfinite.e2m1x4.f32: four elements and 32 random bits
+// per instruction, 8 bits per element, up with probability floor(256 frac) / 256 where frac is the element's
+// position between its two e2m1 neighbours (measured on every probe value and byte of the random word; which
+// byte serves which element does not matter, all are uniform).  One Philox word per four elements, no other
+// arithmetic than the multiplication by 1/s.  Operand order: the last of the four lands in the lowest nibble.
+__device__ __forceinline__ uint32_t cvt_rs_e2m1x4(float e0, float e1, float e2, float e3, uint32_t rbits) {
+  uint16_t r;
+  asm("cvt.rs.satfinite.e2m1x4.f32 %0, {%1, %2, %3, %4}, %5;" : "=h"(r) : "f"(e3), "f"(e2), "f"(e1), "f"(e0), "r"(rbits));
+  return r;
+}
+__device__ __forceinline__ void quantize16_sr_hw(const float (&x)[16], float s, uint4 rnd, uint32_t (&out)[2]) {
+  const float inv = rcp_approx(s);
+  const uint32_t rw[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+  uint32_t h[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w)
+    h[w] = cvt_rs_e2m1x4(x[4 * w] * inv, x[4 * w + 1] * inv, x[4 * w + 2] * inv, x[4 * w + 3] * inv, rw[w]);
+  out[0] = h[0] | (h[1] << 16);
+  out[1] = h[2] | (h[3] << 16);
+}
+
 // ---- loads ------------------------------------------------------------------------------------------------
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }

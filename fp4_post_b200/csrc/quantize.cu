@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kQuantThreads)
 quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int64_t ld,
                      const float* __restrict__ col_mean, uint64_t seed, uint64_t offset,
                      const uint64_t* __restrict__ offset_ctr, uint2* __restrict__ codes, float* __restrict__ amax_out,
-                     unsigned int* __restrict__ gmax) {
+                     unsigned int* __restrict__ gmax, uint32_t sr16) {
   grid_dependency_wait();
   if (kSR && offset_ctr) offset += *offset_ctr;             // per-device call counter (graph-safe stream of offsets)
   const int bc = blockIdx.x * blockDim.x + threadIdx.x;     // column block of this thread
@@ -55,7 +55,8 @@ quantize_rows_kernel(const T* __restrict__ x, int rows, int blocks_per_row, int6
       const int64_t b = (int64_t)r * blocks_per_row + bc;
       uint32_t packed[2];
       if (kSR) {
-        quantize16_sr(v, s, rng((uint64_t)b, offset), packed);      // one counter per block
+        if (sr16) quantize16_sr(v, s, rng((uint64_t)b, offset), packed);      // one counter per block
+        else quantize16_sr_hw(v, s, rng((uint64_t)b, offset), packed);
       } else {
         quantize_rn<2>(v, s, packed);
       }
@@ -119,6 +120,7 @@ struct TileOutputs {
   uint8_t* codes_r;  float* amax_r;  unsigned int* gmax_r;        // Q  [rows, cols] (dual mode)
   unsigned int* error;
   uint32_t hadamard;         // bit 16: rotate every 16-row block of Qt first; bits [0, 16): the sign of each row
+  uint32_t sr16;             // stochastic rounding in software with 16 random bits per element instead of the hardware conversion's 8
 };
 
 // y = H (s . v) for one block of 16 values: the signs flip as the mask says, then the 16-point Walsh-Hadamard
@@ -250,7 +252,9 @@ quantize_tile_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, in
         uint32_t packed[2];
         if (kSR) {
           const uint64_t b = (uint64_t)out_row * (uint64_t)bpc + (uint64_t)((row0 >> 4) + rb);
-          quantize16_sr(v[c], s, rng(b, kRowsOut ? (offset ^ kColumnStream) : offset), packed);   // alone: the transposed call's own stream
+          const uint4 bits = rng(b, kRowsOut ? (offset ^ kColumnStream) : offset);                // alone: the transposed call's own stream
+          if (out.sr16) quantize16_sr(v[c], s, bits, packed);
+          else quantize16_sr_hw(v[c], s, bits, packed);
         } else {
           quantize_rn<2>(v[c], s, packed);
         }
@@ -300,7 +304,10 @@ quantize_tile_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, in
         const float s = block_scale_from_amax(a);
         const int64_t blk = (row0 + r) * bpr + (col0 >> 4) + b;
         uint32_t packed[2];
-        if (kSR) quantize16_sr(v, s, rng((uint64_t)blk, offset), packed);
+        if (kSR) {
+          if (out.sr16) quantize16_sr(v, s, rng((uint64_t)blk, offset), packed);
+          else quantize16_sr_hw(v, s, rng((uint64_t)blk, offset), packed);
+        }
         else     quantize_rn<2>(v, s, packed);
         if (cols_live && row0 + r < rows) {
           reinterpret_cast<uint2*>(out.codes_r)[blk] = make_uint2(packed[0], packed[1]);
@@ -684,7 +691,7 @@ static int sm_count() { return device_sm_count(); }
 template <typename T>
 static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, const float* mean, bool sr,
                         uint64_t seed, uint64_t offset, const uint64_t* ctr, uint32_t* codes, const WorkspaceView& ws,
-                        cudaStream_t st) {
+                        cudaStream_t st, uint32_t sr16 = 0) {
   const int bpr = (int)(cols >> 4);
   // threads along the row: the power of two that pads the row least (hidden 1536 = 96 blocks runs
   // as 3 x 32, not as 128 with a quarter of the lanes idle); ties go to the wider shape
@@ -710,7 +717,7 @@ static void launch_rows(const T* x, int64_t rows, int64_t cols, int64_t ld, cons
   const dim3 g((unsigned)gx, (unsigned)gy), b((unsigned)bx, (unsigned)by);
 #define METIS_LAUNCH_ROWS(MEAN, SR)                                                              \
   launch_overlapped(kLaunchStream, quantize_rows_kernel<T, MEAN, SR>, g, b, 0, st, x, (int)rows, bpr, ld, mean, seed, offset, ctr, \
-                    reinterpret_cast<uint2*>(codes), ws.amax, ws.gmax)
+                    reinterpret_cast<uint2*>(codes), ws.amax, ws.gmax, sr16)
   if (mean) { if (sr) METIS_LAUNCH_ROWS(true, true); else METIS_LAUNCH_ROWS(true, false); }
   else      { if (sr) METIS_LAUNCH_ROWS(false, true); else METIS_LAUNCH_ROWS(false, false); }
 #undef METIS_LAUNCH_ROWS
@@ -821,7 +828,9 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   if (ctr) offset = 0;
   if ((flags & METIS_Q_OFFSET_ON_DEVICE) && (!sr || !ctr || (reinterpret_cast<uintptr_t>(ctr) & 7u)))
     return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_OFFSET_ON_DEVICE needs METIS_Q_STOCHASTIC and an 8-byte aligned device address in offset");
-  if (flags & ~(METIS_Q_TRANSPOSE | METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x", flags);
+  if (flags & ~(METIS_Q_TRANSPOSE | METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK | METIS_Q_SR16)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x", flags);
+  if ((flags & METIS_Q_SR16) && !sr) return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_SR16 without METIS_Q_STOCHASTIC");
+  const uint32_t sr16 = (flags & METIS_Q_SR16) ? 1u : 0u;
   if ((flags & METIS_Q_HADAMARD) && !transpose) return fail(METIS_ERR_UNSUPPORTED, "METIS_Q_HADAMARD rotates the blocks of the transposed quantization: it needs METIS_Q_TRANSPOSE");
   if ((flags & METIS_Q_SIGN_MASK) && !(flags & METIS_Q_HADAMARD)) return fail(METIS_ERR_BAD_ARGUMENT, "sign bits without METIS_Q_HADAMARD");
   const uint32_t rht = (flags & METIS_Q_HADAMARD) ? ((1u << 16) | (flags >> 16)) : 0u;
@@ -852,7 +861,7 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   // flight per CTA, where the register-fed kernel waits on its loads.  Same arithmetic, same bytes.
   const bool rows_by_tiles = !transpose && rows * cols >= kTileRowsMinElements && (ld * esz) % 16 == 0;
   if (rows_by_tiles) {
-    const TileOutputs out = {nullptr, nullptr, nullptr, codes, ws.amax, ws.gmax, ws.gmax + 1, 0u};
+    const TileOutputs out = {nullptr, nullptr, nullptr, codes, ws.amax, ws.gmax, ws.gmax + 1, 0u, sr16};
     const int32_t rc = x_dtype == METIS_DTYPE_BF16
         ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
         : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
@@ -860,12 +869,12 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   } else if (!transpose) {
     if (x_dtype == METIS_DTYPE_BF16)
       launch_rows(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr,
-                  reinterpret_cast<uint32_t*>(codes), ws, st);
+                  reinterpret_cast<uint32_t*>(codes), ws, st, sr16);
     else
       launch_rows(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr,
-                  reinterpret_cast<uint32_t*>(codes), ws, st);
+                  reinterpret_cast<uint32_t*>(codes), ws, st, sr16);
   } else {
-    const TileOutputs out = {codes, ws.amax, ws.gmax, nullptr, nullptr, nullptr, ws.gmax + 1, rht};
+    const TileOutputs out = {codes, ws.amax, ws.gmax, nullptr, nullptr, nullptr, ws.gmax + 1, rht, sr16};
     const int32_t rc = x_dtype == METIS_DTYPE_BF16
         ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
         : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
@@ -907,7 +916,8 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
   if (ctr) offset = 0;
   if ((flags & METIS_Q_OFFSET_ON_DEVICE) && (!sr || !ctr || (reinterpret_cast<uintptr_t>(ctr) & 7u)))
     return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_OFFSET_ON_DEVICE needs METIS_Q_STOCHASTIC and an 8-byte aligned device address in offset");
-  if (flags & ~(METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK | METIS_Q_DEFER_ROWMAJOR | METIS_Q_DEFER_TRANSPOSED)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x (the dual quantizer always writes both orientations)", flags);
+  if (flags & ~(METIS_Q_STOCHASTIC | METIS_Q_OFFSET_ON_DEVICE | METIS_Q_HADAMARD | METIS_Q_SIGN_MASK | METIS_Q_DEFER_ROWMAJOR | METIS_Q_DEFER_TRANSPOSED | METIS_Q_SR16)) return fail(METIS_ERR_BAD_ARGUMENT, "unknown flags 0x%x (the dual quantizer always writes both orientations)", flags);
+  if ((flags & METIS_Q_SR16) && !sr) return fail(METIS_ERR_BAD_ARGUMENT, "METIS_Q_SR16 without METIS_Q_STOCHASTIC");
   if ((flags & METIS_Q_DEFER_ROWMAJOR) && (flags & METIS_Q_DEFER_TRANSPOSED)) return fail(METIS_ERR_BAD_ARGUMENT, "only one of the two scale passes can be deferred");
   if ((flags & METIS_Q_SIGN_MASK) && !(flags & METIS_Q_HADAMARD)) return fail(METIS_ERR_BAD_ARGUMENT, "sign bits without METIS_Q_HADAMARD");
   const uint32_t rht = (flags & METIS_Q_HADAMARD) ? ((1u << 16) | (flags >> 16)) : 0u;      // the transposed output only
@@ -936,7 +946,7 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
   float* amax_r = reinterpret_cast<float*>(static_cast<char*>(workspace) + kHeaderBytes);
   float* amax_t = amax_r + rows * (cols / 16);
   METIS_CUDA_OK(cudaMemsetAsync(head, 0, 3 * sizeof(unsigned int), st));
-  const TileOutputs out = {codes_t, amax_t, head + 2, codes, amax_r, head, head + 1, rht};
+  const TileOutputs out = {codes_t, amax_t, head + 2, codes, amax_r, head, head + 1, rht, (flags & METIS_Q_SR16) ? 1u : 0u};
   const int32_t rc = x_dtype == METIS_DTYPE_BF16
       ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
       : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);

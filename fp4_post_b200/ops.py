@@ -130,12 +130,19 @@ def _hadamard_flags(sign_mask: Optional[int]) -> int:
     return cabi.Q_HADAMARD | (sign_mask << 16)
 
 
+def _sr_flags(stochastic: bool, sr_bits: int) -> int:
+    if sr_bits not in (8, 16):
+        raise ValueError(f"sr_bits must be 8 (hardware conversion) or 16 (software), not {sr_bits}")
+    return cabi.Q_SR16 if stochastic and sr_bits == 16 else 0
+
+
 def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool = False, seed: int = 0,
                    offset: int = 0, sf_layout: int = cabi.SF_MMA,
                    mean: Optional[torch.Tensor] = None,
                    offset_counter: Optional[torch.Tensor] = None,
-                   hadamard_signs: Optional[int] = None) -> NVFP4Tensor:
+                   hadamard_signs: Optional[int] = None, sr_bits: int = 8) -> NVFP4Tensor:
     """Quantize x (viewed as [rows, cols]) or, with transpose=True, its transpose.
+    sr_bits: random bits per element of the stochastic rounding, 8 (the hardware conversion) or 16 (software).
 
     `mean` (fp32 [cols]) is subtracted from every row of x first.  Stochastic rounding draws
     Philox(seed; element, offset); with `offset_counter` (int64 [1] on x's device) the offset is that
@@ -148,6 +155,7 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
         raise ValueError(f"NVFP4 block shape (1, 16) does not divide tensor shape {(R, Cc)}")
     L = cabi.lib()
     flags = (cabi.Q_TRANSPOSE if transpose else 0) | (cabi.Q_STOCHASTIC if stochastic else 0) | _hadamard_flags(hadamard_signs)
+    flags |= _sr_flags(stochastic, sr_bits)
     dev = x2.device
     if stochastic and offset_counter is not None:
         if offset_counter.dtype != torch.int64 or offset_counter.device != dev or offset_counter.numel() != 1:
@@ -179,7 +187,7 @@ def nvfp4_quantize(x: torch.Tensor, *, transpose: bool = False, stochastic: bool
 def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int = 0, offset: int = 0,
                         sf_layout: int = cabi.SF_MMA, mean: Optional[torch.Tensor] = None,
                         offset_counter: Optional[torch.Tensor] = None, hadamard_signs: Optional[int] = None,
-                        token_sums: bool = False, defer: Optional[str] = None):
+                        token_sums: bool = False, defer: Optional[str] = None, sr_bits: int = 8):
     """Both quantizations of x viewed as [rows, cols] from one pass over it: (Q of x, Q of x^T), each
     bit-identical to the separate call (round to nearest).  rows and cols must be multiples of 16.
     With token_sums the second result carries `token_sums` (fp32 [cols]), the sums of its rows' quantized
@@ -194,6 +202,7 @@ def nvfp4_quantize_dual(x: torch.Tensor, *, stochastic: bool = False, seed: int 
         raise ValueError(f"NVFP4 block shape (1, 16) does not divide both dimensions of tensor shape {(rows, cols)}")
     L = cabi.lib()
     flags = (cabi.Q_STOCHASTIC if stochastic else 0) | _hadamard_flags(hadamard_signs)      # rotation: the transposed output only
+    flags |= _sr_flags(stochastic, sr_bits)
     if defer not in (None, "rowmajor", "transposed"):
         raise ValueError(f"defer must be 'rowmajor' or 'transposed', not {defer!r}")
     deferred = {None: 0, "rowmajor": cabi.Q_DEFER_ROWMAJOR, "transposed": cabi.Q_DEFER_TRANSPOSED}[defer]

@@ -66,6 +66,8 @@ extern "C" {
                                          the sign of each of the 16 positions (bit set: minus)                  */
 #define METIS_Q_DEFER_ROWMAJOR   (1u << 4) /* dual quantizer: leave the scale pass of the row-major output to ..._dual_finish */
 #define METIS_Q_DEFER_TRANSPOSED (1u << 5) /* dual quantizer: leave the scale pass of the transposed output to ..._dual_finish */
+#define METIS_Q_SR16        (1u << 6) /* with METIS_Q_STOCHASTIC: 16 random bits per element, in software, instead of
+                                         the hardware conversion's 8 (see below) */
 #define METIS_Q_SIGN_MASK   0xFFFF0000u
 
 /* status codes (host return values are <= 0, device status words are >= 0) */
@@ -119,8 +121,12 @@ int64_t metis_nvfp4_quantize_workspace_bytes(int64_t R, int64_t C);
  * Arithmetic (fp32, round-to-nearest mode bit-exact with the reference run on
  * x.float()): s = amax/6 + 1e-9 per block; unit = max(s)/448; scale = e4m3(s/unit);
  * code = round-half-even of |x|/(s/2) folded onto the e2m1 grid; sign bit = (x < 0).
- * Stochastic mode adds U[-0.5, 0.5) to the folded index before rounding.  The random bits are
- * Philox4x32-10(seed; block index, offset), 16 bits per element.  With METIS_Q_OFFSET_ON_DEVICE the offset is not
+ * Stochastic mode rounds a value up to its upper e2m1 neighbour with the probability of its position between
+ * the two neighbours (the reference adds U[-0.5, 0.5) to the folded index before rounding, quant.py:144-145).
+ * By default the hardware conversion cvt.rs.satfinite.e2m1x4.f32 does it: 8 random bits per element, up with
+ * probability floor(256 p) / 256.  METIS_Q_SR16 selects the software form with 16 random bits per element
+ * (floor(index + U), U in steps of 2^-16), about 8 more instructions per element.  The random bits are
+ * Philox4x32-10(seed; block index, offset), one call per block of 16.  With METIS_Q_OFFSET_ON_DEVICE the offset is not
  * the argument's value but the content of the device uint64 it points to (8-byte aligned),
  * and the call adds 1 to that counter when its kernels have read it: successive calls on one
  * stream draw fresh bits although their arguments are identical, which is what a captured
@@ -153,8 +159,8 @@ int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64
  * one fake-quantized tensor becomes two packed ones here (call sites bitlinear.py:392, :331,
  * :400-402, :580).  Reads x from HBM once instead of twice; outputs are bit-identical to two calls of
  * metis_nvfp4_quantize (round to nearest; stochastic rounding draws from two disjoint Philox
- * counter spaces).  rows and cols must both be multiples of 16.  flags: METIS_Q_STOCHASTIC,
- * METIS_Q_OFFSET_ON_DEVICE.  Launches: zero-fill of the workspace header, one tile pass, one scale
+ * counter spaces).  rows and cols must both be multiples of 16.  flags: METIS_Q_STOCHASTIC, METIS_Q_SR16,
+ * METIS_Q_OFFSET_ON_DEVICE, METIS_Q_HADAMARD, METIS_Q_DEFER_*.  Launches: zero-fill of the workspace header, one tile pass, one scale
  * pass that finishes both outputs.
  *   codes    uint8 [rows, cols/2]   scales    metis_nvfp4_sf_bytes(rows, cols, sf_layout)   unit    fp32 [1]
  *   codes_t  uint8 [cols, rows/2]   scales_t  metis_nvfp4_sf_bytes(cols, rows, sf_layout)   unit_t  fp32 [1]

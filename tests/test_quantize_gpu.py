@@ -182,9 +182,12 @@ def test_gemv_and_row_sums(rows, cols, layout):
 GRID = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
 
 
+@pytest.mark.parametrize("sr_bits", [8, 16])
 @pytest.mark.parametrize("transpose", [False, True])
-def test_stochastic_rounding_is_unbiased_and_stays_on_neighbours(transpose):
+def test_stochastic_rounding_is_unbiased_and_stays_on_neighbours(transpose, sr_bits):
     # every block: one element at 6 (so s = 1 exactly) and 15 copies of a probe value.
+    # 16 bits (software): up with probability p in steps of 2^-16.  8 bits (the hardware conversion):
+    # up with probability floor(256 p) / 256, i.e. at most 1/256 of the distance to the neighbour short of p.
     probes = [0.1, 0.3, 0.6, 0.85, 1.1, 1.7, 2.3, 3.3, 4.4, 5.5, -0.7, -2.6]
     blocks = 70000                       # 15 * 70000 = 1.05e6 draws per probe
     for p in probes:
@@ -192,7 +195,7 @@ def test_stochastic_rounding_is_unbiased_and_stays_on_neighbours(transpose):
         row[:, 0] = 6.0
         x = row.t().contiguous() if transpose else row
         q = ops.nvfp4_quantize(x.to(DEV), transpose=transpose, stochastic=True, seed=1234, offset=int(abs(p) * 100),
-                               sf_layout=cabi.SF_ROWMAJOR)
+                               sf_layout=cabi.SF_ROWMAJOR, sr_bits=sr_bits)
         codes, scales, unit = packed_to_numpy(q)
         vals = O.unpack_codes(codes)[:, 1:]
         lo = GRID[GRID <= abs(p)].max()
@@ -202,22 +205,52 @@ def test_stochastic_rounding_is_unbiased_and_stays_on_neighbours(transpose):
         assert (np.sign(vals[vals != 0]) == np.sign(p)).all()
         frac = (abs(p) - lo) / (hi - lo)
         sigma = (hi - lo) * np.sqrt(frac * (1 - frac) / vals.size)
-        assert abs(mags.mean() - abs(p)) < 4 * sigma + 1e-7, f"probe {p}: mean {mags.mean()}"
+        if sr_bits == 16:
+            assert abs(mags.mean() - abs(p)) < 4 * sigma + 1e-7, f"probe {p}: mean {mags.mean()}"
+        else:
+            # the reciprocal of the block scale is approximate (2 ulp): p may sit one step of 1/256 lower or higher
+            want = lo + (hi - lo) * np.floor(frac * 256) / 256
+            assert abs(mags.mean() - want) < 4 * sigma + (hi - lo) / 256 + 1e-7, f"probe {p}: mean {mags.mean()}, want {want}"
+            assert abs(mags.mean() - abs(p)) < 4 * sigma + (hi - lo) / 256 + 1e-7
         # scales do not depend on the rounding mode
         qr = ops.nvfp4_quantize(x.to(DEV), transpose=transpose, sf_layout=cabi.SF_ROWMAJOR)
         assert np.array_equal(scales, qr.scales.cpu().numpy()) and unit == np.float32(qr.unit.item())
 
 
-def test_stochastic_rounding_depends_on_seed_and_offset_only():
+@pytest.mark.parametrize("sr_bits", [8, 16])
+def test_stochastic_rounding_depends_on_seed_and_offset_only(sr_bits):
     x = synthetic(256, 256, "normal", seed=21, dtype=torch.bfloat16).to(DEV)
-    a = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=1).codes
-    b = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=1).codes
-    c = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=2).codes
+    a = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=1, sr_bits=sr_bits).codes
+    b = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=1, sr_bits=sr_bits).codes
+    c = ops.nvfp4_quantize(x, stochastic=True, seed=7, offset=2, sr_bits=sr_bits).codes
     assert torch.equal(a, b) and not torch.equal(a, c)
     # dequantized SR output is unbiased against the input within the block scale
-    deq = ops.nvfp4_quantize(x, stochastic=True, seed=9, offset=3, sf_layout=cabi.SF_ROWMAJOR).dequantize(torch.float32)
+    deq = ops.nvfp4_quantize(x, stochastic=True, seed=9, offset=3, sf_layout=cabi.SF_ROWMAJOR, sr_bits=sr_bits).dequantize(torch.float32)
     err = (deq - x.float()).mean().abs().item()
     assert err < 5e-3
+    with pytest.raises(ValueError):
+        ops.nvfp4_quantize(x, stochastic=True, sr_bits=12)
+
+
+def test_both_stochastic_roundings_land_on_the_same_two_neighbours():
+    # hardware (8 random bits) and software (16) rounding of the same tensor: every element ends on one of its two
+    # e2m1 neighbours in both, the scales are the same, and where they differ it is by one grid step
+    x = synthetic(512, 1024, "student", seed=4, dtype=torch.bfloat16).to(DEV)
+    mean = ops.col_mean(x)
+    hw, hwt = ops.nvfp4_quantize_dual(x, mean=mean, stochastic=True, seed=3, offset=1, sf_layout=cabi.SF_ROWMAJOR, sr_bits=8)
+    sw, swt = ops.nvfp4_quantize_dual(x, mean=mean, stochastic=True, seed=3, offset=1, sf_layout=cabi.SF_ROWMAJOR, sr_bits=16)
+    rn, rnt = ops.nvfp4_quantize_dual(x, mean=mean, sf_layout=cabi.SF_ROWMAJOR)
+    for a, b, c in ((hw, sw, rn), (hwt, swt, rnt)):
+        assert torch.equal(a.scales, b.scales) and torch.equal(a.scales, c.scales) and torch.equal(a.unit, c.unit)
+        va, vb, vc = (ops.nvfp4_dequantize(t, torch.float32, add_mean=False) for t in (a, b, c))
+        # per block: the scale s = amax / 6 is the value of code magnitude 1.0; neighbouring grid points are at most 2 s apart
+        R, C = va.shape
+        blocks = lambda v: v.reshape(R, C // 16, 16)
+        s_blk = blocks(vc).abs().amax(dim=2, keepdim=True).clamp_min(1e-30) / 4.0      # >= the true s (the block maximum rounds to 4 or 6)
+        for v in (va, vb):
+            assert bool((blocks(v - vc).abs() <= 2.0001 * s_blk * 1.5).all())          # within one grid step of round-to-nearest
+        differ = float((va != vb).float().mean())
+        assert 0.02 < differ < 0.6, differ                                             # independent draws differ often, not always
 
 
 def test_every_bf16_value_below_a_block_maximum():
