@@ -741,6 +741,8 @@ def run_single_kernel(args):
               "quant_transposed": lambda: ops.nvfp4_quantize(x, transpose=True),
               "quant_dual": lambda: ops.nvfp4_quantize_dual(x),
               "quant_dual_sr": lambda: ops.nvfp4_quantize_dual(x, stochastic=True, seed=1, offset=1, mean=x_mean),
+              # the form the output gradient takes in the training step: the token sums of the transposed output too
+              "quant_dual_sr_sums": lambda: ops.nvfp4_quantize_dual(x, stochastic=True, seed=1, offset=1, mean=x_mean, token_sums=True),
               "rmsnorm_quant": lambda: ops.rmsnorm_nvfp4_quantize(x, gamma, 1e-6)}[args.only]
         work, unit = rows * cols * (BYTES_PER_ELEM_DUAL_BF16 if args.only.startswith("quant_dual") else BYTES_PER_ELEM_BF16) / 1e9, "GB/s"
     for _ in range(max(1, args.warmup)):
@@ -765,7 +767,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "gemm_sustained", "gemm_accounting", "step_timeline", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer", "c4", "c5_update"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "quant_dual_sr_sums", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "gemm_sustained", "gemm_accounting", "step_timeline", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer", "c4", "c5_update"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--layers", type=int, default=1,
                     help="stack this many Metis layers (the headline is 1): with several GPUs the gradient all-reduce "

@@ -392,14 +392,7 @@ class LinearLowbitFunction(torch.autograd.Function):
             done = None
             if defer is not None:
                 q, qt, finish = res
-                main, third = torch.cuda.current_stream(flat.device), _aux_stream(flat.device, 2)
-                issued = torch.cuda.Event()
-                issued.record(main)
-                third.wait_event(issued)
-                with torch.cuda.stream(third):
-                    finish()
-                    done = torch.cuda.Event()
-                    done.record(third)
+                done = _finish_beside(finish, flat.device)
             else:
                 q, qt = res
             if getattr(qt, "token_sums", None) is not None:
@@ -484,6 +477,7 @@ class LinearLowbitFunction(torch.autograd.Function):
             out_dtype = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
             y = _packed_matmul(xa.rowmajor(), wq.q, rank1=rank1, out_dtype=out_dtype)
             xa.join_deferred()
+            wq.join_deferred()
             return y.reshape(*xa.shape[:-1], wq.q.shape[0]).to(xa.dtype)
         # dense mode: the reference's wiring
         if isinstance(xa, PackedOperand):
@@ -544,6 +538,20 @@ class LinearLowbitFunction(torch.autograd.Function):
 
 _ONES = {}
 _AUX_STREAMS = {}
+
+
+def _finish_beside(finish, device):
+    """Run the deferred scale pass of a dual quantization (ops.nvfp4_quantize_dual(defer=...)) on the stream kept
+    for such passes, after everything issued so far on the current stream.  Returns the event that marks it done."""
+    here, beside = torch.cuda.current_stream(device), _aux_stream(device, 2)
+    issued = torch.cuda.Event()
+    issued.record(here)
+    beside.wait_event(issued)
+    with torch.cuda.stream(beside):
+        finish()
+        done = torch.cuda.Event()
+        done.record(beside)
+    return done
 
 
 def _aux_stream(device: torch.device, index: int = 0) -> "torch.cuda.Stream":
@@ -743,12 +751,19 @@ class LinearLowbit(torch.nn.Module):
                 return cached_weight
         if packed:
             source = weight_compute.detach()
+            done = None
             if training and _dual_ok(source):        # the input-gradient product contracts over the other dimension
-                q, qt = F.q_forward_weight.quantize_packed_dual(source)
+                if F.defer_scale_pass and not self.cache_quantized_weight:
+                    # only the backward reads the transposed quantization: its scale pass leaves the forward's path
+                    q, qt, finish = F.q_forward_weight.quantize_packed_dual(source, defer="transposed")
+                    done = _finish_beside(finish, source.device)
+                else:
+                    q, qt = F.q_forward_weight.quantize_packed_dual(source)
             else:
                 q, qt = F.q_forward_weight.quantize_packed(source), None
             quantized_weight = PackedOperand(q, source, F.q_forward_weight, source.shape)
             quantized_weight._qt = qt
+            quantized_weight._qt_event = done
         else:
             quant_input = weight_compute
             if F.enable_nv_recipe:
@@ -830,7 +845,8 @@ class MetisFusedFunction(torch.autograd.Function):
         if (MetisFusedFunction.concurrent_branches and xa.q.codes.is_cuda and any(ctx.needs_input_grad)
                 and xa._qt is not None and LinearLowbitFunction._backward_centred()):
             _row_sums_beside(xa)        # queued behind the product: it runs as that one drains, not in front of it
-        xa.join_deferred()              # a scale pass left to the third stream has long finished; this joins that stream
+        for op in (xa, vq, rq):         # scale passes left to another stream have long finished; this joins that stream
+            op.join_deferred()
         ctx.xa, ctx.vq, ctx.rq = xa, vq, rq
         ctx.has_bias = bias is not None
         ctx.dims = (M, N, K)
@@ -1176,8 +1192,9 @@ class BitLinear(nn.Module):
         main, aux = torch.cuda.current_stream(x.device), _aux_stream(x.device)
         aux.wait_stream(main)
         with torch.cuda.stream(aux):
-            vq = v._get_quantized_weight(v.weight.to(v.compute_dtype))
+            # the large one first: it then runs beside the activation's column sums, not beside its quantization
             rq = w._get_quantized_weight(w.weight.to(w.compute_dtype))
+            vq = v._get_quantized_weight(v.weight.to(v.compute_dtype))
             done = torch.cuda.Event()
             done.record(aux)
         for op in (vq, rq):

@@ -115,10 +115,18 @@ template <typename T> struct TileCfg {
 constexpr int64_t kTileRowsMinElements = 1 << 20;          // row-major tensors from this size on go through the tile kernel
 constexpr uint64_t kColumnStream = 1ull << 63;             // Philox counter space of the transposed output in dual mode
 
+// Workspace of the dual quantizer: word 63 = number of CTA records, records from word 64 on (3 words per CTA),
+// then the block maxima of Q and of Qt.
+constexpr int kDualMaxCtas = 640;
+constexpr int kDualHeaderBytes = 256 + ((kDualMaxCtas * 3 * 4 + 255) / 256) * 256;
+
 struct TileOutputs {
   uint8_t* codes_t;  float* amax_t;  unsigned int* gmax_t;        // Qt [cols, rows]
   uint8_t* codes_r;  float* amax_r;  unsigned int* gmax_r;        // Q  [rows, cols] (dual mode)
   unsigned int* error;
+  // dual mode: instead of folding into the three header words above (which somebody has to zero first), CTA b
+  // leaves {largest maximum of Q, of Qt, error} in records[3b..3b+2] and CTA 0 the number of CTAs in records[-1]
+  unsigned int* records;
   uint32_t hadamard;         // bit 16: rotate every 16-row block of Qt first; bits [0, 16): the sign of each row
   uint32_t sr16;             // stochastic rounding in software with 16 random bits per element instead of the hardware conversion's 8
 };
@@ -363,8 +371,29 @@ quantize_tile_kernel(const __grid_constant__ CUtensorMap map_x, int64_t rows, in
         while (!mbar_try(&full[st], ((it + k) / TC::kStages) & 1u) && global_ns() - t0 < kWaitLimitNs) {}
         if (++st == TC::kStages) st = 0;
       }
-      *out.error = 1u;                                 // error word of the workspace header
+      if (!out.records) *out.error = 1u;               // error word of the workspace header
     }
+  }
+  if (out.records) {
+    // every CTA writes its record, so nothing needs zeroing and no two CTAs touch the same word
+    __shared__ float2 s_max[kQuantThreads / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      running_r = fmaxf(running_r, __shfl_xor_sync(0xffffffffu, running_r, o));
+      running_t = fmaxf(running_t, __shfl_xor_sync(0xffffffffu, running_t, o));
+    }
+    if (lane == 0) s_max[warp] = make_float2(running_r, running_t);
+    __syncthreads();
+    if (tid == 0) {
+      float2 m = s_max[0];
+      for (int w = 1; w < kQuantThreads / 32; ++w) { m.x = fmaxf(m.x, s_max[w].x); m.y = fmaxf(m.y, s_max[w].y); }
+      unsigned int* rec = out.records + 3 * (int64_t)blockIdx.x;
+      rec[0] = __float_as_uint(m.x);
+      rec[1] = __float_as_uint(m.y);
+      rec[2] = s_failed ? 1u : 0u;
+      if (blockIdx.x == 0) out.records[-1] = gridDim.x;
+    }
+    return;
   }
   if (kColsOut) fold_global_max(out.gmax_t, running_t);
   if (kRowsOut) fold_global_max(out.gmax_r, running_r);
@@ -384,17 +413,37 @@ struct FinalizeJob {
   // codes the first pass wrote.  A weight-gradient product needs these sums of its operands when they
   // were centred; here they cost one extra read of codes that are still in L2 instead of a pass of their own.
   const uint2* codes;  float* row_sums;
+  // per-CTA records of the dual quantizer (see TileOutputs) in place of gmax / error: word `which` of each is the maximum
+  const unsigned int* records;  int32_t which;
 };
 struct FinalizeJobs { FinalizeJob job[2]; };
 
-// E4M3 bytes of 4 neighbouring blocks from their maxima (quant.py:23): two packed conversions
-__device__ __forceinline__ uint32_t scale_bytes4(const float (&a)[4], int live, float unit) {
+// E4M3 bytes of 4 neighbouring blocks from their maxima (quant.py:23): RN_e4m3(RN_fp32(s / unit)), two packed
+// conversions.  The division is replaced by a product with RN(1 / unit), which lies within 3 fp32 steps of the
+// correctly rounded quotient; the E4M3 byte of a normal value changes only where the 20 dropped mantissa bits
+// pass 0x80000 (the tie), so a product further than that from a tie converts to the same byte.  The others,
+// everything in E4M3's subnormal range (other tie positions) and NaN take the division itself.
+__device__ __forceinline__ uint32_t scale_bytes4(const float (&a)[4], int live, float unit, float inv_unit) {
   float ratio[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) ratio[j] = j < live ? __fdiv_rn(block_scale_from_amax(a[j]), unit) : 0.0f;
+  for (int j = 0; j < 4; ++j) {
+    const float s = block_scale_from_amax(a[j]);
+    float q = __fmul_rn(s, inv_unit);
+    const uint32_t low = __float_as_uint(q) & 0xFFFFFu;
+    if (low - 0x7FFF8u <= 16u || !(q >= 0.0157f)) q = __fdiv_rn(s, unit);
+    ratio[j] = j < live ? q : 0.0f;
+  }
   const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(ratio[0], ratio[1]), __NV_SATFINITE, __NV_E4M3);
   const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(ratio[2], ratio[3]), __NV_SATFINITE, __NV_E4M3);
   return lo | (hi << 16);
+}
+
+// the four E4M3 bytes of a word as floats (exact)
+__device__ __forceinline__ void e4m3x4_to_float(uint32_t packed, float (&f)[4]) {
+  const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(packed & 0xFFFFu), __NV_E4M3);
+  const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(packed >> 16), __NV_E4M3);
+  const float2 l = __half22float2(__half2(lo)), h = __half22float2(__half2(hi));
+  f[0] = l.x; f[1] = l.y; f[2] = h.x; f[3] = h.y;
 }
 
 // Thread (tx, ty) of a bx x by CTA (bx per job) walks the groups tx, tx + bx, ... of the rows ty,
@@ -410,9 +459,32 @@ finalize_scales_kernel(const FinalizeJob job0, const FinalizeJob job1, uint64_t*
   uint8_t* __restrict__ scales = J.scales;
   const int64_t R = J.R, sf_cols = J.sf_cols;
   const bool tiled = J.sf_layout == METIS_SF_MMA;
-  const float smax = block_scale_from_amax(__uint_as_float(*J.gmax));
+  unsigned int top = 0u, bad = 0u;                 // bits of the largest block maximum (>= 0: they order like the value)
+  if (J.records) {
+    __shared__ unsigned int s_top[2];
+    if (threadIdx.x < 32) {                        // one warp reads the few KiB of records (L2) for the CTA
+      const int n = (int)J.records[-1];
+      for (int i = threadIdx.x; i < n; i += 32) {
+        top = max(top, J.records[3 * i + J.which]);
+        bad |= J.records[3 * i + 2];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        top = max(top, __shfl_xor_sync(0xffffffffu, top, o));
+        bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+      }
+      if (threadIdx.x == 0) { s_top[0] = top; s_top[1] = bad; }
+    }
+    __syncthreads();
+    top = s_top[0];
+    bad = s_top[1];
+  } else {
+    top = *J.gmax;
+    bad = *J.error;
+  }
+  const float smax = block_scale_from_amax(__uint_as_float(top));
   // quant.py:21-22; a pass-1 kernel that gave up on a load raises the error word: publish NaN so that it shows
-  const float unit = *J.error ? __uint_as_float(0x7FC00000u) : __fdiv_rn(smax, 448.0f);
+  const float unit = bad ? __uint_as_float(0x7FC00000u) : __fdiv_rn(smax, 448.0f);
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     *J.unit = unit;
     if (offset_ctr && blockIdx.y == 0) *offset_ctr += 1;       // pass 1 of this call has finished: the next call draws fresh bits
@@ -448,31 +520,42 @@ finalize_scales_kernel(const FinalizeJob job0, const FinalizeJob job1, uint64_t*
       for (int j = 0; j < live; ++j) scales[r * sf_cols + k0 + j] = (uint8_t)(packed >> (8 * j));
     }
   };
-  // sum of code values x scale of the 4 blocks of group g of row r, in half units of `unit`
-  auto group_sum = [&](int64_t r, int g, uint32_t packed) -> float {
-    const uint4* c = reinterpret_cast<const uint4*>(J.codes + r * sf_cols + (int64_t)g * 4);
-    const uint4 lo = c[0], hi = c[1];
-    float acc = (float)block_code_sum(make_uint2(lo.x, lo.y)) * e4m3_to_float(packed & 0xFFu);
-    acc = fmaf((float)block_code_sum(make_uint2(lo.z, lo.w)), e4m3_to_float((packed >> 8) & 0xFFu), acc);
-    acc = fmaf((float)block_code_sum(make_uint2(hi.x, hi.y)), e4m3_to_float((packed >> 16) & 0xFFu), acc);
-    return fmaf((float)block_code_sum(make_uint2(hi.z, hi.w)), e4m3_to_float(packed >> 24), acc);
+  // codes of the 4 blocks of group g of row r, and their sum of code values x scale in half units of `unit`
+  auto load_codes = [&](int64_t r, int g, uint4 (&c)[2]) {
+    const uint4* src = reinterpret_cast<const uint4*>(J.codes + r * sf_cols + (int64_t)g * 4);
+    c[0] = src[0];
+    c[1] = src[1];
   };
+  auto group_sum = [&](const uint4 (&c)[2], uint32_t packed) -> float {
+    float f[4];
+    e4m3x4_to_float(packed, f);
+    float acc = (float)block_code_sum(make_uint2(c[0].x, c[0].y)) * f[0];
+    acc = fmaf((float)block_code_sum(make_uint2(c[0].z, c[0].w)), f[1], acc);
+    acc = fmaf((float)block_code_sum(make_uint2(c[1].x, c[1].y)), f[2], acc);
+    return fmaf((float)block_code_sum(make_uint2(c[1].z, c[1].w)), f[3], acc);
+  };
+  const float inv_unit = __fdiv_rn(1.0f, unit);
   // the row loop is uniform over the CTA (the reduction below meets at a barrier)
   for (int64_t r0 = (int64_t)blockIdx.x * by; r0 < R_out; r0 += 2 * row_step) {
     const int64_t r = r0 + ty, r2 = r + row_step;
     float sum_a = 0.0f, sum_b = 0.0f;
     if (r < R_out) {
+      const bool second = r2 < R_out;
       for (int g = tx; g < groups_per_row; g += bx) {
         float a[4], b[4];
+        uint4 ca[2], cb[2];
+        // every load of the two rows is issued before the first use
         const int la = load(r, g, a);
-        const int lb = r2 < R_out ? load(r2, g, b) : 0;
-        const uint32_t pa = scale_bytes4(a, la, unit);
+        const int lb = second ? load(r2, g, b) : 0;
+        if (sums && la) load_codes(r, g, ca);
+        if (sums && lb) load_codes(r2, g, cb);
+        const uint32_t pa = scale_bytes4(a, la, unit, inv_unit);
         store(r, g, pa, la);
-        if (sums && la) sum_a += group_sum(r, g, pa);
-        if (r2 < R_out) {
-          const uint32_t pb = scale_bytes4(b, lb, unit);
+        if (sums && la) sum_a += group_sum(ca, pa);
+        if (second) {
+          const uint32_t pb = scale_bytes4(b, lb, unit, inv_unit);
           store(r2, g, pb, lb);
-          if (sums && lb) sum_b += group_sum(r2, g, pb);
+          if (sums && lb) sum_b += group_sum(cb, pb);
         }
       }
     }
@@ -625,6 +708,8 @@ col_partial_sum_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int6
                        int64_t rows_per_split, float* __restrict__ partial, int64_t mean_of_rows) {
   // mean_of_rows > 0 (a single split): `partial` is the mean itself, sum / mean_of_rows, as stage 2 would write it
   grid_dependency_wait();
+  // stage 2 follows in the stream: its few CTAs may take their places now (they wait for this grid to complete)
+  if (mean_of_rows == 0) grid_launch_dependents();
   // 32 lanes x 8 columns = 256 columns per CTA; 8 warps stride over the rows.
   __shared__ float s_part[kMeanThreads / 32][256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -662,19 +747,26 @@ col_partial_sum_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int6
   if (oc < cols) partial[(int64_t)blockIdx.y * cols + oc] = mean_of_rows > 0 ? __fdiv_rn(__fadd_rn(0.0f, sum), (float)mean_of_rows) : sum;
 }
 
-__global__ void col_mean_finish_kernel(const float* __restrict__ partial, int64_t splits, int64_t rows,
+constexpr int kMeanMaxSplits = 64;
+__global__ void __launch_bounds__(256) col_mean_finish_kernel(const float* __restrict__ partial, int64_t splits, int64_t rows,
                                        int64_t cols, float* __restrict__ mean) {
   grid_dependency_wait();
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
+  // all loads in flight at once (splits <= kMeanMaxSplits), then the additions in their fixed order
+  float v[kMeanMaxSplits];
+#pragma unroll
+  for (int s = 0; s < kMeanMaxSplits; ++s) v[s] = s < splits ? partial[s * cols + c] : 0.0f;
   float sum = 0.0f;
-  for (int64_t s = 0; s < splits; ++s) sum += partial[s * cols + c];
+#pragma unroll
+  for (int s = 0; s < kMeanMaxSplits; ++s)
+    if (s < splits) sum += v[s];
   mean[c] = __fdiv_rn(sum, (float)rows);
 }
 
 static int64_t col_mean_splits(int64_t rows) {
   int64_t s = ceil_div(rows, 128);
-  return s < 1 ? 1 : (s > 64 ? 64 : s);
+  return s < 1 ? 1 : (s > kMeanMaxSplits ? kMeanMaxSplits : s);
 }
 
 // ---- launch helpers ------------------------------------------------------------------------------------------
@@ -734,6 +826,7 @@ static int32_t launch_tile(const T* x, int64_t rows, int64_t cols, int64_t ld, c
   const int64_t tiles = ceil_div(cols, TC::kCols) * ceil_div(rows, TC::kRows);
   int64_t grid = (int64_t)sm_count() * 3;          // three CTAs of ~63 KiB per SM
   if (grid > tiles) grid = tiles;
+  if (out.records && grid > kDualMaxCtas) grid = kDualMaxCtas;
   const bool with_rows = out.codes_r != nullptr, with_cols = out.codes_t != nullptr;
 #define METIS_LAUNCH_TILE(MEAN, SR, ROWS, COLS)                                                             \
   do {                                                                                                      \
@@ -770,7 +863,7 @@ static int32_t launch_finalize_jobs(FinalizeJobs jobs, int njobs, cudaStream_t s
   }
   if (njobs == 1) jobs.job[1] = jobs.job[0];
   const int64_t cap = (int64_t)sm_count() * 8 / njobs;
-  if (blocks > cap) blocks = cap;
+  if (blocks > cap) blocks = ceil_div(blocks, ceil_div(blocks, cap));    // the fewest CTAs that need no more rounds than `cap` would
   METIS_CUDA_OK(launch_overlapped(kLaunchShort, finalize_scales_kernel, dim3((unsigned)blocks, (unsigned)njobs), dim3(kQuantThreads), 0, st,
                                   jobs.job[0], jobs.job[1], offset_ctr));
   return METIS_OK;
@@ -779,7 +872,7 @@ static int32_t launch_finalize_jobs(FinalizeJobs jobs, int njobs, cudaStream_t s
 int32_t launch_finalize(const WorkspaceView& ws, int64_t R, int64_t C, int32_t sf_layout,
                         uint8_t* scales, float* unit, cudaStream_t st, uint64_t* offset_ctr) {
   FinalizeJobs jobs = {};
-  jobs.job[0] = {ws.amax, ws.gmax, ws.gmax + 1, R, C / 16, sf_layout, scales, unit, 0, nullptr, nullptr};
+  jobs.job[0] = {ws.amax, ws.gmax, ws.gmax + 1, R, C / 16, sf_layout, scales, unit, 0, nullptr, nullptr, nullptr, 0};
   return launch_finalize_jobs(jobs, 1, st, offset_ctr);
 }
 
@@ -861,7 +954,7 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
   // flight per CTA, where the register-fed kernel waits on its loads.  Same arithmetic, same bytes.
   const bool rows_by_tiles = !transpose && rows * cols >= kTileRowsMinElements && (ld * esz) % 16 == 0;
   if (rows_by_tiles) {
-    const TileOutputs out = {nullptr, nullptr, nullptr, codes, ws.amax, ws.gmax, ws.gmax + 1, 0u, sr16};
+    const TileOutputs out = {nullptr, nullptr, nullptr, codes, ws.amax, ws.gmax, ws.gmax + 1, nullptr, 0u, sr16};
     const int32_t rc = x_dtype == METIS_DTYPE_BF16
         ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
         : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
@@ -874,7 +967,7 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
       launch_rows(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr,
                   reinterpret_cast<uint32_t*>(codes), ws, st, sr16);
   } else {
-    const TileOutputs out = {codes, ws.amax, ws.gmax, nullptr, nullptr, nullptr, ws.gmax + 1, rht, sr16};
+    const TileOutputs out = {codes, ws.amax, ws.gmax, nullptr, nullptr, nullptr, ws.gmax + 1, nullptr, rht, sr16};
     const int32_t rc = x_dtype == METIS_DTYPE_BF16
         ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
         : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);
@@ -888,22 +981,22 @@ extern "C" int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t 
 static int32_t finish_dual(int64_t rows, int64_t cols, int32_t sf_layout, uint8_t* scales, float* unit, const uint8_t* codes_t,
                            uint8_t* scales_t, float* unit_t, float* token_sums_t, void* workspace, bool rowmajor,
                            bool transposed, cudaStream_t st, uint64_t* ctr) {
-  unsigned int* head = static_cast<unsigned int*>(workspace);
-  float* amax_r = reinterpret_cast<float*>(static_cast<char*>(workspace) + kHeaderBytes);
+  const unsigned int* records = static_cast<const unsigned int*>(workspace) + 64;
+  float* amax_r = reinterpret_cast<float*>(static_cast<char*>(workspace) + kDualHeaderBytes);
   float* amax_t = amax_r + rows * (cols / 16);
   FinalizeJobs jobs = {};
   int n = 0;
-  if (rowmajor) jobs.job[n++] = {amax_r, head, head + 1, rows, cols / 16, sf_layout, scales, unit, 0, nullptr, nullptr};
+  if (rowmajor) jobs.job[n++] = {amax_r, nullptr, nullptr, rows, cols / 16, sf_layout, scales, unit, 0, nullptr, nullptr, records, 0};
   if (transposed)
-    jobs.job[n++] = {amax_t, head + 2, head + 1, cols, rows / 16, sf_layout, scales_t, unit_t, 0,
-                     token_sums_t ? reinterpret_cast<const uint2*>(codes_t) : nullptr, token_sums_t};
+    jobs.job[n++] = {amax_t, nullptr, nullptr, cols, rows / 16, sf_layout, scales_t, unit_t, 0,
+                     token_sums_t ? reinterpret_cast<const uint2*>(codes_t) : nullptr, token_sums_t, records, 1};
   if (n == 0) return METIS_OK;
   return launch_finalize_jobs(jobs, n, st, ctr);      // job 0 of the launch bumps the Philox offset counter, if there is one
 }
 
 extern "C" int64_t metis_nvfp4_quantize_dual_workspace_bytes(int64_t rows, int64_t cols) {
-  if (rows <= 0 || cols <= 0) return kHeaderBytes;
-  return kHeaderBytes + 2 * rows * ceil_div(cols, 16) * (int64_t)sizeof(float);
+  if (rows <= 0 || cols <= 0) return kDualHeaderBytes;
+  return kDualHeaderBytes + 2 * rows * ceil_div(cols, 16) * (int64_t)sizeof(float);
 }
 
 extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int64_t rows, int64_t cols, int64_t ld,
@@ -941,12 +1034,11 @@ extern "C" int32_t metis_nvfp4_quantize_dual(const void* x, int32_t x_dtype, int
   if (rows >= ((int64_t)1 << 31) || cols >= ((int64_t)1 << 31)) return fail(METIS_ERR_TOO_LARGE, "tensor too large");
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  // header: [0] largest block maximum of Q, [1] error word, [2] largest block maximum of Qt
-  unsigned int* head = static_cast<unsigned int*>(workspace);
-  float* amax_r = reinterpret_cast<float*>(static_cast<char*>(workspace) + kHeaderBytes);
+  // every CTA of the first pass leaves its maxima and its error word in a record of its own: nothing to zero first
+  unsigned int* records = static_cast<unsigned int*>(workspace) + 64;
+  float* amax_r = reinterpret_cast<float*>(static_cast<char*>(workspace) + kDualHeaderBytes);
   float* amax_t = amax_r + rows * (cols / 16);
-  METIS_CUDA_OK(cudaMemsetAsync(head, 0, 3 * sizeof(unsigned int), st));
-  const TileOutputs out = {codes_t, amax_t, head + 2, codes, amax_r, head, head + 1, rht, (flags & METIS_Q_SR16) ? 1u : 0u};
+  const TileOutputs out = {codes_t, amax_t, nullptr, codes, amax_r, nullptr, nullptr, records, rht, (flags & METIS_Q_SR16) ? 1u : 0u};
   const int32_t rc = x_dtype == METIS_DTYPE_BF16
       ? launch_tile(static_cast<const __nv_bfloat16*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st)
       : launch_tile(static_cast<const float*>(x), rows, cols, ld, col_mean, sr, seed, offset, ctr, out, st);

@@ -160,8 +160,9 @@ int32_t metis_nvfp4_quantize(const void* x, int32_t x_dtype, int64_t rows, int64
  * :400-402, :580).  Reads x from HBM once instead of twice; outputs are bit-identical to two calls of
  * metis_nvfp4_quantize (round to nearest; stochastic rounding draws from two disjoint Philox
  * counter spaces).  rows and cols must both be multiples of 16.  flags: METIS_Q_STOCHASTIC, METIS_Q_SR16,
- * METIS_Q_OFFSET_ON_DEVICE, METIS_Q_HADAMARD, METIS_Q_DEFER_*.  Launches: zero-fill of the workspace header, one tile pass, one scale
- * pass that finishes both outputs.
+ * METIS_Q_OFFSET_ON_DEVICE, METIS_Q_HADAMARD, METIS_Q_DEFER_*.  Launches: one tile pass (every CTA leaves its largest
+ * block maxima in a record of its own in the workspace, so nothing is zeroed first), one scale pass that finishes both
+ * outputs.
  *   codes    uint8 [rows, cols/2]   scales    metis_nvfp4_sf_bytes(rows, cols, sf_layout)   unit    fp32 [1]
  *   codes_t  uint8 [cols, rows/2]   scales_t  metis_nvfp4_sf_bytes(cols, rows, sf_layout)   unit_t  fp32 [1]
  *   token_sums_t  optional fp32 [cols]: sum over the rows of x (the tokens) of the quantized values,
