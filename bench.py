@@ -382,6 +382,52 @@ def run_decode_layer(args):
         del layer
 
 
+def run_decode_block(args):
+    """`--only decode_block`: the rollout forward (no_grad, packed-weight cache) of ONE decoder block of the 7B
+    configuration at 1-128 tokens, `steps` forwards replayed as one CUDA graph: the seven Metis projections with
+    their fused norms, attention over the tokens of the call.  `grouped`: q/k/v and gate/up issued as parallel
+    branches behind their shared quantization (forward_group) against one projection after the other."""
+    import torch
+    import fp4_post_b200
+    from fp4_post_b200.graphs import GraphedStep
+    fp4_post_b200.install_reference_aliases()
+    from fp4_post_b200.decoder import Block, QWEN2_7B
+    from Metis.Metis import bitlinear
+    from grpo.grpo import MetisArgs, replace_linear_with_metis
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    cfg = QWEN2_7B
+    blk = Block(cfg, fuse_norms=True).to(dev).to(torch.bfloat16)
+    margs = MetisArgs(forward_svd_rank=RANK, activation_lowrank_svd=RANK, backward_lowrank_svd=RANK, cache_quantized_weight=True)
+    margs.device = dev
+    replace_linear_with_metis(blk, dtype=torch.bfloat16, metis_args=margs, compute_dtype=torch.bfloat16)
+    for tokens in (1, 16, 32, 128):
+        x = torch.randn(1, tokens, cfg.hidden, device=dev, dtype=torch.bfloat16)
+        ang = torch.zeros(1, 1, tokens, cfg.head_dim, device=dev, dtype=torch.bfloat16)
+        cos, sin = ang.cos(), ang.sin()
+        out = {"only": "decode_block", "tokens": tokens, "hidden": cfg.hidden, "ffn": cfg.ffn, "rank": RANK}
+        for grouped in (False, True):
+            bitlinear.GROUP_BRANCHES = grouped
+
+            def burst():
+                with torch.no_grad():
+                    for _ in range(args.steps):
+                        y = blk(x, cos, sin)
+                return y
+            graphed = GraphedStep(burst, warmup=2)
+            graphed()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graphed()
+            e1.record()
+            torch.cuda.synchronize()
+            out["grouped_us" if grouped else "sequential_us"] = round(e0.elapsed_time(e1) / args.steps * 1e3, 2)
+            graphed.release()
+        bitlinear.GROUP_BRANCHES = True
+        print(json.dumps(out), flush=True)
+
+
 def run_gemm_yardstick(args):
     """`--only gemm_yardstick`: cuBLASLt's NVFP4 GEMM (e2m1 codes, E4M3 scales per 16 elements, through
     torch._scaled_mm) on random codes and unit scales; one JSON line per shape.  A yardstick for the
@@ -767,7 +813,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "quant_dual_sr_sums", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "gemm_sustained", "gemm_accounting", "step_timeline", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer", "c4", "c5_update"],
+    ap.add_argument("--only", default=None, choices=["quant_rows", "quant_transposed", "quant_dual", "quant_dual_sr", "quant_dual_sr_sums", "rmsnorm_quant", "gemm", "gemm_sweep", "gemm_yardstick", "gemm_sustained", "gemm_accounting", "step_timeline", "rmsnorm_sweep", "decode_quant_sweep", "decode_layer", "decode_block", "c4", "c5_update"],
                     help="time one kernel alone on a small case (the command used for ncu captures)")
     ap.add_argument("--layers", type=int, default=1,
                     help="stack this many Metis layers (the headline is 1): with several GPUs the gradient all-reduce "
@@ -796,6 +842,8 @@ def main():
         return run_step_timeline(args)
     if args.only == "rmsnorm_sweep":
         return run_rmsnorm_sweep(args)
+    if args.only == "decode_block":
+        return run_decode_block(args)
     if args.only == "decode_layer":
         return run_decode_layer(args)
     if args.only == "decode_quant_sweep":

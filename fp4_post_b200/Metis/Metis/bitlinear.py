@@ -554,12 +554,57 @@ def _finish_beside(finish, device):
     return done
 
 
+GROUP_BRANCHES = True     # forward_group: members of a projection group on streams of their own (rollout)
+_BRANCH = 0          # which member of a projection group is being issued (forward_group): each has its own side streams
+
+
 def _aux_stream(device: torch.device, index: int = 0) -> "torch.cuda.Stream":
     """The second (index 0), third or fourth stream of `device` for work that may overlap the current stream's."""
-    st = _AUX_STREAMS.get((device, index))
+    key = (device, index, _BRANCH)
+    st = _AUX_STREAMS.get(key)
     if st is None:
-        st = _AUX_STREAMS[(device, index)] = torch.cuda.Stream(device=device)
+        st = _AUX_STREAMS[key] = torch.cuda.Stream(device=device)
     return st
+
+
+def forward_group(layers, x: torch.Tensor):
+    """[layer(x) for layer in layers] for projections that read the same activation (q/k/v, gate/up: the groups
+    of bitlinear.py:676-702, which quantize that activation once).  At rollout sizes a member's forward is a chain
+    of half a dozen kernels of a few microseconds each, far too small to fill the GPU, so without autograd the
+    members are issued on streams of their own behind the shared quantization and run side by side (inside a
+    captured graph: parallel branches).  Results are bit for bit those of the calls one after the other."""
+    global _BRANCH
+    layers = list(layers)
+    parallel = (GROUP_BRANCHES and len(layers) > 1 and x.is_cuda and not torch.is_grad_enabled()
+                and MetisFusedFunction.concurrent_branches and _BRANCH == 0 and all(isinstance(l, BitLinear) and l.is_svd_quant for l in layers))
+    if not parallel:
+        return [layer(x) for layer in layers]
+    dev = x.device
+    main = torch.cuda.current_stream(dev)
+    LinearLowbitFunction.mean_cache = layers[0].mean_cache
+    layers[0]._get_shared_quantized_input(x)          # a grouped activation is quantized here, once, in front of the fork
+    fork = torch.cuda.Event()
+    fork.record(main)
+    outs = [None] * len(layers)
+    try:
+        for i in range(1, len(layers)):
+            _BRANCH = i
+            st = _aux_stream(dev, 3)
+            st.wait_event(fork)
+            with torch.cuda.stream(st):
+                outs[i] = layers[i](x)
+                done = torch.cuda.Event()
+                done.record(st)
+            outs[i].record_stream(main)
+            outs[i] = (outs[i], done)
+    finally:
+        _BRANCH = 0
+    outs[0] = layers[0](x)
+    for i in range(1, len(layers)):
+        y, done = outs[i]
+        main.wait_event(done)
+        outs[i] = y
+    return outs
 
 
 class _beside:

@@ -182,6 +182,130 @@ gemv_tall_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ sc
   }
 }
 
+// The same product with the vector staged in shared memory once per CTA and shared by all its rows: a CTA
+// takes 8 * kRowsPerWarp consecutive rows and the whole of C, a warp kRowsPerWarp of them, a lane the blocks
+// lane, lane + 32, ...  From global memory a block then costs its 8 bytes of codes and its scale byte; the 64
+// bytes of v come from shared memory (stored chunk-major, so the lanes' 16-byte reads are conflict free) and are
+// used for every row of the warp.  gemv_kernel reads v through L1 once per row: 8 times the bytes of the
+// codes, which is what bounds it on wide matrices (3584 x 18944: 50 us; here 10).  Codes become floats by the
+// hardware conversion, two per instruction.
+constexpr int64_t kGemvStagedMaxCols = 40960;           // 160 KiB of v
+constexpr int64_t kGemvStagedMinCols = 2048;
+template <int kRowsPerWarp>
+__global__ void __launch_bounds__(256)
+gemv_staged_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
+                   const float* __restrict__ unit_ptr, int32_t sf_layout, int64_t R, int64_t C,
+                   const float* __restrict__ v, float* __restrict__ out) {
+  extern __shared__ float4 s_v[];                          // [4][sf_cols]: chunk j of block k at j * sf_cols + k
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sf_cols = (int)(C >> 4);                       // blocks per row
+  const int64_t tiles = sf_tiles_per_row(C);
+  for (int i = threadIdx.x; i < sf_cols * 4; i += 256)     // coalesced read of v, scattered 16-byte writes
+    s_v[(i & 3) * sf_cols + (i >> 2)] = __ldg(reinterpret_cast<const float4*>(v) + i);
+  __syncthreads();
+  const int64_t row0 = ((int64_t)blockIdx.x * 8 + warp) * kRowsPerWarp;
+  if (row0 >= R) return;
+  float acc[kRowsPerWarp];
+#pragma unroll
+  for (int j = 0; j < kRowsPerWarp; ++j) acc[j] = 0.0f;
+#pragma unroll(kRowsPerWarp == 1 ? 4 : 2)
+  for (int k = lane; k < sf_cols; k += 32) {
+    uint2 w2[kRowsPerWarp];
+    uint32_t sb[kRowsPerWarp];
+#pragma unroll
+    for (int j = 0; j < kRowsPerWarp; ++j) {               // every global load of the trip before the arithmetic
+      const int64_t row = row0 + j < R ? row0 + j : R - 1;
+      w2[j] = __ldg(codes + row * sf_cols + k);
+      const int64_t off = (sf_layout == METIS_SF_MMA) ? sf_mma_offset(row, k, tiles) : row * sf_cols + k;
+      sb[j] = __ldg(scales + off);
+    }
+    float f[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 q = s_v[i * sf_cols + k];
+      f[4 * i] = q.x; f[4 * i + 1] = q.y; f[4 * i + 2] = q.z; f[4 * i + 3] = q.w;
+    }
+#pragma unroll
+    for (int j = 0; j < kRowsPerWarp; ++j) {
+      const uint32_t w[2] = {w2[j].x, w2[j].y};
+      float part = 0.0f;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        const float2 c = e2m1x2_to_float2((w[b >> 2] >> (8 * (b & 3))) & 0xFFu);
+        part = fmaf(c.x, f[2 * b], part);
+        part = fmaf(c.y, f[2 * b + 1], part);
+      }
+      acc[j] = fmaf(part, e4m3_to_float((uint8_t)sb[j]), acc[j]);
+    }
+  }
+  const float unit = __ldg(unit_ptr);
+#pragma unroll
+  for (int j = 0; j < kRowsPerWarp; ++j) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    if (lane == 0 && row0 + j < R) out[row0 + j] = acc[j] * unit;
+  }
+}
+
+// Few, wide rows (the rank-r factor V against a wide activation mean): one row per CTA, its blocks dealt round
+// robin to all 256 threads, the eight warps' sums added in warp order.
+__global__ void __launch_bounds__(256)
+gemv_row_kernel(const uint2* __restrict__ codes, const uint8_t* __restrict__ scales,
+                const float* __restrict__ unit_ptr, int32_t sf_layout, int64_t R, int64_t C,
+                const float* __restrict__ v, float* __restrict__ out) {
+  __shared__ float s_part[8];
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = blockIdx.x;
+  const int sf_cols = (int)(C >> 4);
+  const int64_t tiles = sf_tiles_per_row(C);
+  float acc = 0.0f;
+#pragma unroll 2
+  for (int k = threadIdx.x; k < sf_cols; k += 256) {
+    const uint2 w2 = __ldg(codes + row * sf_cols + k);
+    const int64_t off = (sf_layout == METIS_SF_MMA) ? sf_mma_offset(row, k, tiles) : row * sf_cols + k;
+    const uint32_t sb = __ldg(scales + off);
+    const float4* v4 = reinterpret_cast<const float4*>(v) + 4 * (int64_t)k;
+    float f[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 q = __ldg(v4 + i);
+      f[4 * i] = q.x; f[4 * i + 1] = q.y; f[4 * i + 2] = q.z; f[4 * i + 3] = q.w;
+    }
+    const uint32_t w[2] = {w2.x, w2.y};
+    float part = 0.0f;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const float2 c = e2m1x2_to_float2((w[b >> 2] >> (8 * (b & 3))) & 0xFFu);
+      part = fmaf(c.x, f[2 * b], part);
+      part = fmaf(c.y, f[2 * b + 1], part);
+    }
+    acc = fmaf(part, e4m3_to_float((uint8_t)sb), acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) s_part[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) sum += s_part[w8];
+    out[row] = sum * __ldg(unit_ptr);
+  }
+}
+
+template <int kRowsPerWarp>
+static cudaError_t launch_gemv_staged(const uint2* codes, const uint8_t* scales, const float* unit, int32_t sf_layout,
+                                      int64_t R, int64_t C, const float* v, float* out, cudaStream_t st) {
+  auto kern = gemv_staged_kernel<kRowsPerWarp>;
+  const size_t smem = (size_t)C * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  return launch_overlapped(kLaunchShort, kern, dim3((unsigned)ceil_div(R, 8 * kRowsPerWarp)), dim3(256), smem, st,
+                           codes, scales, unit, sf_layout, R, C, v, out);
+}
+
 // t = bf16( float(bf16(yv * s)) / (unit_a * unit_b) ), 8 elements per thread
 template <typename TS>
 __global__ void __launch_bounds__(256)
@@ -274,7 +398,18 @@ extern "C" int32_t metis_nvfp4_gemv(const uint8_t* codes, const uint8_t* scales,
   if (v && !aligned16(v)) return fail(METIS_ERR_BAD_ALIGNMENT, "v must be 16-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const uint2* c4 = reinterpret_cast<const uint2*>(codes);
-  if (v && R >= kGemvTallMinRows) launch_overlapped(kLaunchShort, gemv_tall_kernel, dim3((unsigned)ceil_div(R, 8 * kGemvTallRows)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
+  // rows of 2048 elements and more: the kernel that stages v in shared memory; too few rows for it: a CTA per
+  // row.  Every CTA stages the whole of v, so with very wide rows fewer CTAs of more rows win although they
+  // fill the SMs less evenly (3584 x 18944: 16 rows per CTA 19.6 us, 8 rows 28.2).
+  if (v && C >= kGemvStagedMinCols && C <= kGemvStagedMaxCols) {
+    const int64_t sms = device_sm_count();
+    const bool wide = C >= 8192;
+    const int64_t want = wide ? sms : 3 * sms;               // CTAs a launch should at least have
+    if (ceil_div(R, 32) >= want) METIS_CUDA_OK(launch_gemv_staged<4>(c4, scales, unit, sf_layout, R, C, v, out, st));
+    else if (ceil_div(R, 16) >= want) METIS_CUDA_OK(launch_gemv_staged<2>(c4, scales, unit, sf_layout, R, C, v, out, st));
+    else if (R >= (wide ? 4 * sms : want)) METIS_CUDA_OK(launch_gemv_staged<1>(c4, scales, unit, sf_layout, R, C, v, out, st));
+    else METIS_CUDA_OK(launch_overlapped(kLaunchShort, gemv_row_kernel, dim3((unsigned)R), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out));
+  } else if (v && R >= kGemvTallMinRows) launch_overlapped(kLaunchShort, gemv_tall_kernel, dim3((unsigned)ceil_div(R, 8 * kGemvTallRows)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
   else if (v) launch_overlapped(kLaunchShort, gemv_kernel<true>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
   else   launch_overlapped(kLaunchShort, gemv_kernel<false>, dim3((unsigned)ceil_div(R, 8)), dim3(256), 0, st, c4, scales, unit, sf_layout, R, C, v, out);
   METIS_CUDA_OK(cudaGetLastError());

@@ -21,6 +21,7 @@ import torch
 import torch.nn.functional as Fn
 from torch import nn
 
+from fp4_post_b200.Metis.Metis.bitlinear import forward_group
 from fp4_post_b200.Metis.models.llama import RMSNorm
 
 
@@ -67,9 +68,10 @@ class Attention(nn.Module):
     def forward(self, h, cos, sin):
         B, T, _ = h.shape
         c = self.cfg
-        q = self.q_proj(h).view(B, T, c.heads, c.head_dim).transpose(1, 2)
-        k = self.k_proj(h).view(B, T, c.kv_heads, c.head_dim).transpose(1, 2)
-        v = self.v_proj(h).view(B, T, c.kv_heads, c.head_dim).transpose(1, 2)
+        q, k, v = forward_group((self.q_proj, self.k_proj, self.v_proj), h)     # one shared activation, three branches
+        q = q.view(B, T, c.heads, c.head_dim).transpose(1, 2)
+        k = k.view(B, T, c.kv_heads, c.head_dim).transpose(1, 2)
+        v = v.view(B, T, c.kv_heads, c.head_dim).transpose(1, 2)
         q, k = _rope(q, cos, sin), _rope(k, cos, sin)
         a = Fn.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
         return self.o_proj(a.transpose(1, 2).reshape(B, T, c.heads * c.head_dim))
@@ -83,7 +85,8 @@ class MLP(nn.Module):
         self.down_proj = nn.Linear(cfg.ffn, cfg.hidden, bias=False)
 
     def forward(self, h):
-        return self.down_proj(Fn.silu(self.gate_proj(h)) * self.up_proj(h))
+        gate, up = forward_group((self.gate_proj, self.up_proj), h)
+        return self.down_proj(Fn.silu(gate) * up)
 
 
 class Block(nn.Module):

@@ -13,7 +13,8 @@ fp4_post_b200.install_reference_aliases()
 from fp4_post_b200.decoder import Decoder, DecoderConfig  # noqa: E402
 from fp4_post_b200.graphs import GraphedStep  # noqa: E402
 from grpo.grpo import MetisArgs, replace_linear_with_metis  # noqa: E402
-from Metis.Metis.bitlinear import BitLinear, LinearLowbitFunction as F  # noqa: E402
+from Metis.Metis import bitlinear  # noqa: E402
+from Metis.Metis.bitlinear import BitLinear, LinearLowbitFunction as F, forward_group  # noqa: E402
 from Metis.Metis.quant import Cast2NVFp4e2m1BlockNOSR  # noqa: E402
 
 pytestmark = pytest.mark.gpu
@@ -89,3 +90,37 @@ def test_a_whole_decoder_step_replays_from_one_graph():
     graphed.release()
     assert abs(l1 - eager) < 1e-3 * abs(eager) and l1 == l2            # the forward rounds to nearest: deterministic
     assert torch.isfinite(g2).all() and not torch.equal(g1, g2)         # the backward draws fresh bits per replay
+
+
+@pytest.mark.parametrize("tokens", [16, 128])
+def test_a_projection_group_on_parallel_streams_equals_the_calls_one_after_the_other(tokens):
+    """Rollout (no_grad): q/k/v and gate/up run as branches of their own behind the shared quantization; the
+    logits are bit for bit those of the sequential forward, eagerly and replayed from a CUDA graph."""
+    model = _metis_decoder(True)
+    for m in model.modules():
+        if hasattr(m, "cache_quantized_weight"):
+            m.cache_quantized_weight = True
+    ids = torch.randint(0, SMALL.vocab, (1, tokens), device=DEV, generator=torch.Generator(device=DEV).manual_seed(3))
+    attn = model.layers[0].self_attn
+    h = torch.randn(1, tokens, SMALL.hidden, device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        bitlinear.GROUP_BRANCHES = False
+        try:
+            want_logits = model(ids)
+            want = forward_group((attn.q_proj, attn.k_proj, attn.v_proj), h)
+        finally:
+            bitlinear.GROUP_BRANCHES = True
+        got = forward_group((attn.q_proj, attn.k_proj, attn.v_proj), h)
+        logits = model(ids)
+        torch.cuda.synchronize()
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+        assert torch.equal(logits, want_logits)
+
+        def rollout():
+            return model(ids)
+        graphed = GraphedStep(rollout, warmup=2)
+        replayed = graphed()
+        torch.cuda.synchronize()
+        assert torch.equal(replayed, want_logits)
+        graphed.release()

@@ -163,9 +163,11 @@ def test_dequantize_roundtrip_bf16_and_tiled_scales():
         assert np.array_equal(got16, torch.from_numpy(want).to(torch.bfloat16).float().numpy())
 
 
-# the vector product: a warp per row (short and long rows, a row count that is not a multiple of 8), and
-# four rows per warp for tall matrices (12290 rows leave a warp with two live rows)
-@pytest.mark.parametrize("rows,cols", [(200, 512), (128, 4096), (2050, 1024), (12290, 272)])
+# the vector product: a warp per row (short and long rows, a row count that is not a multiple of 8); tall and wide
+# matrices with the vector staged in shared memory (12290 rows leave a warp with two live rows; 1, 2 and 4 rows per
+# warp); few wide rows with a CTA per row
+@pytest.mark.parametrize("rows,cols", [(200, 512), (128, 4096), (2050, 1024), (12290, 272), (40, 8208), (600, 8192),
+                                       (2372, 8192), (7202, 2048), (14306, 2064)])
 @pytest.mark.parametrize("layout", [cabi.SF_ROWMAJOR, cabi.SF_MMA])
 def test_gemv_and_row_sums(rows, cols, layout):
     x = synthetic(rows, cols, "normal", seed=13 + rows, dtype=torch.float32)
