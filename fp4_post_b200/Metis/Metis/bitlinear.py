@@ -540,10 +540,12 @@ _ONES = {}
 _AUX_STREAMS = {}
 
 
-def _finish_beside(finish, device):
-    """Run the deferred scale pass of a dual quantization (ops.nvfp4_quantize_dual(defer=...)) on the stream kept
-    for such passes, after everything issued so far on the current stream.  Returns the event that marks it done."""
-    here, beside = torch.cuda.current_stream(device), _aux_stream(device, 2)
+def _finish_beside(finish, device, index=2):
+    """Run the deferred scale pass of a dual quantization (ops.nvfp4_quantize_dual(defer=...)) on a stream kept
+    for such passes (index 2: activations and gradients, 4: weights, which are quantized on the second stream and
+    would otherwise hold up the activation's pass queued behind theirs), after everything issued so far on the
+    current stream.  Returns the event that marks it done."""
+    here, beside = torch.cuda.current_stream(device), _aux_stream(device, index)
     issued = torch.cuda.Event()
     issued.record(here)
     beside.wait_event(issued)
@@ -801,7 +803,7 @@ class LinearLowbit(torch.nn.Module):
                 if F.defer_scale_pass and not self.cache_quantized_weight:
                     # only the backward reads the transposed quantization: its scale pass leaves the forward's path
                     q, qt, finish = F.q_forward_weight.quantize_packed_dual(source, defer="transposed")
-                    done = _finish_beside(finish, source.device)
+                    done = _finish_beside(finish, source.device, index=4)
                 else:
                     q, qt = F.q_forward_weight.quantize_packed_dual(source)
             else:
@@ -850,6 +852,11 @@ class MetisFusedFunction(torch.autograd.Function):
         act = xa.dtype if xa.dtype in (torch.bfloat16, torch.float32) else torch.float32
         rank1_v, rank1_r = [], []
         join_residual = None
+
+        def ready(op):
+            if op.ready_event is not None:             # quantized on another stream: order this stream after it, once
+                torch.cuda.current_stream(xa.q.device).wait_event(op.ready_event)
+                op.ready_event = None
         if xa.mean is not None:
             # mu_x V^T and mu_x R^T need the mean only: on the second stream they run beside the
             # quantization of x instead of after it
@@ -857,13 +864,20 @@ class MetisFusedFunction(torch.autograd.Function):
             # stream are still being quantized here)
             beside = vq.ready_event is not None and rq.ready_event is not None
             overlap = MetisFusedFunction.concurrent_branches and (beside or (not vq.fresh and not rq.fresh))
+            if not overlap:
+                ready(vq)
+                ready(rq)
             with _beside(xa.mean_event if overlap else None, xa.mean.device) as join:
+                if overlap and vq.ready_event is not None:      # quantized on a stream of their own: order this one after each
+                    torch.cuda.current_stream(xa.mean.device).wait_event(vq.ready_event)
                 row_v = ops.nvfp4_gemv(vq.q, xa.mean)
                 # the product with V needs only this one: the pass over the (much larger) residual
                 # weight stays off the critical path until the residual product
                 v_ready = torch.cuda.Event() if overlap else None
                 if v_ready is not None:
                     v_ready.record()
+                if overlap and rq.ready_event is not None:
+                    torch.cuda.current_stream(xa.mean.device).wait_event(rq.ready_event)
                 row_r = ops.nvfp4_gemv(rq.q, xa.mean)
             if v_ready is not None:
                 torch.cuda.current_stream(xa.mean.device).wait_event(v_ready)
@@ -873,10 +887,7 @@ class MetisFusedFunction(torch.autograd.Function):
             rank1_r.append((None, row_r))
         if bias is not None:
             rank1_r.append((None, bias.float()))
-        for op in (vq, rq):
-            if op.ready_event is not None:             # quantized on the second stream: order this stream after it, once
-                torch.cuda.current_stream(xa.q.device).wait_event(op.ready_event)
-                op.ready_event = None
+        ready(vq)
         yv = _packed_matmul(xa.q, vq.q, rank1=rank1_v, out_dtype=act)                 # [M, r]
         # torch.mul(self.s, y), in the units the side product accumulates in: 1/(unit_x * unit_R)
         if act == torch.bfloat16:
@@ -886,6 +897,7 @@ class MetisFusedFunction(torch.autograd.Function):
             lowrank = _bf16_factors(ts.float() / (xa.q.unit * rq.q.unit), u_weight.detach(), act)
         if join_residual is not None:
             join_residual()
+        ready(rq)
         y = _packed_matmul(xa.q, rq.q, rank1=rank1_r, lowrank=lowrank, out_dtype=act)
         if (MetisFusedFunction.concurrent_branches and xa.q.codes.is_cuda and any(ctx.needs_input_grad)
                 and xa._qt is not None and LinearLowbitFunction._backward_centred()):
@@ -1234,15 +1246,19 @@ class BitLinear(nn.Module):
         if v.cache_quantized_weight and w.cache_quantized_weight and v._quantized_weight_cache is not None \
                 and w._quantized_weight_cache is not None:
             return                                        # (probably) cache hits: nothing to overlap
-        main, aux = torch.cuda.current_stream(x.device), _aux_stream(x.device)
+        # a stream of their own (not the one the mean's row vectors run on: those would queue behind the residual
+        # weight's quantization although the first of them needs V only)
+        main, aux = torch.cuda.current_stream(x.device), _aux_stream(x.device, 5)
         aux.wait_stream(main)
         with torch.cuda.stream(aux):
-            # the large one first: it then runs beside the activation's column sums, not beside its quantization
-            rq = w._get_quantized_weight(w.weight.to(w.compute_dtype))
+            # the small one first: the product with V is the first consumer on the forward's critical path
             vq = v._get_quantized_weight(v.weight.to(v.compute_dtype))
-            done = torch.cuda.Event()
-            done.record(aux)
-        for op in (vq, rq):
+            v_done = torch.cuda.Event()
+            v_done.record(aux)
+            rq = w._get_quantized_weight(w.weight.to(w.compute_dtype))
+            r_done = torch.cuda.Event()
+            r_done.record(aux)
+        for op, done in ((vq, v_done), (rq, r_done)):
             if isinstance(op, PackedOperand) and op.fresh:
                 op.ready_event = done
                 for q in (op.q, op._qt):
