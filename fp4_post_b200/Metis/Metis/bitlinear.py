@@ -562,11 +562,20 @@ _BRANCH = 0          # which member of a projection group is being issued (forwa
 
 def _aux_stream(device: torch.device, index: int = 0) -> "torch.cuda.Stream":
     """The second (index 0), third or fourth stream of `device` for work that may overlap the current stream's."""
-    key = (device, index, _BRANCH)
+    # the streams of deferred scale passes (2, 4) yield to everything else: their results are wanted last.  Not in a
+    # data-parallel step: the collectives' kernel (default priority) would queue behind every side stream for the
+    # SMs the capped GEMM leaves it
+    priority = 0 if (index in (2, 4) or GRADIENT_REDUCER is not None) else -1
+    key = (device, index, _BRANCH, priority)
     st = _AUX_STREAMS.get(key)
     if st is None:
-        st = _AUX_STREAMS[key] = torch.cuda.Stream(device=device)
+        st = _AUX_STREAMS[key] = torch.cuda.Stream(device=device, priority=priority)
     return st
+
+
+def critical_path_priority() -> int:
+    """Priority for the stream a step is issued or captured on (see _aux_stream)."""
+    return 0 if GRADIENT_REDUCER is not None else -1
 
 
 def forward_group(layers, x: torch.Tensor):

@@ -26,6 +26,23 @@ from typing import Any, Callable, Optional
 import torch
 
 
+_CAPTURE_STREAMS = {}
+
+
+def _capture_stream() -> "torch.cuda.Stream":
+    """The stream every capture on the current device runs on (one per device: autograd ties a parameter's gradient
+    accumulation to the stream of its first backward, so a second capture on another stream would depend on
+    uncaptured work).  High priority in a single-process step: the capturing stream carries the step's critical
+    path, and the streams the library keeps for deferred scale passes have the lowest, so where both have CTAs
+    waiting the path goes first."""
+    dev = torch.cuda.current_device()
+    st = _CAPTURE_STREAMS.get(dev)
+    if st is None:                # the priority is settled by the first capture of the process
+        from fp4_post_b200.Metis.Metis.bitlinear import critical_path_priority
+        st = _CAPTURE_STREAMS[dev] = torch.cuda.Stream(priority=critical_path_priority())
+    return st
+
+
 class GraphedStep:
     """`fn` (no arguments; it reads static input tensors and returns tensors or None) captured into one
     CUDA graph.  Calling the object replays the graph and returns what `fn` returned during capture
@@ -50,7 +67,7 @@ class GraphedStep:
             cur.wait_stream(side)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph, pool=pool):
+            with torch.cuda.graph(self.graph, pool=pool, stream=_capture_stream()):
                 self.outputs = fn()
         finally:
             if quiet is not None:
