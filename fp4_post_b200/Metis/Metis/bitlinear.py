@@ -561,7 +561,9 @@ _BRANCH = 0          # which member of a projection group is being issued (forwa
 
 
 def _aux_stream(device: torch.device, index: int = 0) -> "torch.cuda.Stream":
-    """The second (index 0), third or fourth stream of `device` for work that may overlap the current stream's."""
+    """A side stream of `device` for work that may overlap the current stream's.  Index 0: the low-rank branch and
+    the mean's row vectors; 1: the mean row of the input gradient; 2, 4: deferred scale passes (activations and
+    gradients, weights); 3: members of a projection group (forward_group); 5: the weights' quantization."""
     # the streams of deferred scale passes (2, 4) yield to everything else: their results are wanted last.  Not in a
     # data-parallel step: the collectives' kernel (default priority) would queue behind every side stream for the
     # SMs the capped GEMM leaves it
