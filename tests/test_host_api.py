@@ -265,6 +265,23 @@ def test_projections_of_one_group_quantize_their_input_once():
     gc.collect()
 
 
+def test_forward_group_off_the_gpu_is_the_calls_one_after_the_other():
+    from Metis.Metis.bitlinear import forward_group
+    Q = counting_quantizer()
+    F.q_forward_input = Q
+    mean_mode()
+    group = {"name": "blk.attention.qkv", "mean_cache": {}, "input_ref": None, "quantized_input": None}
+    q_proj, k_proj = svd_layer("blk.q_proj", group), svd_layer("blk.k_proj", group)
+    x = torch.randn(2, 3, 16)
+    with torch.no_grad():
+        got = forward_group((q_proj, k_proj), x)
+        want = [q_proj(x), k_proj(x)]
+    assert Q.calls == 1                                  # one shared quantization for all four calls
+    assert all(torch.equal(a, b) for a, b in zip(got, want))
+    plain = torch.nn.Linear(16, 8)
+    assert torch.equal(forward_group((plain,), x)[0], plain(x))        # anything callable, e.g. before the layers are installed
+
+
 def test_group_entry_is_dropped_when_the_input_dies():
     mean_mode()
     group = {"name": "g", "mean_cache": {}, "input_ref": None, "quantized_input": None}
