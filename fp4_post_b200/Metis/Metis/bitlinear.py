@@ -594,8 +594,9 @@ def forward_group(layers, x: torch.Tensor):
         return [layer(x) for layer in layers]
     dev = x.device
     main = torch.cuda.current_stream(dev)
-    LinearLowbitFunction.mean_cache = layers[0].mean_cache
-    layers[0]._get_shared_quantized_input(x)          # a grouped activation is quantized here, once, in front of the fork
+    if getattr(layers[0], "activation_group", None) is not None:
+        LinearLowbitFunction.mean_cache = layers[0].mean_cache
+        layers[0]._get_shared_quantized_input(x)      # a grouped activation is quantized here, once, in front of the fork
     fork = torch.cuda.Event()
     fork.record(main)
     outs = [None] * len(layers)
